@@ -1,0 +1,297 @@
+/*
+ * TEST INFRASTRUCTURE ONLY -- see matmul_oracle.h.  Every function cites the
+ * reference lines it restates.  Build with -ffp-contract=off (oracle/Makefile):
+ * the reference's loops round the multiply and the add separately.
+ */
+#include "matmul_oracle.h"
+#include <stdlib.h>
+#include <string.h>
+
+static size_t esize(int dtype) {
+    switch (dtype) {
+        case ORC_F32: return 4;
+        case ORC_F64: return 8;
+        case ORC_F16: case ORC_BF16: return 2;
+        default: return 0;
+    }
+}
+
+static float bits_to_float(uint32_t u) { float f; memcpy(&f, &u, 4); return f; }
+static uint32_t float_to_bits(float f) { uint32_t u; memcpy(&u, &f, 4); return u; }
+
+/* core/half_precision.h:20-48 */
+float orc_fp16_to_fp32(uint16_t h) {
+    uint32_t s = (uint32_t)(h & 0x8000u) << 16;
+    uint32_t e = (h >> 10) & 0x1Fu, frac = h & 0x3FFu;
+    if (e == 0) {
+        if (!frac) return bits_to_float(s);
+        /* subnormal: frac/1024 * 2^-14, both steps exact in fp32 */
+        float v = ((float)frac / 1024.0f) * (1.0f / 16384.0f);
+        return s ? -v : v;
+    }
+    if (e == 0x1Fu) return bits_to_float(s | 0x7F800000u | (frac << 13));
+    return bits_to_float(s | ((e + 112u) << 23) | (frac << 13));
+}
+
+/* core/half_precision.h:50-83: round-half-UP on the dropped bits (not RNE); the
+ * carry of the +1 is allowed to ripple into the exponent field. */
+uint16_t orc_fp32_to_fp16(float f) {
+    uint32_t u = float_to_bits(f);
+    uint32_t s = (u >> 16) & 0x8000u;
+    uint32_t be = (u >> 23) & 0xFFu;
+    uint32_t frac = u & 0x7FFFFFu;
+    int32_t e = (int32_t)be - 112;              /* -127 + 15 */
+    if (be == 0xFFu)
+        return (uint16_t)(frac ? (s | 0x7C00u | (frac >> 13) | 1u) : (s | 0x7C00u));
+    if (e <= 0) {
+        if (e < -10) return (uint16_t)s;
+        frac |= 0x800000u;
+        int sh = 14 - e;
+        uint16_t r = (uint16_t)(s | (frac >> sh));
+        return (uint16_t)(r + ((frac >> (sh - 1)) & 1u));
+    }
+    if (e >= 0x1F) return (uint16_t)(s | 0x7C00u);
+    uint16_t r = (uint16_t)(s | ((uint32_t)e << 10) | (frac >> 13));
+    return (uint16_t)(r + ((frac >> 12) & 1u));
+}
+
+/* core/half_precision.h:85-90 */
+float orc_bf16_to_fp32(uint16_t h) { return bits_to_float((uint32_t)h << 16); }
+
+/* core/half_precision.h:92-97: add bit 15 to the upper half, no NaN special case */
+uint16_t orc_fp32_to_bf16(float f) {
+    uint32_t u = float_to_bits(f);
+    return (uint16_t)((u >> 16) + ((u >> 15) & 1u));
+}
+
+/* core/half_precision.h:115-127 */
+void orc_widen(const void* src, float* dst, size_t n, int dtype) {
+    const uint16_t* s = (const uint16_t*)src;
+    if (dtype == ORC_F16) for (size_t i = 0; i < n; i++) dst[i] = orc_fp16_to_fp32(s[i]);
+    else                  for (size_t i = 0; i < n; i++) dst[i] = orc_bf16_to_fp32(s[i]);
+}
+void orc_narrow(const float* src, void* dst, size_t n, int dtype) {
+    uint16_t* d = (uint16_t*)dst;
+    if (dtype == ORC_F16) for (size_t i = 0; i < n; i++) d[i] = orc_fp32_to_fp16(src[i]);
+    else                  for (size_t i = 0; i < n; i++) d[i] = orc_fp32_to_bf16(src[i]);
+}
+
+/* functional/functional_host.c:780-792.  The running sum lives in C itself, in
+ * the storage precision, in (i, j, l) order. */
+int orc_matmul_f32(float* C, const float* A, const float* B, int m, int k, int n) {
+    if (!C || !A || !B || m <= 0 || k <= 0 || n <= 0) return -1;
+    for (int i = 0; i < m; i++) {
+        const float* arow = A + (size_t)i * k;
+        for (int j = 0; j < n; j++) {
+            volatile float acc = 0.0f;          /* forces a rounding per step */
+            for (int l = 0; l < k; l++) {
+                float p = arow[l] * B[(size_t)l * n + j];
+                acc = acc + p;
+            }
+            C[(size_t)i * n + j] = acc;
+        }
+    }
+    return 0;
+}
+
+/* functional/functional_host.c:794-806 */
+int orc_matmul_f64(double* C, const double* A, const double* B, int m, int k, int n) {
+    if (!C || !A || !B || m <= 0 || k <= 0 || n <= 0) return -1;
+    for (int i = 0; i < m; i++) {
+        const double* arow = A + (size_t)i * k;
+        for (int j = 0; j < n; j++) {
+            volatile double acc = 0.0;
+            for (int l = 0; l < k; l++) {
+                double p = arow[l] * B[(size_t)l * n + j];
+                acc = acc + p;
+            }
+            C[(size_t)i * n + j] = acc;
+        }
+    }
+    return 0;
+}
+
+/* functional/functional.c:978-1002: f16/bf16 are widened to fp32, multiplied by
+ * the fp32 loop and narrowed once at the end. */
+int orc_rp_matmul(void* C, const void* A, const void* B, int m, int k, int n, int dtype) {
+    if (!C || !A || !B || m <= 0 || k <= 0 || n <= 0) return -1;
+    if (dtype == ORC_F32) return orc_matmul_f32((float*)C, (const float*)A, (const float*)B, m, k, n);
+    if (dtype == ORC_F64) return orc_matmul_f64((double*)C, (const double*)A, (const double*)B, m, k, n);
+    if (dtype != ORC_F16 && dtype != ORC_BF16) return -1;
+    size_t na = (size_t)m * k, nb = (size_t)k * n, nc = (size_t)m * n;
+    float* wa = (float*)malloc(na * 4);
+    float* wb = (float*)malloc(nb * 4);
+    float* wc = (float*)malloc(nc * 4);
+    int rc = -1;
+    if (wa && wb && wc) {
+        orc_widen(A, wa, na, dtype);
+        orc_widen(B, wb, nb, dtype);
+        rc = orc_matmul_f32(wc, wa, wb, m, k, n);
+        if (rc == 0) orc_narrow(wc, C, nc, dtype);
+    }
+    free(wa); free(wb); free(wc);
+    return rc;
+}
+
+/* functional/functional.c:1130-1220: element gather in row-major index order. */
+int orc_contiguous(void* dst, const void* src, int ndim, const int* shape,
+                   const int* strides, int dtype) {
+    size_t es = esize(dtype);
+    if (!dst || !src || ndim <= 0 || ndim > 8 || !es) return -1;
+    size_t total = 1;
+    for (int d = 0; d < ndim; d++) { if (shape[d] <= 0) return -1; total *= (size_t)shape[d]; }
+    int idx[8] = {0};
+    for (size_t o = 0; o < total; o++) {
+        long off = 0;
+        for (int d = 0; d < ndim; d++) off += (long)idx[d] * strides[d];
+        memcpy((char*)dst + o * es, (const char*)src + off * (long)es, es);
+        for (int d = ndim - 1; d >= 0; d--) { if (++idx[d] < shape[d]) break; idx[d] = 0; }
+    }
+    return 0;
+}
+
+static void* packed_copy(const void* src, const int* strides, int rows, int cols, int dtype) {
+    int shape[2] = {rows, cols};
+    int packed[2] = {cols, 1};
+    void* p = malloc((size_t)rows * cols * esize(dtype));
+    if (!p) return NULL;
+    if (orc_contiguous(p, src, 2, shape, strides ? strides : packed, dtype) != 0) { free(p); return NULL; }
+    return p;
+}
+
+/* ops/ops.c:6816-6847: both inputs are made contiguous (ensure_contiguous,
+ * ops.c:21-25), then rp_matmul. */
+int orc_op_matmul(void* C, const void* A, const int* a_strides, const void* B,
+                  const int* b_strides, int m, int k, int n, int dtype) {
+    if (m <= 0 || k <= 0 || n <= 0) return -1;
+    void* ac = packed_copy(A, a_strides, m, k, dtype);
+    void* bc = packed_copy(B, b_strides, k, n, dtype);
+    int rc = (ac && bc) ? orc_rp_matmul(C, ac, bc, m, k, n, dtype) : -1;
+    free(ac); free(bc);
+    return rc;
+}
+
+/* functional_host.c add (element-wise a+b in the storage dtype); for f16/bf16 the
+ * reference's rp_add widens each element, adds in fp32 and narrows. */
+static void grad_add(void* acc, const void* inc, size_t cnt, int dtype) {
+    if (dtype == ORC_F32) { float* a = (float*)acc; const float* b = (const float*)inc; for (size_t i = 0; i < cnt; i++) a[i] = a[i] + b[i]; }
+    else if (dtype == ORC_F64) { double* a = (double*)acc; const double* b = (const double*)inc; for (size_t i = 0; i < cnt; i++) a[i] = a[i] + b[i]; }
+    else {
+        uint16_t* a = (uint16_t*)acc; const uint16_t* b = (const uint16_t*)inc;
+        for (size_t i = 0; i < cnt; i++) {
+            float x, y;
+            orc_widen(&a[i], &x, 1, dtype); orc_widen(&b[i], &y, 1, dtype);
+            float s = x + y;
+            orc_narrow(&s, &a[i], 1, dtype);
+        }
+    }
+}
+
+/* ops/ops.c:6759-6814: dA[m,k] = dC[m,n] x contiguous(B^T)[n,k],
+ * dB[k,n] = contiguous(A^T)[k,m] x dC[m,n]. */
+int orc_matmul_backward(void* dA, void* dB, const void* A, const int* a_strides,
+                        const void* B, const int* b_strides, const void* dC,
+                        int m, int k, int n, int dtype, int accumulate) {
+    size_t es = esize(dtype);
+    if (!es || m <= 0 || k <= 0 || n <= 0 || !dC) return -1;
+    int pa[2] = {k, 1}, pb[2] = {n, 1};
+    if (!a_strides) a_strides = pa;
+    if (!b_strides) b_strides = pb;
+    if (dA) {
+        int ts[2] = {b_strides[1], b_strides[0]};          /* rp_transpose view of B */
+        void* bt = packed_copy(B, ts, n, k, dtype);
+        void* g = malloc((size_t)m * k * es);
+        int rc = (bt && g) ? orc_rp_matmul(g, dC, bt, m, n, k, dtype) : -1;
+        if (rc == 0) { if (accumulate) grad_add(dA, g, (size_t)m * k, dtype); else memcpy(dA, g, (size_t)m * k * es); }
+        free(bt); free(g);
+        if (rc) return rc;
+    }
+    if (dB) {
+        int ts[2] = {a_strides[1], a_strides[0]};
+        void* at = packed_copy(A, ts, k, m, dtype);
+        void* g = malloc((size_t)k * n * es);
+        int rc = (at && g) ? orc_rp_matmul(g, at, dC, k, m, n, dtype) : -1;
+        if (rc == 0) { if (accumulate) grad_add(dB, g, (size_t)k * n, dtype); else memcpy(dB, g, (size_t)k * n * es); }
+        free(at); free(g);
+        if (rc) return rc;
+    }
+    return 0;
+}
+
+int orc_bmm(void* C, const void* A, const void* B, int batch, size_t a_bstride,
+            size_t b_bstride, int m, int k, int n, int dtype) {
+    size_t es = esize(dtype);
+    if (!es || batch <= 0) return -1;
+    for (int b = 0; b < batch; b++) {
+        int rc = orc_rp_matmul((char*)C + (size_t)b * m * n * es,
+                               (const char*)A + b * a_bstride * es,
+                               (const char*)B + b * b_bstride * es, m, k, n, dtype);
+        if (rc) return rc;
+    }
+    return 0;
+}
+
+/* Unrounded per-batch product in the accumulation type (float, or double for f64). */
+static int wide_product(void* out, const void* X, const void* Y, int m, int k, int n, int dtype) {
+    if (dtype == ORC_F64) return orc_matmul_f64((double*)out, (const double*)X, (const double*)Y, m, k, n);
+    if (dtype == ORC_F32) return orc_matmul_f32((float*)out, (const float*)X, (const float*)Y, m, k, n);
+    float* wx = (float*)malloc((size_t)m * k * 4);
+    float* wy = (float*)malloc((size_t)k * n * 4);
+    int rc = -1;
+    if (wx && wy) {
+        orc_widen(X, wx, (size_t)m * k, dtype); orc_widen(Y, wy, (size_t)k * n, dtype);
+        rc = orc_matmul_f32((float*)out, wx, wy, m, k, n);
+    }
+    free(wx); free(wy);
+    return rc;
+}
+
+static void* transpose_packed(const void* X, int rows, int cols, int dtype) {
+    int ts[2] = {1, cols};
+    return packed_copy(X, ts, cols, rows, dtype);
+}
+
+int orc_bmm_backward(void* dA, void* dB, const void* A, const void* B, const void* dC,
+                     int batch, size_t a_bstride, size_t b_bstride,
+                     int m, int k, int n, int dtype) {
+    size_t es = esize(dtype), ws = (dtype == ORC_F64) ? 8 : 4;
+    if (!es || batch <= 0) return -1;
+    int rc = 0;
+    for (int side = 0; side < 2 && !rc; side++) {
+        void* grad = side == 0 ? dA : dB;
+        if (!grad) continue;
+        size_t bstride = side == 0 ? a_bstride : b_bstride;
+        int gr = side == 0 ? m : k, gc = side == 0 ? k : n;
+        size_t gsz = (size_t)gr * gc;
+        int reduce = (bstride == 0 && batch > 1);
+        void* sum = reduce ? calloc(gsz, ws) : NULL;
+        void* tmp = reduce ? malloc(gsz * ws) : NULL;
+        if (reduce && (!sum || !tmp)) { free(sum); free(tmp); return -1; }
+        for (int b = 0; b < batch && !rc; b++) {
+            const char* Ab = (const char*)A + b * a_bstride * es;
+            const char* Bb = (const char*)B + b * b_bstride * es;
+            const char* Gb = (const char*)dC + (size_t)b * m * n * es;
+            void* t = side == 0 ? transpose_packed(Bb, k, n, dtype) : transpose_packed(Ab, m, k, dtype);
+            if (!t) { rc = -1; break; }
+            if (!reduce) {
+                char* out = (char*)grad + b * bstride * es;
+                rc = side == 0 ? orc_rp_matmul(out, Gb, t, m, n, k, dtype)
+                               : orc_rp_matmul(out, t, Gb, k, m, n, dtype);
+            } else {
+                rc = side == 0 ? wide_product(tmp, Gb, t, m, n, k, dtype)
+                               : wide_product(tmp, t, Gb, k, m, n, dtype);
+                if (!rc) {
+                    if (ws == 8) for (size_t i = 0; i < gsz; i++) ((double*)sum)[i] += ((double*)tmp)[i];
+                    else         for (size_t i = 0; i < gsz; i++) ((float*)sum)[i] = ((float*)sum)[i] + ((float*)tmp)[i];
+                }
+            }
+            free(t);
+        }
+        if (reduce && !rc) {
+            if (dtype == ORC_F64 || dtype == ORC_F32) memcpy(grad, sum, gsz * ws);
+            else orc_narrow((const float*)sum, grad, gsz, dtype);
+        }
+        free(sum); free(tmp);
+    }
+    return rc;
+}

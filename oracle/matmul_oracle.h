@@ -1,0 +1,73 @@
+/*
+ * TEST INFRASTRUCTURE ONLY.  CPU restatement of RecPulse's matmul forward and
+ * autograd backward, used as the parity checker by tests/, by the smoke test
+ * and as the timed CPU baseline of bench.py.  Nothing in the shipped library
+ * links, loads or calls this file.
+ *
+ * Parity status: PINNED.  tests/test_oracle.py checks this restatement against
+ * (1) the known-answer vectors of the reference's own tests, (2) fixtures in
+ * tests/golden/ that were produced by the unmodified reference
+ * (tests/golden/make_golden.py) and (3) the reference compiled from its own
+ * sources (oracle/_ref/recpulse_cuda.so) when that file is present.
+ *
+ * dtype codes follow core/tensor.h:7-13 of the reference.
+ */
+#ifndef RECPULSE_MATMUL_ORACLE_H
+#define RECPULSE_MATMUL_ORACLE_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum { ORC_F32 = 0, ORC_F64 = 1, ORC_F16 = 2, ORC_BF16 = 3 };
+
+/* core/half_precision.h:20-48, 50-83, 85-90, 92-97 */
+float    orc_fp16_to_fp32(uint16_t h);
+uint16_t orc_fp32_to_fp16(float f);
+float    orc_bf16_to_fp32(uint16_t h);
+uint16_t orc_fp32_to_bf16(float f);
+void     orc_widen(const void* src, float* dst, size_t n, int dtype);
+void     orc_narrow(const float* src, void* dst, size_t n, int dtype);
+
+/* functional/functional_host.c:780-806 */
+int orc_matmul_f32(float* C, const float* A, const float* B, int m, int k, int n);
+int orc_matmul_f64(double* C, const double* A, const double* B, int m, int k, int n);
+
+/* functional/functional.c:978-1002, host branch */
+int orc_rp_matmul(void* C, const void* A, const void* B, int m, int k, int n, int dtype);
+
+/* functional/functional.c:1130-1220 (host gather of a strided view, rank <= 8) */
+int orc_contiguous(void* dst, const void* src, int ndim, const int* shape,
+                   const int* strides, int dtype);
+
+/* ops/ops.c:6816-6884 forward on (possibly strided) 2-D operands */
+int orc_op_matmul(void* C, const void* A, const int* a_strides, const void* B,
+                  const int* b_strides, int m, int k, int n, int dtype);
+
+/* ops/ops.c:6759-6814; dA and/or dB may be NULL (that input does not require grad).
+ * accumulate!=0 restates the rp_add branch (:6781-6789): grad += new, rounded in
+ * the storage dtype as functional_host.c's add does (fp16/bf16: widen, add, narrow). */
+int orc_matmul_backward(void* dA, void* dB, const void* A, const int* a_strides,
+                        const void* B, const int* b_strides, const void* dC,
+                        int m, int k, int n, int dtype, int accumulate);
+
+/* Batched / broadcast-batched matmul: not in the reference.  Defined as a loop of
+ * reference 2-D matmuls over the broadcast batch index; a_bstride / b_bstride are
+ * batch strides in elements (0 = broadcast operand).  Operand matrices are packed
+ * row-major. */
+int orc_bmm(void* C, const void* A, const void* B, int batch, size_t a_bstride,
+            size_t b_bstride, int m, int k, int n, int dtype);
+/* Backward of the above.  A gradient of a broadcast operand is the sum over the
+ * batch of the per-batch products, accumulated without intermediate rounding
+ * (fp32 for f32/f16/bf16, fp64 for f64) and rounded to the storage dtype once. */
+int orc_bmm_backward(void* dA, void* dB, const void* A, const void* B, const void* dC,
+                     int batch, size_t a_bstride, size_t b_bstride,
+                     int m, int k, int n, int dtype);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,152 @@
+"""ctypes/numpy front end of ``liboracle.so`` (oracle/matmul_oracle.c).
+
+TEST INFRASTRUCTURE ONLY.  The shipped library never imports this module.
+Half-precision arrays are carried as ``uint16`` bit patterns so that the
+reference's round-half-up narrowing (core/half_precision.h:50-97) is the only
+conversion ever applied.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+F32, F64, F16, BF16 = 0, 1, 2, 3
+DTYPE_NAMES = {F32: "float32", F64: "float64", F16: "float16", BF16: "bfloat16"}
+_NP = {F32: np.float32, F64: np.float64, F16: np.uint16, BF16: np.uint16}
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB = None
+
+
+def build() -> str:
+    """Compile liboracle.so (and the reference, when its tree is present)."""
+    subprocess.run(["make", "-s", "-C", _HERE, "all"], check=True)
+    return os.path.join(_HERE, "liboracle.so")
+
+
+def lib() -> C.CDLL:
+    global _LIB
+    if _LIB is None:
+        path = os.path.join(_HERE, "liboracle.so")
+        if not os.path.exists(path):
+            subprocess.run(["make", "-s", "-C", _HERE, "oracle"], check=True)
+        _LIB = C.CDLL(path)
+        _LIB.orc_fp16_to_fp32.restype = C.c_float
+        _LIB.orc_fp16_to_fp32.argtypes = [C.c_uint16]
+        _LIB.orc_bf16_to_fp32.restype = C.c_float
+        _LIB.orc_bf16_to_fp32.argtypes = [C.c_uint16]
+        _LIB.orc_fp32_to_fp16.restype = C.c_uint16
+        _LIB.orc_fp32_to_fp16.argtypes = [C.c_float]
+        _LIB.orc_fp32_to_bf16.restype = C.c_uint16
+        _LIB.orc_fp32_to_bf16.argtypes = [C.c_float]
+    return _LIB
+
+
+def storage(dtype: int):
+    return _NP[dtype]
+
+
+def _p(a):
+    return None if a is None else a.ctypes.data_as(C.c_void_p)
+
+
+def _ints(v):
+    return None if v is None else (C.c_int * len(v))(*[int(x) for x in v])
+
+
+def narrow(x: np.ndarray, dtype: int) -> np.ndarray:
+    """fp32 -> storage bits of ``dtype`` with the reference's rounding."""
+    if dtype == F32:
+        return np.ascontiguousarray(x, np.float32)
+    if dtype == F64:
+        return np.ascontiguousarray(x, np.float64)
+    src = np.ascontiguousarray(x, np.float32)
+    out = np.empty(src.shape, np.uint16)
+    lib().orc_narrow(_p(src), _p(out), C.c_size_t(src.size), dtype)
+    return out
+
+
+def widen(x: np.ndarray, dtype: int) -> np.ndarray:
+    """storage bits -> float32 (f16/bf16), or the array itself as float."""
+    if dtype in (F32, F64):
+        return np.asarray(x)
+    src = np.ascontiguousarray(x, np.uint16)
+    out = np.empty(src.shape, np.float32)
+    lib().orc_widen(_p(src), _p(out), C.c_size_t(src.size), dtype)
+    return out
+
+
+def to_f64(x: np.ndarray, dtype: int) -> np.ndarray:
+    return widen(x, dtype).astype(np.float64)
+
+
+def rp_matmul(a: np.ndarray, b: np.ndarray, dtype: int) -> np.ndarray:
+    """Packed 2-D product, functional.c:978-1002 (host branch)."""
+    a = np.ascontiguousarray(a, _NP[dtype]); b = np.ascontiguousarray(b, _NP[dtype])
+    m, k = a.shape; k2, n = b.shape
+    assert k == k2
+    c = np.empty((m, n), _NP[dtype])
+    rc = lib().orc_rp_matmul(_p(c), _p(a), _p(b), m, k, n, dtype)
+    if rc != 0:
+        raise RuntimeError("orc_rp_matmul failed")
+    return c
+
+
+def _elem_strides(x: np.ndarray):
+    return [s // x.itemsize for s in x.strides]
+
+
+def op_matmul(a: np.ndarray, b: np.ndarray, dtype: int) -> np.ndarray:
+    """Forward on (possibly strided) 2-D numpy views, ops.c:6816-6847."""
+    m, k = a.shape; _, n = b.shape
+    c = np.empty((m, n), _NP[dtype])
+    rc = lib().orc_op_matmul(_p(c), _p(a), _ints(_elem_strides(a)), _p(b),
+                             _ints(_elem_strides(b)), m, k, n, dtype)
+    if rc != 0:
+        raise RuntimeError("orc_op_matmul failed")
+    return c
+
+
+def matmul_backward(a, b, dc, dtype, need_da=True, need_db=True, acc_da=None, acc_db=None):
+    """ops.c:6759-6814.  ``acc_*``: existing grads to accumulate into (copied)."""
+    m, k = a.shape; _, n = b.shape
+    dc = np.ascontiguousarray(dc, _NP[dtype])
+    accumulate = int(acc_da is not None or acc_db is not None)
+    da = (acc_da.copy() if acc_da is not None else np.empty((m, k), _NP[dtype])) if need_da else None
+    db = (acc_db.copy() if acc_db is not None else np.empty((k, n), _NP[dtype])) if need_db else None
+    rc = lib().orc_matmul_backward(_p(da), _p(db), _p(a), _ints(_elem_strides(a)), _p(b),
+                                   _ints(_elem_strides(b)), _p(dc), m, k, n, dtype, accumulate)
+    if rc != 0:
+        raise RuntimeError("orc_matmul_backward failed")
+    return da, db
+
+
+def _batch_stride(x):
+    return 0 if x.shape[0] == 1 else x.shape[1] * x.shape[2]
+
+
+def bmm(a: np.ndarray, b: np.ndarray, dtype: int) -> np.ndarray:
+    """[Ba,m,k] x [Bb,k,n] with Ba/Bb in {1, batch}: loop of reference 2-D products."""
+    a = np.ascontiguousarray(a, _NP[dtype]); b = np.ascontiguousarray(b, _NP[dtype])
+    batch = max(a.shape[0], b.shape[0]); m, k = a.shape[1:]; n = b.shape[2]
+    c = np.empty((batch, m, n), _NP[dtype])
+    rc = lib().orc_bmm(_p(c), _p(a), _p(b), batch, C.c_size_t(_batch_stride(a)),
+                       C.c_size_t(_batch_stride(b)), m, k, n, dtype)
+    if rc != 0:
+        raise RuntimeError("orc_bmm failed")
+    return c
+
+
+def bmm_backward(a, b, dc, dtype):
+    a = np.ascontiguousarray(a, _NP[dtype]); b = np.ascontiguousarray(b, _NP[dtype])
+    dc = np.ascontiguousarray(dc, _NP[dtype])
+    batch = dc.shape[0]; m, k = a.shape[1:]; n = b.shape[2]
+    da = np.empty(a.shape, _NP[dtype]); db = np.empty(b.shape, _NP[dtype])
+    rc = lib().orc_bmm_backward(_p(da), _p(db), _p(a), _p(b), _p(dc), batch,
+                                C.c_size_t(_batch_stride(a)), C.c_size_t(_batch_stride(b)),
+                                m, k, n, dtype)
+    if rc != 0:
+        raise RuntimeError("orc_bmm_backward failed")
+    return da, db

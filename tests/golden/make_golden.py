@@ -1,0 +1,87 @@
+"""Generate tests/golden/matmul_golden.npz from the UNMODIFIED reference.
+
+Run in a container where the reference tree is mounted and compiled by
+``make -C oracle ref`` (produces oracle/_ref/recpulse_cuda.so):
+
+    python tests/golden/make_golden.py
+
+Every case runs the reference's own CPU ``op_matmul`` + ``backward()`` through
+its CPython binding (python/tensor_python.c) and stores inputs and outputs as
+raw storage bits (float16/bfloat16 as uint16), so the fixtures can be replayed
+without the reference.  The upstream gradient dC is injected as
+``loss = sum(y * w)``, whose backward hands ``w`` to ``backward_matmul_fn``
+unchanged (1 * w is exact in every dtype).
+"""
+import os
+import sys
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(os.path.dirname(HERE))
+sys.path.insert(0, os.path.join(ROOT, "oracle", "_ref"))
+import recpulse_cuda as rp  # noqa: E402
+
+DT = {"float32": np.float32, "float64": np.float64, "float16": np.float16, "bfloat16": np.float32}
+
+
+def to_rp(x64, dtype):
+    """float64 numpy -> CPU reference tensor of `dtype`, narrowed by the reference itself."""
+    if dtype == "bfloat16":
+        return rp.from_numpy(np.ascontiguousarray(x64, np.float32)).to(dtype="bfloat16")
+    return rp.from_numpy(np.ascontiguousarray(x64.astype(DT[dtype])))
+
+
+def bits(t):
+    """reference tensor -> numpy storage bits."""
+    dt = t.dtype
+    if dt == "bfloat16":
+        f = t.to(dtype="float32").to_numpy()
+        return (np.ascontiguousarray(f).view(np.uint32) >> 16).astype(np.uint16)
+    a = np.ascontiguousarray(t.to_numpy())
+    return a.view(np.uint16) if dt == "float16" else a
+
+
+def run_case(name, dtype, m, k, n, rng, ta=False, tb=False, twice=False, scale=1.0):
+    a64 = rng.uniform(-1, 1, (k, m) if ta else (m, k)) * scale
+    b64 = rng.uniform(-1, 1, (n, k) if tb else (k, n)) * scale
+    w64 = rng.uniform(-1, 1, (m, n))
+    a = to_rp(a64, dtype); b = to_rp(b64, dtype); w = to_rp(w64, dtype)
+    a.requires_grad_(True); b.requires_grad_(True)
+    av = a.transpose(0, 1) if ta else a
+    bv = b.transpose(0, 1) if tb else b
+    y = av.op_matmul(bv)
+    loss = y.op_mul(w).op_sum_all()
+    keep = [y, loss]
+    if twice:            # second use of the same leaves: grads accumulate through rp_add
+        y2 = av.op_matmul(bv)
+        l2 = y2.op_mul(w).op_sum_all()
+        loss = loss.op_add(l2)
+        keep += [y2, l2, loss]
+    loss.backward()
+    out = {
+        "a": bits(a), "b": bits(b), "w": bits(w), "c": bits(y),
+        "da": bits(a.grad), "db": bits(b.grad),
+        "meta": np.array([m, k, n, int(ta), int(tb), int(twice)], np.int64),
+    }
+    return {f"{name}/{dtype}/{key}": val for key, val in out.items()}
+
+
+def main():
+    rng = np.random.default_rng(20240607)
+    store = {}
+    shapes = [(3, 4, 5), (16, 32, 8), (1, 7, 1), (64, 64, 64), (33, 65, 17), (2, 300, 3)]
+    for dtype in DT:
+        for (m, k, n) in shapes:
+            store.update(run_case(f"nn_{m}x{k}x{n}", dtype, m, k, n, rng))
+        store.update(run_case("ta_12x20x9", dtype, 12, 20, 9, rng, ta=True))
+        store.update(run_case("tb_12x20x9", dtype, 12, 20, 9, rng, tb=True))
+        store.update(run_case("tatb_24x40x16", dtype, 24, 40, 16, rng, ta=True, tb=True))
+        store.update(run_case("acc_10x14x6", dtype, 10, 14, 6, rng, twice=True))
+        store.update(run_case("big_40x130x50", dtype, 40, 130, 50, rng, scale=4.0))
+    np.savez_compressed(os.path.join(HERE, "matmul_golden.npz"), **store)
+    print("cases:", len(store) // 7)
+
+
+if __name__ == "__main__":
+    main()
