@@ -1,0 +1,358 @@
+#!/usr/bin/env python
+"""Benchmark of the matmul forward + backward path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl ours|reference]
+
+A step is one forward + backward of one matmul: C = A.B, dB = A^T.dC, dA = dC.B^T (both inputs
+require grad).  The default workload is the row-sharded large GEMM, bf16 A[65536,8192] x B[8192,8192]
+with fp32 accumulation: A's rows are split evenly over the N ranks (strong scaling, total work
+fixed), B is replicated, the dB partials are all-reduced over NCCL overlapped with the dA GEMM.
+Other workloads (--workload square4096 | bmm_fp16 | mlp_fp32 | lstm_fp32 | fp64_2048) run on one GPU.
+
+Inputs are seeded synthetic data with the shapes and distributions of the named workload and
+are larger than L2 (126 MB), so no L2 flush is needed between iterations.
+
+One JSON line is printed by rank 0.  `value` times the kernels with inputs resident in HBM
+(CUDA events on the launching stream, max over ranks); `e2e` times the same step through the C ABI
+starting from pinned HOST buffers (H2D of A, B, dC and D2H of C, dA, dB inside the timed region);
+`roofline` is the tcgen05 GEMM kernel against the measured cuBLAS bf16 peak; `cpu_baseline` is the
+reference's own CPU matmul (compiled from its sources, oracle/_ref) on a bounded slab.
+`--impl reference` times only that CPU implementation.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "matmul fwd+bwd TFLOP/s"
+UNIT = "TFLOP/s"
+
+WORKLOADS = {
+    # name: (dtype, batch, m, k, n, broadcast_b, shards)
+    "rowsharded_65536x8192x8192": ("bfloat16", 1, 65536, 8192, 8192, False, True),
+    "square4096": ("bfloat16", 1, 4096, 4096, 4096, False, False),
+    "bmm_fp16": ("float16", 64, 512, 64, 512, True, True),
+    "mlp_fp32": ("float32", 1, 128, 784, 256, False, False),
+    "lstm_fp32": ("float32", 1, 64, 512, 2048, False, False),
+    "fp64_2048": ("float64", 1, 2048, 2048, 2048, False, False),
+}
+DEFAULT_WORKLOAD = "rowsharded_65536x8192x8192"
+
+
+def parse():
+    p = argparse.ArgumentParser()
+    p.add_argument("--gpus", type=int, default=1)
+    p.add_argument("--steps", type=int, default=10)
+    p.add_argument("--warmup", type=int, default=3)
+    p.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    p.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=list(WORKLOADS))
+    p.add_argument("--e2e-steps", type=int, default=3)
+    p.add_argument("--no-cpu-baseline", action="store_true")
+    p.add_argument("--no-e2e", action="store_true")
+    return p.parse_args()
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        d = json.load(open(path))
+        return {"tflops": d["bf16_tflops_sustained"], "tflops_burst": d["bf16_tflops"], "hbm": d["hbm_gbs"], "src": "measured"}
+    return {"tflops": 1400.0, "tflops_burst": 1590.0, "hbm": 6650.0, "src": "fallback"}
+
+
+# --------------------------------------------------------------------------- CPU reference arm
+
+def cpu_reference_matmul():
+    """(callable(C, A, B, m, k, n, dtype_code) -> rc, kind): the reference's own rp_matmul on host
+    memory when it was compiled from its sources, else the C oracle port."""
+    so = os.path.join(ROOT, "oracle", "_ref", "recpulse_cuda.so")
+    if os.path.exists(so):
+        ref = C.CDLL(so)
+        ref.rp_matmul.restype = C.c_int
+        ref.rp_matmul.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]
+        return (lambda c, a, b, m, k, n, dt: ref.rp_matmul(c, a, b, m, k, n, dt, -1)), "reference"
+    from oracle import oracle as O
+    lib = O.lib()
+    return (lambda c, a, b, m, k, n, dt: lib.orc_rp_matmul(c, a, b, m, k, n, dt)), "port"
+
+
+def cpu_sample(workload, budget_s, steps=1, warmup=0):
+    """Times fwd + dA + dB of a row slab of the workload on the reference's serial CPU loop.
+    Returns (tflops, description, kind, per-step seconds)."""
+    import numpy as np
+    from oracle import oracle as O
+    dtype, batch, m, k, n, _, _ = WORKLOADS[workload]
+    code = {"float32": O.F32, "float64": O.F64, "float16": O.F16, "bfloat16": O.BF16}[dtype]
+    fn, kind = cpu_reference_matmul()
+    rng = np.random.default_rng(0)
+    b = O.narrow(rng.standard_normal((k, n)), code)
+    bt = np.ascontiguousarray(b.T)
+    p = lambda x: x.ctypes.data_as(C.c_void_p)
+
+    def run(rows):
+        a = O.narrow(rng.standard_normal((rows, k)) / np.sqrt(k), code)
+        dc = O.narrow(rng.standard_normal((rows, n)), code)
+        at = np.ascontiguousarray(a.T)
+        c = np.empty((rows, n), a.dtype); da = np.empty((rows, k), a.dtype); db = np.empty((k, n), a.dtype)
+        t0 = time.perf_counter()
+        assert fn(p(c), p(a), p(b), rows, k, n, code) == 0          # C  = A . B
+        assert fn(p(da), p(dc), p(bt), rows, n, k, code) == 0       # dA = dC . B^T (B^T packed, as ops.c:6771 does)
+        assert fn(p(db), p(at), p(dc), k, rows, n, code) == 0       # dB = A^T . dC
+        return time.perf_counter() - t0
+
+    total_rows = batch * m
+    t1 = run(1)                                                     # probe: one row
+    per_step_budget = budget_s / max(1, steps + warmup)
+    rows = int(max(1, min(total_rows, per_step_budget / max(t1, 1e-6))))
+    for _ in range(warmup):
+        run(rows)
+    times = [run(rows) for _ in range(steps)]
+    dt = sum(times) / len(times)
+    flops = 3 * 2.0 * rows * k * n
+    desc = f"fwd+dA+dB of a {rows}-row slab ({rows}x{k}x{n} {dtype}) of {workload}, serial reference loop"
+    return flops / dt / 1e12, desc, kind, dt
+
+
+def run_reference_arm(args, rank):
+    if rank != 0:
+        return
+    budget = 150.0
+    tflops, desc, kind, dt = cpu_sample(args.workload, budget, steps=args.steps, warmup=args.warmup)
+    dtype = WORKLOADS[args.workload][0]
+    line = {
+        "impl": "reference", "metric": METRIC, "value": tflops, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": {"bfloat16": "bf16", "float16": "f16", "float32": "f32", "float64": "f64"}[dtype],
+        "data": "synthetic", "config": {"workload": args.workload, "sample": desc},
+        "cpu_baseline": {"value": tflops, "unit": UNIT, "cores": 1, "kind": kind, "sample": desc},
+        "e2e": {"value": tflops, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------- clocks
+
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        for line in out.strip().splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 8:
+                continue
+            try:
+                sm.append(float(f[0])); mx.append(float(f[1]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[4:8]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------- GPU arm
+
+def main():
+    args = parse()
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.impl == "reference":
+        run_reference_arm(args, rank)
+        return
+
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    import recpulse_b200
+    from recpulse_b200 import _lib
+    from recpulse_b200.sharded import RowShardedMatmul, cuda_gemm, row_partition
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device (the matmul path has no CPU implementation)")
+    lib = recpulse_b200.load()
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    if args.gpus != world and rank == 0 and world > 1:
+        print(f"bench.py: --gpus {args.gpus} but WORLD_SIZE {world}; using WORLD_SIZE", file=sys.stderr)
+    n_gpus = world
+
+    dtype_name, batch, m, k, n, bcast_b, shards = WORKLOADS[args.workload]
+    tdtype = {"bfloat16": torch.bfloat16, "float16": torch.float16, "float32": torch.float32, "float64": torch.float64}[dtype_name]
+    es = torch.empty((), dtype=tdtype).element_size()
+    rows_total = batch * m            # a broadcast-batched product folds its batch into the rows of A
+    if world > 1 and not shards:
+        raise SystemExit(f"workload {args.workload} is single-GPU (replicas only)")
+    r0, r1 = row_partition(rows_total, world, rank)
+    rows = r1 - r0
+
+    gen = torch.Generator(device=dev); gen.manual_seed(1234 + rank)
+    a_scale = 1.0 / np.sqrt(k) if dtype_name == "bfloat16" else 1.0
+    A = (torch.randn((rows, k), generator=gen, device=dev, dtype=torch.float32) * a_scale).to(tdtype)
+    gen_b = torch.Generator(device=dev); gen_b.manual_seed(99)
+    Bm = (torch.randn((k, n), generator=gen_b, device=dev, dtype=torch.float32) * (0.125 if bcast_b else 1.0)).to(tdtype)
+    dC = torch.randn((rows, n), generator=gen, device=dev, dtype=torch.float32).to(tdtype)
+    Cc = torch.empty((rows, n), device=dev, dtype=tdtype)
+    dA = torch.empty((rows, k), device=dev, dtype=tdtype)
+    dB = torch.empty((k, n), device=dev, dtype=tdtype)
+
+    op = RowShardedMatmul(Bm, gemm=cuda_gemm)
+
+    def step():
+        op.forward(A, out=Cc)
+        op.backward(A, dC, da_out=dA, db_out=dB)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    for _ in range(max(3, args.warmup)):
+        step()
+    barrier()
+    if lib.rpb_device_status(local_rank) != 0:
+        raise SystemExit("bench.py: a bounded wait inside the tcgen05 kernel ran out during warm-up")
+
+    # ---- timed region: K steps, kernels only, inputs resident in HBM
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    launches0 = lib.rpb_launch_count()
+    stream = torch.cuda.current_stream(dev)
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    # per-launch events for the roofline of the dominant kernel (forward GEMM of every step)
+    fwd_ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    barrier()
+    ev0.record(stream)
+    for i in range(args.steps):
+        fwd_ev[i][0].record(stream)
+        op.forward(A, out=Cc)
+        fwd_ev[i][1].record(stream)
+        op.backward(A, dC, da_out=dA, db_out=dB)
+    ev1.record(stream)
+    barrier()
+    elapsed_ms = ev0.elapsed_time(ev1)
+    launches = lib.rpb_launch_count() - launches0
+    clocks = sampler.stop() if rank == 0 else None
+    fwd_ms = sum(a.elapsed_time(b) for a, b in fwd_ev) / args.steps
+    if world > 1:
+        t = torch.tensor([elapsed_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        elapsed_ms = float(t.item())
+    if lib.rpb_device_status(local_rank) != 0:
+        raise SystemExit("bench.py: a bounded wait inside the tcgen05 kernel ran out")
+
+    flops_step = 3 * 2.0 * rows_total * k * n
+    ms_per_step = elapsed_ms / args.steps
+    value = flops_step / (ms_per_step * 1e-3) / 1e12
+
+    # ---- end to end from pinned host buffers through the C ABI
+    e2e = None
+    if not args.no_e2e:
+        hA = torch.empty((rows, k), dtype=tdtype).pin_memory(); hA.copy_(A)
+        hB = torch.empty((k, n), dtype=tdtype).pin_memory(); hB.copy_(Bm)
+        hdC = torch.empty((rows, n), dtype=tdtype).pin_memory(); hdC.copy_(dC)
+        hC = torch.empty((rows, n), dtype=tdtype).pin_memory()
+        hdA = torch.empty((rows, k), dtype=tdtype).pin_memory()
+        hdB = torch.empty((k, n), dtype=tdtype).pin_memory()
+
+        def e2e_step():
+            A.copy_(hA, non_blocking=True); Bm.copy_(hB, non_blocking=True); dC.copy_(hdC, non_blocking=True)
+            step()
+            hC.copy_(Cc, non_blocking=True); hdA.copy_(dA, non_blocking=True); hdB.copy_(dB, non_blocking=True)
+
+        e2e_step()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(args.e2e_steps):
+            e2e_step()
+        e1.record(stream)
+        barrier()
+        e2e_ms = e0.elapsed_time(e1) / args.e2e_steps
+        if world > 1:
+            t = torch.tensor([e2e_ms], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            e2e_ms = float(t.item())
+        h2d = (rows * k + k * n + rows * n) * es
+        d2h = (rows * n + rows * k + k * n) * es
+        e2e = {"value": flops_step / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "h2d_bytes_per_step": int(h2d),
+               "d2h_bytes_per_step": int(d2h), "ms_per_step": e2e_ms, "steps": args.e2e_steps}
+
+    if rank == 0:
+        pk = peaks()
+        half = dtype_name in ("bfloat16", "float16")
+        flops_fwd = 2.0 * rows * k * n                               # one launch of the dominant kernel on this rank
+        if half and args.workload != "bmm_fp16":
+            achieved = flops_fwd / (fwd_ms * 1e-3) / 1e12
+            roof = {"bound": "tensor", "kernel": "rpb_umma::gemm_kernel (forward GEMM launch)", "achieved": achieved,
+                    "peak": pk["tflops"], "unit": "TFLOP/s", "frac": achieved / pk["tflops"],
+                    "peak_source": pk["src"] + " cuBLAS bf16, sustained", "traffic": None,
+                    "avg_launch_ms": fwd_ms}
+        else:
+            bytes_fwd = (rows * k + k * n + rows * n) * es
+            achieved = bytes_fwd / (fwd_ms * 1e-3) / 1e9
+            roof = {"bound": "hbm", "kernel": "forward GEMM launch", "achieved": achieved, "peak": pk["hbm"], "unit": "GB/s",
+                    "frac": achieved / pk["hbm"], "peak_source": pk["src"] + " copy bandwidth", "traffic": None,
+                    "avg_launch_ms": fwd_ms}
+        cpu = None
+        if n_gpus == 1 and not args.no_cpu_baseline:
+            tf, desc, kind, _ = cpu_sample(args.workload, 20.0)
+            cpu = {"value": tf, "unit": UNIT, "cores": 1, "kind": kind, "sample": desc}
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": n_gpus, "steps": args.steps, "warmup": max(3, args.warmup),
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": {"bfloat16": "bf16", "float16": "f16", "float32": "f32", "float64": "f64"}[dtype_name],
+            "data": "synthetic",
+            "config": {"workload": args.workload, "m": rows_total, "k": k, "n": n, "rows_per_gpu": rows,
+                       "parallelism": f"rows of A over {n_gpus} GPU(s), B replicated, dB all-reduced" if n_gpus > 1 else "single GPU",
+                       "l2": "inputs larger than L2, no flush", "accumulate": "fp32"},
+            "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches), "roofline": roof, "cpu_baseline": cpu,
+            "pct_of_nominal_dense_peak": value / (2250.0 * n_gpus) if half else None,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

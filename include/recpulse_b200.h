@@ -1,0 +1,186 @@
+/*
+ * recpulse_b200 -- Blackwell (sm_100a) dense-matmul path for RecPulse.
+ *
+ * C ABI of librecpulse_b200.so.  The first four entry points carry the exact
+ * names and signatures of the RecPulse symbols they replace, so the library can
+ * be linked in place of those functions or loaded in front of an unmodified
+ * recpulse_cuda.so (symbol interposition).  Everything else is additive.
+ *
+ * Conventions kept from RecPulse: row-major, strides in ELEMENTS, `data`
+ * already offset for views, int 0 / -1 and NULL for errors with a diagnostic
+ * on stderr, results complete (stream synchronised) when an entry point that
+ * has no stream argument returns.
+ *
+ * Device tensors only.  There is no CPU implementation in this library: a call
+ * with device_id == -1 is forwarded to a loaded recpulse_cuda.so when there is
+ * one (its own host code, untouched) and fails with -1 / NULL otherwise.
+ */
+#ifndef RECPULSE_B200_H
+#define RECPULSE_B200_H
+
+#include <stdbool.h>
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- types shared with RecPulse (layout-identical) ------------------------
+ * A translation unit that also needs RecPulse's own headers includes them FIRST
+ * (their include guards are TENSOR_H and OPS_H); their definitions are then used
+ * instead of the copies below. */
+#ifndef TENSOR_H
+typedef enum {                      /* core/tensor.h:7-13 */
+    DTYPE_FLOAT32 = 0,
+    DTYPE_FLOAT64 = 1,
+    DTYPE_FLOAT16 = 2,
+    DTYPE_BFLOAT16 = 3,
+    DTYPE_PRESERVE = -1,
+} DType;
+
+typedef struct Tensor Tensor;
+typedef struct GradFn GradFn;
+
+typedef struct {                    /* core/tensor.h:18-24 */
+    bool is_leaf;
+    bool requires_grad;
+    bool is_frozen;
+    GradFn* grad_fn;
+    Tensor* grad;
+} Meta;
+
+struct Tensor {                     /* core/tensor.h:27-42 */
+    DType dtype;
+    void* data;
+    int ndim;
+    size_t size;
+    int* shape;
+    int* strides;                   /* in elements */
+    int device_id;                  /* -1 = host */
+    bool owns_data;
+    int refcount;
+    Tensor* base_tensor;
+    size_t data_offset;
+    Meta* metadata;
+};
+#endif /* TENSOR_H */
+
+#ifndef OPS_H
+typedef void (*BackwardFunction)(GradFn* self, Tensor* grad_output);   /* ops/ops.h:12 */
+struct GradFn {                     /* ops/ops.h:14-20 */
+    BackwardFunction backward;
+    Tensor** inputs;
+    int num_inputs;
+    void* saved_data;
+    Tensor* owner;
+};
+#endif /* OPS_H */
+
+/* ---- drop-in entry points --------------------------------------------------*/
+
+/* Replaces matmul_kernel_device (functional/functional.h:426,
+ * functional/functional_device.cu:991-1071): C[m,n] = A[m,k] . B[k,n], packed
+ * row-major device pointers on the CURRENT device, legacy default stream,
+ * synchronised before return.  0 on success, -1 on error. */
+int matmul_kernel_device(void* C, const void* A, const void* B, int m, int k, int n, DType dtype);
+
+/* Replaces rp_matmul (functional/functional.h:220, functional/functional.c:978-1006):
+ * argument checks, cudaSetDevice(device_id) (not restored, as in RecPulse), then
+ * matmul_kernel_device. */
+int rp_matmul(void* C, const void* A, const void* B, int m, int k, int n, DType dtype, int device_id);
+
+/* Replaces op_matmul (ops/ops.h:85, ops/ops.c:6816-6884).  Same checks (NULL,
+ * inner dimension, dtype, device) and same autograd bookkeeping (Meta/GradFn
+ * allocated with calloc/malloc, inputs retained, owner set).  Differences, all
+ * additive: strided / transposed 2-D views are read in place (no contiguous
+ * copy), and operands with ndim > 2 are accepted as batched matrices whose
+ * leading dimensions broadcast NumPy-style.  The result is a new contiguous
+ * tensor, refcount 1, owns_data, data from cudaMalloc on the operands' device. */
+Tensor* op_matmul(Tensor* a, Tensor* b);
+
+/* Replaces backward_matmul_fn (ops/ops.c:6759-6814): dA = dC . B^T and
+ * dB = A^T . dC for the inputs that require grad, reading A and B through their
+ * strides.  A missing grad is assigned; an existing one is accumulated inside
+ * the GEMM epilogue (no temporary, no separate add).  Gradients of broadcast
+ * batch dimensions are summed over those dimensions.  On failure grads are left
+ * untouched (the function is void, as in RecPulse). */
+void backward_matmul_fn(GradFn* self, Tensor* grad_output);
+
+/* ---- additive: strided / batched GEMM on raw pointers ----------------------*/
+
+typedef struct {
+    int m, n, k;                    /* C[m,n] (+)= sum over k of A[m,k] * B[k,n]              */
+    int batch;                      /* independent problems (>= 1)                           */
+    int reduce;                     /* problems SUMMED into one C (>= 1); used for grads of  */
+                                    /* broadcast operands: C = sum_r A_r . B_r               */
+    long long a_row, a_col;         /* element strides of A[i,l]                             */
+    long long a_batch, a_reduce;    /* element strides between batches / summed problems     */
+    long long b_row, b_col;         /* element strides of B[l,j]                             */
+    long long b_batch, b_reduce;
+    long long c_row;                /* row stride of C; its column stride is 1               */
+    long long c_batch;
+    int accumulate;                 /* 0: C = AB ; 1: C = C + AB (one rounding of the sum)   */
+} RpbGemm;
+
+/* Fills `g` for a packed row-major m x k times k x n product (batch = reduce = 1). */
+void rpb_gemm_packed(RpbGemm* g, int m, int k, int n);
+
+/* No RecPulse counterpart (RecPulse can only multiply packed matrices,
+ * functional/functional.h:220).  Runs on `stream` (a cudaStream_t; NULL = legacy
+ * default stream) of device `device_id` WITHOUT synchronising.  Any stride may be
+ * zero (broadcast) except C's.  0 on success, -1 on error. */
+int rp_matmul_ex(void* C, const void* A, const void* B, const RpbGemm* g, DType dtype,
+                 int device_id, void* stream);
+
+/* Same through HOST buffers: allocates device memory, copies A and B up,
+ * multiplies, copies C down (packed operands).  Exists so a host-only caller and the
+ * end-to-end benchmark can exercise the full path; -1 on error. */
+int rp_matmul_host(void* C, const void* A, const void* B, int m, int k, int n, DType dtype,
+                   int device_id);
+
+/* ---- additive: diagnostics and tuning --------------------------------------*/
+
+enum {                              /* values of rpb_last_kernel()                           */
+    RPB_KERNEL_NONE = 0,
+    RPB_KERNEL_SIMT = 1,            /* FFMA / DFMA tiled kernel                              */
+    RPB_KERNEL_UMMA = 2,            /* tcgen05 + TMEM + TMA kernel (f16 / bf16)              */
+    RPB_KERNEL_UMMA_SPLITK = 3      /* the same with K split over CTAs + reduction pass      */
+};
+/* Which kernel family the last GEMM issued by the calling thread used. */
+int rpb_last_kernel(void);
+/* Number of kernel launches issued by this library since load (all threads). */
+unsigned long long rpb_launch_count(void);
+/* 0 = choose automatically, RPB_KERNEL_SIMT / RPB_KERNEL_UMMA = force that family where it
+ * applies.  Also settable with the environment variable RPB_FORCE_KERNEL=simt|umma. */
+void rpb_force_kernel(int family);
+/* Device-side status word of the last tcgen05 launch on `device_id`: 0 = ok, otherwise a
+ * bounded wait inside the kernel ran out (the kernel returned early; results invalid).
+ * Synchronises the device. */
+int rpb_device_status(int device_id);
+/* Library version string. */
+const char* rpb_version(void);
+
+/* ---- additive: minimal tensor helpers for C callers without RecPulse --------
+ * They follow RecPulse's allocation conventions (struct, shape, strides and Meta from
+ * malloc/calloc, device data from cudaMalloc), so tensors made here can be released by
+ * RecPulse's free_tensor and vice versa. */
+Tensor* rpb_tensor_from_host(const void* host_data, DType dtype, int ndim, const int* shape,
+                             int device_id, bool requires_grad);
+Tensor* rpb_tensor_empty(DType dtype, int ndim, const int* shape, int device_id);
+/* A view sharing `base`'s data: explicit shape/strides (elements) and element offset.  When
+ * `base` requires grad the view gets its own Meta and collects its own gradient. */
+Tensor* rpb_tensor_view(Tensor* base, int ndim, const int* shape, const int* strides,
+                        size_t offset_elems);
+/* Copies a (possibly strided) tensor to a packed host buffer of t->size elements. */
+int rpb_tensor_to_host(const Tensor* t, void* host_out);
+/* Drops one reference; frees at zero (data, grad, grad_fn with its retained inputs, base). */
+void rpb_tensor_release(Tensor* t);
+/* Runs the backward function recorded on `out` with upstream gradient `grad_output`
+ * and frees the node (single-use graph, as tensor_backward does, core/tensor.c:219-347).
+ * Only a single matmul node is walked; RecPulse's tensor_backward remains the real driver. */
+int rpb_backward_node(Tensor* out, Tensor* grad_output);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RECPULSE_B200_H */

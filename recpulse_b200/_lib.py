@@ -1,0 +1,99 @@
+"""ctypes binding of librecpulse_b200.so (the C ABI declared in include/recpulse_b200.h).
+
+There is no Python or CPU implementation behind this module: when the shared
+library is missing and cannot be built, importing fails with an error.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+from . import build as _build
+
+F32, F64, F16, BF16 = 0, 1, 2, 3
+DTYPE_CODE = {"float32": F32, "float64": F64, "float16": F16, "bfloat16": BF16}
+DTYPE_NAME = {v: k for k, v in DTYPE_CODE.items()}
+DTYPE_SIZE = {F32: 4, F64: 8, F16: 2, BF16: 2}
+
+KERNEL_NONE, KERNEL_SIMT, KERNEL_UMMA, KERNEL_UMMA_SPLITK = 0, 1, 2, 3
+
+
+class Meta(C.Structure):
+    pass
+
+
+class GradFn(C.Structure):
+    pass
+
+
+class CTensor(C.Structure):
+    pass
+
+
+Meta._fields_ = [("is_leaf", C.c_bool), ("requires_grad", C.c_bool), ("is_frozen", C.c_bool),
+                 ("grad_fn", C.POINTER(GradFn)), ("grad", C.POINTER(CTensor))]
+CTensor._fields_ = [("dtype", C.c_int), ("data", C.c_void_p), ("ndim", C.c_int), ("size", C.c_size_t),
+                    ("shape", C.POINTER(C.c_int)), ("strides", C.POINTER(C.c_int)), ("device_id", C.c_int),
+                    ("owns_data", C.c_bool), ("refcount", C.c_int), ("base_tensor", C.POINTER(CTensor)),
+                    ("data_offset", C.c_size_t), ("metadata", C.POINTER(Meta))]
+GradFn._fields_ = [("backward", C.c_void_p), ("inputs", C.POINTER(C.POINTER(CTensor))), ("num_inputs", C.c_int),
+                   ("saved_data", C.c_void_p), ("owner", C.POINTER(CTensor))]
+
+
+class RpbGemm(C.Structure):
+    _fields_ = [("m", C.c_int), ("n", C.c_int), ("k", C.c_int), ("batch", C.c_int), ("reduce", C.c_int),
+                ("a_row", C.c_longlong), ("a_col", C.c_longlong), ("a_batch", C.c_longlong), ("a_reduce", C.c_longlong),
+                ("b_row", C.c_longlong), ("b_col", C.c_longlong), ("b_batch", C.c_longlong), ("b_reduce", C.c_longlong),
+                ("c_row", C.c_longlong), ("c_batch", C.c_longlong), ("accumulate", C.c_int)]
+
+
+# every symbol include/recpulse_b200.h declares: name -> (restype, argtypes)
+TP = C.POINTER(CTensor)
+SYMBOLS = {
+    "matmul_kernel_device": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int]),
+    "rp_matmul": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
+    "op_matmul": (TP, [TP, TP]),
+    "backward_matmul_fn": (None, [C.POINTER(GradFn), TP]),
+    "rpb_gemm_packed": (None, [C.POINTER(RpbGemm), C.c_int, C.c_int, C.c_int]),
+    "rp_matmul_ex": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(RpbGemm), C.c_int, C.c_int, C.c_void_p]),
+    "rp_matmul_host": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
+    "rpb_last_kernel": (C.c_int, []),
+    "rpb_launch_count": (C.c_ulonglong, []),
+    "rpb_force_kernel": (None, [C.c_int]),
+    "rpb_device_status": (C.c_int, [C.c_int]),
+    "rpb_version": (C.c_char_p, []),
+    "rpb_tensor_from_host": (TP, [C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_int), C.c_int, C.c_bool]),
+    "rpb_tensor_empty": (TP, [C.c_int, C.c_int, C.POINTER(C.c_int), C.c_int]),
+    "rpb_tensor_view": (TP, [TP, C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_int), C.c_size_t]),
+    "rpb_tensor_to_host": (C.c_int, [TP, C.c_void_p]),
+    "rpb_tensor_release": (None, [TP]),
+    "rpb_backward_node": (C.c_int, [TP, TP]),
+}
+
+_LIB = None
+
+
+def lib_path() -> str:
+    return _build.LIB
+
+
+def load(global_scope: bool = False) -> C.CDLL:
+    """Load (building first if stale) the shared library.
+
+    ``global_scope=True`` puts its symbols in the process's global scope, which is
+    how the library takes over ``rp_matmul`` / ``op_matmul`` inside an unmodified
+    ``recpulse_cuda.so`` imported afterwards.
+    """
+    global _LIB
+    if _LIB is None or global_scope:
+        path = _build.build()
+        if not os.path.exists(path):
+            raise ImportError(f"{path} is missing: run `python -m recpulse_b200.build`")
+        mode = C.RTLD_GLOBAL if global_scope else C.DEFAULT_MODE
+        lib = C.CDLL(path, mode=mode)
+        for name, (res, args) in SYMBOLS.items():
+            fn = getattr(lib, name)      # AttributeError if the export is missing
+            fn.restype = res
+            fn.argtypes = args
+        _LIB = lib
+    return _LIB

@@ -1,0 +1,360 @@
+/*
+ * tcgen05 GEMM for float16 / bfloat16 (fp32 accumulation in tensor memory).
+ *
+ * One persistent CTA per SM, 6 warps:
+ *   warp 0      TMA producer: 128B-swizzled tiles of A and B into a shared-memory ring
+ *   warp 1      owns tensor memory; one lane issues tcgen05.mma (M=128, N=BN, K=16)
+ *   warps 2..5  epilogue: tcgen05.ld of the fp32 accumulator, optional "+= C", rounding,
+ *               global stores (or fp32 partial tiles when K is split across CTAs)
+ * Two accumulators (2 x BN tensor-memory columns) let the epilogue of tile i overlap
+ * the main loop of tile i+1.
+ *
+ * Operands are read where they lie: each one may be K-major (reduction index
+ * contiguous) or MN-major (output index contiguous); the TMA descriptor is built from
+ * the tensor's own strides and the MMA descriptors carry the matching major bit, so
+ * the transposed operands of the backward GEMMs (dC.B^T, A^T.dC) need no copy.
+ *
+ * Every wait on an mbarrier is bounded.  When a bound runs out the kernel records a
+ * code in *status, all roles leave their loops, tensor memory is released and the
+ * kernel returns; the host reports the failure (rpb_device_status).
+ */
+#ifndef RPB_GEMM_UMMA_CUH
+#define RPB_GEMM_UMMA_CUH
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace rpb_umma {
+
+constexpr int BLOCK_M = 128;
+constexpr int BLOCK_K = 64;             /* 64 x 2 bytes = one 128-byte swizzle row */
+constexpr int UMMA_K = 16;
+constexpr int NUM_THREADS = 192;
+constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;   /* 2 s per wait */
+constexpr int SMEM_LIMIT = 227 * 1024;
+
+template <int BN> struct Config {
+    static constexpr int A_BYTES = BLOCK_M * BLOCK_K * 2;
+    static constexpr int B_BYTES = BN * BLOCK_K * 2;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int STAGES_RAW = (SMEM_LIMIT - 2048) / STAGE_BYTES;
+    static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
+    static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;   /* power of two: BN in {32,64,128,256} */
+};
+
+struct Args {
+    int m, n, k;
+    int batch, reduce;
+    int k_blocks;          /* ceil(k / BLOCK_K) */
+    int k_iters;           /* reduce * k_blocks */
+    int splits;            /* CTAs sharing one output tile along K (1 = none) */
+    int iters_per_split;
+    int tiles_m, tiles_n;
+    long long total_work;  /* tiles_m * tiles_n * batch * splits */
+    int a_batch_mul, a_reduce_mul, b_batch_mul, b_reduce_mul;   /* 0 when that operand is broadcast */
+    void* c;               /* output (T), or nullptr when splits > 1 */
+    long long c_row, c_batch;
+    int accumulate;
+    float* partial;        /* [splits][batch][m][n] fp32 when splits > 1 */
+    uint32_t idesc;        /* tcgen05 instruction descriptor */
+    uint64_t a_desc_base, b_desc_base;   /* shared-memory descriptors without start address */
+    uint32_t a_kstep, b_kstep;           /* descriptor advance per UMMA_K, in 16-byte units */
+    int* status;
+};
+
+/* ------------------------------------------------------------------ PTX wrappers */
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok;
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+/* Bounded wait: gives up after WAIT_LIMIT_NS of wall time.  false = gave up (or another role
+ * already did): the caller leaves its main loop and the kernel tears down. */
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          int* status, int code) {
+    unsigned long long t0 = 0;
+    for (uint32_t i = 0;; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 63u) == 63u) {
+            if (*abort_flag) return false;
+            const unsigned long long now = global_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > WAIT_LIMIT_NS) break;
+        }
+    }
+    *abort_flag = 1;
+    atomicCAS(status, 0, code);
+    return false;
+}
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
+                                            int c0, int c1, int c2, int c3) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                         uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+/* mbarrier arrives once every tcgen05.mma issued so far by this thread has completed */
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+                 ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_load_32(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+          "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+          "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <> __device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+template <> __device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half_rn(v); }
+template <typename T> __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+    T a = from_f32<T>(lo), b = from_f32<T>(hi);
+    return (uint32_t) * reinterpret_cast<uint16_t*>(&a) | ((uint32_t) * reinterpret_cast<uint16_t*>(&b) << 16);
+}
+
+/* ------------------------------------------------------------------ kernel */
+
+template <typename T, int BN, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+            const Args args)
+{
+    using Cfg = Config<BN>;
+    extern __shared__ uint8_t smem_raw[];
+    /* the swizzle pattern and the descriptors' base_offset = 0 need 1024-byte aligned tiles */
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    const uint32_t bar_base = smem_base + Cfg::STAGES * Cfg::STAGE_BYTES;
+    /* barrier words: full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], then tmem ptr, abort flag */
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (Cfg::STAGES + s); };
+    auto tfull_bar = [&](int i) { return bar_base + 8u * (2 * Cfg::STAGES + i); };
+    auto tempty_bar = [&](int i) { return bar_base + 8u * (2 * Cfg::STAGES + 2 + i); };
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + Cfg::STAGES * Cfg::STAGE_BYTES + 8 * (2 * Cfg::STAGES + 4));
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < Cfg::STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+        for (int i = 0; i < 2; ++i) { mbar_init(tfull_bar(i), 1); mbar_init(tempty_bar(i), 128); }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)Cfg::TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const long long work_begin = blockIdx.x;
+    const long long work_step = gridDim.x;
+
+    auto decode = [&](long long w, int& mt, int& nt, int& split, int& bz) {
+        mt = (int)(w % args.tiles_m); w /= args.tiles_m;
+        nt = (int)(w % args.tiles_n); w /= args.tiles_n;
+        split = (int)(w % args.splits);
+        bz = (int)(w / args.splits);
+    };
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int stage = 0; uint32_t phase = 0;
+            bool alive = true;
+            for (long long w = work_begin; alive && w < args.total_work; w += work_step) {
+                int mt, nt, split, bz; decode(w, mt, nt, split, bz);
+                const int it0 = split * args.iters_per_split;
+                const int it1 = min(it0 + args.iters_per_split, args.k_iters);
+                for (int it = it0; it < it1; ++it) {
+                    const int r = it / args.k_blocks;
+                    const int k0 = (it - r * args.k_blocks) * BLOCK_K;
+                    if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, args.status, 1)) { alive = false; break; }
+                    const uint32_t sa = smem_base + stage * Cfg::STAGE_BYTES;
+                    const uint32_t sb = sa + Cfg::A_BYTES;
+                    mbar_expect_tx(full_bar(stage), Cfg::STAGE_BYTES);
+                    if (!A_MN) {
+                        tma_load_4d(sa, &map_a, full_bar(stage), k0, mt * BLOCK_M, r * args.a_reduce_mul, bz * args.a_batch_mul);
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < BLOCK_M / 64; ++c)
+                            tma_load_4d(sa + c * (BLOCK_K * 128), &map_a, full_bar(stage), mt * BLOCK_M + c * 64, k0,
+                                        r * args.a_reduce_mul, bz * args.a_batch_mul);
+                    }
+                    if (!B_MN) {
+                        tma_load_4d(sb, &map_b, full_bar(stage), k0, nt * BN, r * args.b_reduce_mul, bz * args.b_batch_mul);
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < BN / 64; ++c)
+                            tma_load_4d(sb + c * (BLOCK_K * 128), &map_b, full_bar(stage), nt * BN + c * 64, k0,
+                                        r * args.b_reduce_mul, bz * args.b_batch_mul);
+                    }
+                    if (++stage == Cfg::STAGES) { stage = 0; phase ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            int stage = 0; uint32_t phase = 0;
+            uint32_t local_tile = 0;
+            bool alive = true;
+            for (long long w = work_begin; alive && w < args.total_work; w += work_step, ++local_tile) {
+                int mt, nt, split, bz; decode(w, mt, nt, split, bz);
+                const int it0 = split * args.iters_per_split;
+                const int it1 = min(it0 + args.iters_per_split, args.k_iters);
+                const uint32_t ab = local_tile & 1u;
+                const uint32_t acc_phase = (local_tile >> 1) & 1u;
+                if (!mbar_wait(tempty_bar(ab), acc_phase ^ 1u, abort_flag, args.status, 2)) { alive = false; break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + ab * BN;
+                for (int it = it0; it < it1; ++it) {
+                    if (!mbar_wait(full_bar(stage), phase, abort_flag, args.status, 3)) { alive = false; break; }
+                    tc_fence_after();
+                    const uint32_t sa = smem_base + stage * Cfg::STAGE_BYTES;
+                    const uint32_t sb = sa + Cfg::A_BYTES;
+                    const uint64_t da = args.a_desc_base | (uint64_t)((sa >> 4) & 0x3FFFu);
+                    const uint64_t db = args.b_desc_base | (uint64_t)((sb >> 4) & 0x3FFFu);
+#pragma unroll
+                    for (int kk = 0; kk < BLOCK_K / UMMA_K; ++kk) {
+                        umma_f16(d_tmem, da + (uint64_t)(kk * args.a_kstep), db + (uint64_t)(kk * args.b_kstep),
+                                 args.idesc, (it > it0 || kk > 0) ? 1u : 0u);
+                    }
+                    umma_commit(empty_bar(stage));            /* frees the stage when the MMAs have read it */
+                    if (++stage == Cfg::STAGES) { stage = 0; phase ^= 1u; }
+                }
+                if (alive) umma_commit(tfull_bar(ab));        /* accumulator complete */
+            }
+        }
+    } else {
+        /* epilogue: warp w may touch tensor-memory lanes 32*(w%4) .. +31 */
+        const int quarter = warp & 3;
+        const uint32_t lane_field = (uint32_t)(quarter * 32) << 16;
+        uint32_t local_tile = 0;
+        bool alive = true;
+        T* cT = reinterpret_cast<T*>(args.c);
+        for (long long w = work_begin; alive && w < args.total_work; w += work_step, ++local_tile) {
+            int mt, nt, split, bz; decode(w, mt, nt, split, bz);
+            const uint32_t ab = local_tile & 1u;
+            const uint32_t acc_phase = (local_tile >> 1) & 1u;
+            if (!mbar_wait(tfull_bar(ab), acc_phase, abort_flag, args.status, 4)) { alive = false; break; }
+            __syncwarp();
+            tc_fence_after();
+            const int row = mt * BLOCK_M + quarter * 32 + lane;
+            const bool row_ok = row < args.m;
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                uint32_t v[32];
+                __syncwarp();                 /* tcgen05.ld is warp-collective */
+                tmem_load_32(tmem_base + ab * BN + c0 + lane_field, v);
+                const int col = nt * BN + c0;
+                if (!row_ok || col >= args.n) {
+                    /* nothing to store for this lane */
+                } else if (args.splits > 1) {
+                    float* dst = args.partial + (((long long)split * args.batch + bz) * args.m + row) * (long long)args.n + col;
+                    if (col + 32 <= args.n && ((reinterpret_cast<uintptr_t>(dst) & 15u) == 0)) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4)
+                            *reinterpret_cast<uint4*>(dst + j) = make_uint4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                    } else {
+                        for (int j = 0; j < 32 && col + j < args.n; ++j) dst[j] = __uint_as_float(v[j]);
+                    }
+                } else {
+                    T* dst = cT + bz * args.c_batch + (long long)row * args.c_row + col;
+                    if (col + 32 <= args.n && ((reinterpret_cast<uintptr_t>(dst) & 15u) == 0)) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 8) {
+                            float f[8];
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(v[j + e]);
+                            if (args.accumulate) {
+                                uint4 old = *reinterpret_cast<const uint4*>(dst + j);
+                                const T* o = reinterpret_cast<const T*>(&old);
+#pragma unroll
+                                for (int e = 0; e < 8; ++e) f[e] += to_f32<T>(o[e]);
+                            }
+                            uint4 out = make_uint4(pack2<T>(f[0], f[1]), pack2<T>(f[2], f[3]),
+                                                   pack2<T>(f[4], f[5]), pack2<T>(f[6], f[7]));
+                            *reinterpret_cast<uint4*>(dst + j) = out;
+                        }
+                    } else {
+                        for (int j = 0; j < 32 && col + j < args.n; ++j) {
+                            float f = __uint_as_float(v[j]);
+                            if (args.accumulate) f += to_f32<T>(dst[j]);
+                            dst[j] = from_f32<T>(f);
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(tempty_bar(ab));
+        }
+    }
+
+    /* teardown: if a wait gave up, let copies that are still in flight land first */
+    if (*abort_flag) {
+        for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;"
+                     ::"r"(tmem_base), "r"((uint32_t)Cfg::TMEM_COLS) : "memory");
+    }
+}
+
+}  // namespace rpb_umma
+#endif

@@ -1,0 +1,410 @@
+/*
+ * Host side of the matmul path in C: the autograd node (op_matmul), its backward
+ * (backward_matmul_fn) and the few tensor helpers a C caller needs when RecPulse
+ * itself is not linked.  Works on RecPulse's Tensor / Meta / GradFn structs in place
+ * and keeps RecPulse's allocation conventions (malloc/calloc for host structs,
+ * cudaMalloc for device data) so either side can free what the other made.
+ *
+ * Unlike ops/ops.c:6816-6884 of RecPulse nothing is copied: strided and transposed
+ * views go to the GEMM as strides, batched operands as batch strides, and gradient
+ * accumulation happens in the GEMM epilogue.
+ */
+#include <cuda_runtime_api.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include "rpb_common.h"
+
+#define RPB_MAX_BATCH_DIMS 8
+
+void* rpb_reference_symbol(const char* name);   /* gemm_dispatch.cu */
+
+/* ------------------------------------------------------------------ tensor helpers */
+
+static void free_dims(Tensor* t) {
+    free(t->shape);
+    free(t->strides);
+}
+
+static Tensor* alloc_struct(DType dtype, int ndim, const int* shape, int device_id) {
+    if (ndim <= 0 || !shape || !rpb_dtype_size(dtype)) return NULL;
+    size_t total = 1;
+    for (int d = 0; d < ndim; d++) {
+        if (shape[d] <= 0) return NULL;
+        if (total > ((size_t)-1) / (size_t)shape[d]) return NULL;
+        total *= (size_t)shape[d];
+    }
+    Tensor* t = (Tensor*)calloc(1, sizeof(Tensor));
+    if (!t) return NULL;
+    t->shape = (int*)malloc(sizeof(int) * ndim);
+    t->strides = (int*)malloc(sizeof(int) * ndim);
+    if (!t->shape || !t->strides) { free_dims(t); free(t); return NULL; }
+    long long s = 1;
+    for (int d = ndim - 1; d >= 0; d--) { t->shape[d] = shape[d]; t->strides[d] = (int)s; s *= shape[d]; }
+    t->dtype = dtype; t->ndim = ndim; t->size = total; t->device_id = device_id;
+    t->owns_data = true; t->refcount = 1;
+    return t;
+}
+
+/* Uninitialised contiguous device tensor.  RecPulse's zeros_device_tensor
+ * (core/tensor_device.cu:12-63) also memsets; the GEMM overwrites every element, so no memset here. */
+Tensor* rpb_tensor_empty(DType dtype, int ndim, const int* shape, int device_id) {
+    if (device_id < 0) { fprintf(stderr, "recpulse_b200: device tensors only\n"); return NULL; }
+    Tensor* t = alloc_struct(dtype, ndim, shape, device_id);
+    if (!t) return NULL;
+    if (cudaSetDevice(device_id) != cudaSuccess ||
+        cudaMalloc(&t->data, t->size * rpb_dtype_size(dtype)) != cudaSuccess) {
+        fprintf(stderr, "recpulse_b200: cudaMalloc of %zu bytes failed: %s\n", t->size * rpb_dtype_size(dtype),
+                cudaGetErrorString(cudaGetLastError()));
+        free_dims(t); free(t);
+        return NULL;
+    }
+    return t;
+}
+
+Tensor* rpb_tensor_from_host(const void* host_data, DType dtype, int ndim, const int* shape, int device_id,
+                             bool requires_grad) {
+    if (!host_data) return NULL;
+    Tensor* t = rpb_tensor_empty(dtype, ndim, shape, device_id);
+    if (!t) return NULL;
+    if (cudaMemcpy(t->data, host_data, t->size * rpb_dtype_size(dtype), cudaMemcpyHostToDevice) != cudaSuccess) {
+        rpb_tensor_release(t);
+        return NULL;
+    }
+    if (requires_grad) {
+        t->metadata = (Meta*)calloc(1, sizeof(Meta));
+        if (!t->metadata) { rpb_tensor_release(t); return NULL; }
+        t->metadata->is_leaf = true;
+        t->metadata->requires_grad = true;
+    }
+    return t;
+}
+
+Tensor* rpb_tensor_view(Tensor* base, int ndim, const int* shape, const int* strides, size_t offset_elems) {
+    if (!base || ndim <= 0 || !shape || !strides) return NULL;
+    Tensor* t = alloc_struct(base->dtype, ndim, shape, base->device_id);
+    if (!t) return NULL;
+    memcpy(t->strides, strides, sizeof(int) * ndim);
+    t->data = (char*)base->data + offset_elems * rpb_dtype_size(base->dtype);
+    t->owns_data = false;
+    t->data_offset = base->data_offset + offset_elems;
+    t->base_tensor = base;
+    base->refcount++;
+    if (base->metadata && base->metadata->requires_grad) {
+        /* the view collects its own gradient (in the view's shape); RecPulse's view ops route it
+         * back to the leaf through their own autograd nodes, which are outside this library */
+        t->metadata = (Meta*)calloc(1, sizeof(Meta));
+        if (!t->metadata) { rpb_tensor_release(t); return NULL; }
+        t->metadata->requires_grad = true;
+    }
+    return t;
+}
+
+static bool is_contiguous(const Tensor* t) {      /* functional/functional.c:1117-1128 */
+    long long s = 1;
+    for (int d = t->ndim - 1; d >= 0; d--) {
+        if (t->strides[d] != s) return false;
+        s *= t->shape[d];
+    }
+    return true;
+}
+
+int rpb_tensor_to_host(const Tensor* t, void* host_out) {
+    if (!t || !host_out || t->device_id < 0 || t->ndim > RPB_MAX_BATCH_DIMS + 2) return -1;
+    const size_t es = rpb_dtype_size(t->dtype);
+    if (cudaSetDevice(t->device_id) != cudaSuccess) return -1;
+    if (is_contiguous(t))
+        return cudaMemcpy(host_out, t->data, t->size * es, cudaMemcpyDeviceToHost) == cudaSuccess ? 0 : -1;
+    /* strided view: one 2-D copy per innermost row pair (diagnostic path, not a hot path) */
+    int idx[RPB_MAX_BATCH_DIMS + 2] = {0};
+    const int nd = t->ndim;
+    size_t rows = t->size / (size_t)t->shape[nd - 1];
+    for (size_t r = 0; r < rows; r++) {
+        long long off = 0;
+        for (int d = 0; d < nd - 1; d++) off += (long long)idx[d] * t->strides[d];
+        char* dst = (char*)host_out + r * (size_t)t->shape[nd - 1] * es;
+        const char* src = (const char*)t->data + off * (long long)es;
+        if (cudaMemcpy2D(dst, es, src, (size_t)t->strides[nd - 1] * es, es, (size_t)t->shape[nd - 1],
+                         cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+        for (int d = nd - 2; d >= 0; d--) { if (++idx[d] < t->shape[d]) break; idx[d] = 0; }
+    }
+    return 0;
+}
+
+static void free_node(GradFn* fn) {               /* ops/ops.c:7227-7322, generic branch */
+    if (!fn) return;
+    free(fn->saved_data);
+    for (int i = 0; i < fn->num_inputs; i++)
+        if (fn->inputs && fn->inputs[i] && fn->inputs[i] != fn->owner) rpb_tensor_release(fn->inputs[i]);
+    free(fn->inputs);
+    free(fn);
+}
+
+void rpb_tensor_release(Tensor* t) {              /* core/tensor.c:360-379, core/tensor_device.cu:269-293 */
+    if (!t) return;
+    if (t->refcount > 1) { t->refcount--; return; }
+    Tensor* base = t->base_tensor;
+    if (t->metadata) {
+        if (t->metadata->grad_fn) { free_node(t->metadata->grad_fn); t->metadata->grad_fn = NULL; }
+        if (t->metadata->grad) rpb_tensor_release(t->metadata->grad);
+    }
+    if (t->owns_data && t->data) {
+        if (t->device_id >= 0) { cudaSetDevice(t->device_id); cudaFree(t->data); }
+        else free(t->data);
+    }
+    free_dims(t);
+    free(t->metadata);
+    free(t);
+    rpb_tensor_release(base);
+}
+
+/* ------------------------------------------------------------------ batch geometry */
+
+typedef struct { long long extent, a, b, c; } BatchDim;      /* strides in elements */
+
+/* Merge dimensions that form one arithmetic progression in all three operands. */
+static int collapse(BatchDim* d, int n) {
+    int changed = 1;
+    while (changed) {
+        changed = 0;
+        for (int i = 0; i < n && !changed; i++) {
+            for (int j = 0; j < n && !changed; j++) {
+                if (i == j) continue;
+                /* j becomes the outer part of i */
+                if (d[j].a == d[i].a * d[i].extent && d[j].b == d[i].b * d[i].extent &&
+                    d[j].c == d[i].c * d[i].extent) {
+                    d[i].extent *= d[j].extent;
+                    d[j] = d[n - 1];
+                    n--;
+                    changed = 1;
+                }
+            }
+        }
+    }
+    return n;
+}
+
+/* Runs C (+)= A.B for one matmul whose leading dimensions are split into independent ("batch") and
+ * summed ("reduce") lists.  One list entry of each kind goes into the kernel; the rest is looped here. */
+static int run_batched(void* C, const void* A, const void* B, RpbGemm g, BatchDim* bd, int nb, BatchDim* rd, int nr,
+                       DType dtype, int device_id) {
+    nb = collapse(bd, nb);
+    nr = collapse(rd, nr);
+    const size_t es = rpb_dtype_size(dtype);
+    /* pick the largest entry of each kind for the kernel */
+    int kb = -1, kr = -1;
+    for (int i = 0; i < nb; i++) if (kb < 0 || bd[i].extent > bd[kb].extent) kb = i;
+    for (int i = 0; i < nr; i++) if (kr < 0 || rd[i].extent > rd[kr].extent) kr = i;
+    if (kb >= 0) {
+        if (bd[kb].extent > 0x7fffffffLL) return -1;
+        g.batch = (int)bd[kb].extent; g.a_batch = bd[kb].a; g.b_batch = bd[kb].b; g.c_batch = bd[kb].c;
+        bd[kb] = bd[--nb];
+    }
+    if (kr >= 0) {
+        if (rd[kr].extent > 0x7fffffffLL) return -1;
+        g.reduce = (int)rd[kr].extent; g.a_reduce = rd[kr].a; g.b_reduce = rd[kr].b;
+        rd[kr] = rd[--nr];
+    }
+    /* odometer over what is left: batch entries first (outer), reduce entries inner */
+    BatchDim loop[2 * RPB_MAX_BATCH_DIMS];
+    int kind[2 * RPB_MAX_BATCH_DIMS];
+    int nl = 0;
+    for (int i = 0; i < nb; i++) { loop[nl] = bd[i]; kind[nl++] = 0; }
+    for (int i = 0; i < nr; i++) { loop[nl] = rd[i]; kind[nl++] = 1; }
+    long long idx[2 * RPB_MAX_BATCH_DIMS] = {0};
+    const int base_acc = g.accumulate;
+    for (;;) {
+        long long oa = 0, ob = 0, oc = 0;
+        int later_reduce = 0;
+        for (int i = 0; i < nl; i++) {
+            oa += idx[i] * loop[i].a; ob += idx[i] * loop[i].b; oc += idx[i] * loop[i].c;
+            if (kind[i] == 1 && idx[i] > 0) later_reduce = 1;
+        }
+        g.accumulate = base_acc || later_reduce;
+        if (rp_matmul_ex((char*)C + oc * (long long)es, (const char*)A + oa * (long long)es,
+                         (const char*)B + ob * (long long)es, &g, dtype, device_id, NULL) != 0) return -1;
+        int d = nl - 1;
+        for (; d >= 0; d--) { if (++idx[d] < loop[d].extent) break; idx[d] = 0; }
+        if (d < 0) break;
+    }
+    return 0;
+}
+
+static int broadcast_batch(const Tensor* a, const Tensor* b, int* out_nd, int* out_shape) {
+    const int na = a->ndim - 2, nbd = b->ndim - 2;
+    const int nd = na > nbd ? na : nbd;
+    if (nd > RPB_MAX_BATCH_DIMS) return -1;
+    for (int i = 0; i < nd; i++) {
+        const int ia = i - (nd - na), ib = i - (nd - nbd);
+        const int ea = ia >= 0 ? a->shape[ia] : 1, eb = ib >= 0 ? b->shape[ib] : 1;
+        if (ea != eb && ea != 1 && eb != 1) return -1;
+        out_shape[i] = ea > eb ? ea : eb;
+    }
+    *out_nd = nd;
+    return 0;
+}
+
+/* stride of tensor t along broadcast batch dimension i (of nd), 0 where t is broadcast */
+static long long batch_stride(const Tensor* t, int nd, int i) {
+    const int it = i - (nd - (t->ndim - 2));
+    if (it < 0 || t->shape[it] == 1) return 0;
+    return t->strides[it];
+}
+
+/* ------------------------------------------------------------------ autograd node */
+
+Tensor* op_matmul(Tensor* a, Tensor* b) {
+    if (!a || !b) return NULL;
+    if (a->ndim < 2 || b->ndim < 2) return NULL;
+    if (a->shape[a->ndim - 1] != b->shape[b->ndim - 2]) return NULL;
+    if (a->dtype != b->dtype || a->device_id != b->device_id) return NULL;
+    if (a->device_id < 0) {
+        /* host tensors stay with RecPulse's own implementation when it is loaded */
+        typedef Tensor* (*Fn)(Tensor*, Tensor*);
+        Fn ref = (Fn)rpb_reference_symbol("op_matmul");
+        if (ref && ref != &op_matmul) return ref(a, b);
+        fprintf(stderr, "recpulse_b200: op_matmul on host tensors: this library has no CPU path\n");
+        return NULL;
+    }
+
+    const int m = a->shape[a->ndim - 2], k = a->shape[a->ndim - 1], n = b->shape[b->ndim - 1];
+    int nd = 0, oshape[RPB_MAX_BATCH_DIMS + 2];
+    if (broadcast_batch(a, b, &nd, oshape)) return NULL;
+    oshape[nd] = m; oshape[nd + 1] = n;
+
+    Tensor* out = rpb_tensor_empty(a->dtype, nd + 2, oshape, a->device_id);
+    if (!out) return NULL;
+
+    RpbGemm g;
+    rpb_gemm_packed(&g, m, k, n);
+    g.a_row = a->strides[a->ndim - 2]; g.a_col = a->strides[a->ndim - 1];
+    g.b_row = b->strides[b->ndim - 2]; g.b_col = b->strides[b->ndim - 1];
+    g.a_batch = g.b_batch = g.c_batch = 0;
+    BatchDim bd[RPB_MAX_BATCH_DIMS];
+    int nbd = 0;
+    for (int i = 0; i < nd; i++) {
+        if (oshape[i] == 1) continue;
+        bd[nbd].extent = oshape[i];
+        bd[nbd].a = batch_stride(a, nd, i); bd[nbd].b = batch_stride(b, nd, i); bd[nbd].c = out->strides[i];
+        nbd++;
+    }
+    int rc = run_batched(out->data, a->data, b->data, g, bd, nbd, NULL, 0, a->dtype, a->device_id);
+    /* callers assume the result is complete on return (every RecPulse device op synchronises) */
+    if (rc == 0 && cudaStreamSynchronize(NULL) != cudaSuccess) rc = -1;
+    if (rc != 0) { rpb_tensor_release(out); return NULL; }
+
+    const bool needs_grad = (a->metadata && a->metadata->requires_grad) || (b->metadata && b->metadata->requires_grad);
+    if (needs_grad) {
+        out->metadata = (Meta*)calloc(1, sizeof(Meta));
+        GradFn* fn = (GradFn*)calloc(1, sizeof(GradFn));
+        Tensor** inputs = (Tensor**)malloc(2 * sizeof(Tensor*));
+        if (!out->metadata || !fn || !inputs) { free(fn); free(inputs); rpb_tensor_release(out); return NULL; }
+        out->metadata->requires_grad = true;
+        out->metadata->is_leaf = false;
+        fn->backward = backward_matmul_fn;
+        fn->num_inputs = 2;
+        fn->inputs = inputs;
+        inputs[0] = a; inputs[1] = b;
+        fn->saved_data = NULL;
+        /* grad_fn_attach, ops/ops.c:11-19 */
+        fn->owner = out;
+        for (int i = 0; i < 2; i++) if (inputs[i] != out) inputs[i]->refcount++;
+        out->metadata->grad_fn = fn;
+    }
+    return out;
+}
+
+/* grad of `x` (one of the two inputs): target = x's grad tensor, new or existing */
+static int grad_into(Tensor* x, const Tensor* other, const Tensor* grad_output, int side, int nd, const int* oshape) {
+    const Tensor* a = side == 0 ? x : other;
+    const Tensor* b = side == 0 ? other : x;
+    const int m = a->shape[a->ndim - 2], k = a->shape[a->ndim - 1], n = b->shape[b->ndim - 1];
+
+    Tensor* grad = x->metadata->grad;
+    const bool fresh = grad == NULL;
+    if (fresh) {
+        grad = rpb_tensor_empty(x->dtype, x->ndim, x->shape, x->device_id);
+        if (!grad) return -1;
+    } else if (!is_contiguous(grad) || grad->size != x->size || grad->dtype != x->dtype) {
+        fprintf(stderr, "recpulse_b200: existing grad is not a packed tensor of the input's shape\n");
+        return -1;
+    }
+
+    RpbGemm g;
+    memset(&g, 0, sizeof(g));
+    g.batch = g.reduce = 1;
+    g.accumulate = fresh ? 0 : 1;
+    const long long go_row = grad_output->strides[grad_output->ndim - 2];
+    const long long go_col = grad_output->strides[grad_output->ndim - 1];
+    const void *A, *B;
+    if (side == 0) {            /* dA[m,k] = dC[m,n] . B^T[n,k] */
+        g.m = m; g.n = k; g.k = n;
+        g.a_row = go_row; g.a_col = go_col;
+        g.b_row = b->strides[b->ndim - 1]; g.b_col = b->strides[b->ndim - 2];
+        A = grad_output->data; B = b->data;
+    } else {                    /* dB[k,n] = A^T[k,m] . dC[m,n] */
+        g.m = k; g.n = n; g.k = m;
+        g.a_row = a->strides[a->ndim - 1]; g.a_col = a->strides[a->ndim - 2];
+        g.b_row = go_row; g.b_col = go_col;
+        A = a->data; B = grad_output->data;
+    }
+    g.c_row = grad->strides[grad->ndim - 2];
+
+    BatchDim bd[RPB_MAX_BATCH_DIMS], rd[RPB_MAX_BATCH_DIMS];
+    int nb = 0, nr = 0;
+    for (int i = 0; i < nd; i++) {
+        if (oshape[i] == 1) continue;
+        const long long sx = batch_stride(x, nd, i);          /* 0: x is broadcast here -> sum */
+        const long long so = batch_stride(other, nd, i);
+        const long long sg = grad_output->strides[i + (grad_output->ndim - 2 - nd)];
+        BatchDim e;
+        e.extent = oshape[i];
+        e.a = side == 0 ? sg : so;                            /* side 1: A operand is `other` = a */
+        e.b = side == 0 ? so : sg;
+        if (sx == 0) { e.c = 0; rd[nr++] = e; }
+        else {
+            const int ix = i - (nd - (x->ndim - 2));
+            e.c = grad->strides[ix];
+            bd[nb++] = e;
+        }
+    }
+    int rc = run_batched(grad->data, A, B, g, bd, nb, rd, nr, x->dtype, x->device_id);
+    if (rc == 0 && cudaStreamSynchronize(NULL) != cudaSuccess) rc = -1;
+    if (rc != 0) {
+        if (fresh) rpb_tensor_release(grad);
+        return -1;
+    }
+    if (fresh) x->metadata->grad = grad;
+    return 0;
+}
+
+void backward_matmul_fn(GradFn* self, Tensor* grad_output) {
+    if (!self || !grad_output || self->num_inputs != 2 || !self->inputs) return;
+    Tensor* a = self->inputs[0];
+    Tensor* b = self->inputs[1];
+    if (!a || !b) return;
+    if (a->device_id < 0) {
+        typedef void (*Fn)(GradFn*, Tensor*);
+        Fn ref = (Fn)rpb_reference_symbol("backward_matmul_fn");
+        if (ref && ref != &backward_matmul_fn) ref(self, grad_output);
+        return;
+    }
+    int nd = 0, oshape[RPB_MAX_BATCH_DIMS + 2];
+    if (broadcast_batch(a, b, &nd, oshape)) return;
+    if (grad_output->ndim != nd + 2 || grad_output->dtype != a->dtype || grad_output->device_id != a->device_id) {
+        fprintf(stderr, "recpulse_b200: backward_matmul_fn: upstream gradient does not match the output\n");
+        return;
+    }
+    if (a->metadata && a->metadata->requires_grad) grad_into(a, b, grad_output, 0, nd, oshape);
+    if (b->metadata && b->metadata->requires_grad) grad_into(b, a, grad_output, 1, nd, oshape);
+}
+
+int rpb_backward_node(Tensor* out, Tensor* grad_output) {
+    if (!out || !grad_output || !out->metadata || !out->metadata->grad_fn) return -1;
+    GradFn* fn = out->metadata->grad_fn;
+    fn->backward(fn, grad_output);
+    free_node(fn);
+    out->metadata->grad_fn = NULL;
+    return 0;
+}

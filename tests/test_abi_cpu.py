@@ -1,0 +1,86 @@
+"""CPU-side checks: the shared library builds, loads and exports the whole C ABI;
+host-side argument checks that need no GPU."""
+import ctypes as C
+import os
+import re
+
+import numpy as np
+import pytest
+
+import recpulse_b200 as rpb
+from recpulse_b200 import _lib
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_library_loads_and_exports_every_declared_symbol():
+    lib = rpb.load()
+    header = open(os.path.join(ROOT, "include", "recpulse_b200.h")).read()
+    body = header[header.index("drop-in entry points"):]
+    declared = set(re.findall(r"\b([a-z_0-9]+)\s*\(", re.sub(r"/\*.*?\*/", "", body, flags=re.S)))
+    declared = {d for d in declared if d.startswith(("rp_", "rpb_", "op_", "matmul_", "backward_"))}
+    assert declared, "no declarations found"
+    assert declared == set(_lib.SYMBOLS), declared ^ set(_lib.SYMBOLS)
+    for name in declared:
+        assert hasattr(lib, name), name
+    assert b"sm_100a" in lib.rpb_version()
+
+
+def test_struct_layout_matches_reference_abi():
+    # core/tensor.h:27-42 on LP64: dtype@0 data@8 ndim@16 size@24 shape@32 strides@40 device_id@48
+    # owns_data@52 refcount@56 base_tensor@64 data_offset@72 metadata@80, sizeof 88
+    T = _lib.CTensor
+    assert (T.dtype.offset, T.data.offset, T.ndim.offset, T.size.offset) == (0, 8, 16, 24)
+    assert (T.shape.offset, T.strides.offset, T.device_id.offset, T.owns_data.offset) == (32, 40, 48, 52)
+    assert (T.refcount.offset, T.base_tensor.offset, T.data_offset.offset, T.metadata.offset) == (56, 64, 72, 80)
+    assert C.sizeof(T) == 88
+    assert C.sizeof(_lib.Meta) == 24 and _lib.Meta.grad_fn.offset == 8 and _lib.Meta.grad.offset == 16
+    assert C.sizeof(_lib.GradFn) == 40
+
+
+def test_packed_descriptor():
+    lib = rpb.load()
+    g = rpb.RpbGemm()
+    lib.rpb_gemm_packed(C.byref(g), 3, 4, 5)
+    assert (g.m, g.k, g.n, g.batch, g.reduce) == (3, 4, 5, 1, 1)
+    assert (g.a_row, g.a_col, g.b_row, g.b_col, g.c_row, g.accumulate) == (4, 1, 5, 1, 5, 0)
+
+
+def test_argument_errors_without_gpu():
+    lib = rpb.load()
+    buf = np.zeros(16, np.float32).ctypes.data_as(C.c_void_p)
+    # rp_matmul's checks, functional/functional.c:979
+    assert lib.rp_matmul(None, buf, buf, 2, 2, 2, 0, 0) == -1
+    assert lib.rp_matmul(buf, buf, buf, 0, 2, 2, 0, 0) == -1
+    assert lib.rp_matmul(buf, buf, buf, 2, -1, 2, 0, 0) == -1
+    # host memory is not this library's business and no reference is loaded here
+    assert lib.rp_matmul(buf, buf, buf, 2, 2, 2, 0, -1) == -1
+    g = rpb.RpbGemm()
+    lib.rpb_gemm_packed(C.byref(g), 2, 2, 2)
+    assert lib.rp_matmul_ex(buf, buf, buf, C.byref(g), 0, -1, None) == -1
+    assert lib.op_matmul(None, None) is None or not lib.op_matmul(None, None)
+
+
+def test_op_matmul_rejects_bad_operands_on_host_structs():
+    # shape / dtype / device checks happen before any CUDA call (ops/ops.c:6817-6820)
+    lib = rpb.load()
+
+    def host_struct(shape, dtype=0, device=-1):
+        t = _lib.CTensor()
+        t.dtype = dtype; t.ndim = len(shape); t.device_id = device
+        t.shape = (C.c_int * len(shape))(*shape)
+        strides = [int(np.prod(shape[i + 1:])) for i in range(len(shape))]
+        t.strides = (C.c_int * len(shape))(*strides)
+        t.size = int(np.prod(shape))
+        return t
+
+    a, b = host_struct([2, 3]), host_struct([4, 5])
+    assert not lib.op_matmul(C.byref(a), C.byref(b))           # inner dimension mismatch
+    a, b = host_struct([2, 3]), host_struct([3, 5], dtype=1)
+    assert not lib.op_matmul(C.byref(a), C.byref(b))           # dtype mismatch
+    a, b = host_struct([2, 3], device=0), host_struct([3, 5], device=-1)
+    assert not lib.op_matmul(C.byref(a), C.byref(b))           # cpu @ cuda
+    a, b = host_struct([3]), host_struct([3, 5])
+    assert not lib.op_matmul(C.byref(a), C.byref(b))           # 1-D operand
+    a, b = host_struct([2, 3]), host_struct([3, 5])
+    assert not lib.op_matmul(C.byref(a), C.byref(b))           # host tensors: no CPU path here

@@ -1,0 +1,201 @@
+"""GPU parity of the raw GEMM entry points (rp_matmul, matmul_kernel_device, rp_matmul_ex)
+against the CPU oracle, through the C ABI.  Sizes are kept where the oracle's naive loop
+finishes in seconds; full-size workloads are covered by test_full_size_gpu.py."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+import recpulse_b200 as rpb
+from recpulse_b200 import _lib
+from oracle import oracle as O
+from helpers import CODE, check_close, f64, rand_operand
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def lib():
+    lib = rpb.load()
+    yield lib
+    lib.rpb_force_kernel(0)
+    assert lib.rpb_device_status(0) == 0
+
+
+def dev(arr, dtype):
+    return rpb.Tensor.from_numpy(np.ascontiguousarray(arr), dtype=dtype)
+
+
+def store(logical, transposed, pad):
+    """Lay a [..., r, c] array out in memory: optionally transposed storage, optionally padded rows.
+    Returns (buffer, row_stride, col_stride, matrix_elems) with strides in elements of the LOGICAL matrix."""
+    x = np.swapaxes(logical, -1, -2) if transposed else logical
+    rows, cols = x.shape[-2:]
+    ld = cols + pad
+    buf = np.zeros(x.shape[:-1] + (ld,), x.dtype)
+    buf[..., :cols] = x
+    rs, cs = (1, ld) if transposed else (ld, 1)
+    return buf, rs, cs, rows * ld
+
+
+def run_ex(lib, dtype, a, b, ta=False, tb=False, pad_a=0, pad_b=0, c_init=None, expect=None):
+    """a: [batch|1, reduce|1, m, k] bits, b: [batch|1, reduce|1, k, n] bits (size-1 dims broadcast)."""
+    batch = max(a.shape[0], b.shape[0]); reduce = max(a.shape[1], b.shape[1])
+    m, k = a.shape[2:]; n = b.shape[3]
+    abuf, a_rs, a_cs, a_mat = store(a, ta, pad_a)
+    bbuf, b_rs, b_cs, b_mat = store(b, tb, pad_b)
+    g = rpb.RpbGemm()
+    g.m, g.n, g.k, g.batch, g.reduce = m, n, k, batch, reduce
+    g.a_row, g.a_col, g.b_row, g.b_col = a_rs, a_cs, b_rs, b_cs
+    g.a_reduce = a_mat if a.shape[1] > 1 else 0
+    g.a_batch = a_mat * a.shape[1] if a.shape[0] > 1 else 0
+    g.b_reduce = b_mat if b.shape[1] > 1 else 0
+    g.b_batch = b_mat * b.shape[1] if b.shape[0] > 1 else 0
+    g.c_row, g.c_batch = n, m * n
+    g.accumulate = int(c_init is not None)
+    ta_, tb_ = dev(abuf, dtype), dev(bbuf, dtype)
+    c0 = c_init if c_init is not None else np.zeros((batch, m, n), O.storage(CODE[dtype]))
+    tc = dev(c0, dtype)
+    rc = lib.rp_matmul_ex(C.c_void_p(tc.data_ptr), C.c_void_p(ta_.data_ptr), C.c_void_p(tb_.data_ptr), C.byref(g),
+                          CODE[dtype], 0, None)
+    assert rc == 0
+    got = tc.to_numpy()
+    if expect is not None:
+        assert lib.rpb_last_kernel() in expect, lib.rpb_last_kernel()
+    # reference: per batch, sum over the summed problems, unrounded, then one rounding
+    a64 = np.broadcast_to(f64(a, dtype), (batch, reduce, m, k))
+    b64 = np.broadcast_to(f64(b, dtype), (batch, reduce, k, n))
+    ref64 = np.einsum("brmk,brkn->bmn", a64, b64)
+    if c_init is not None:
+        ref64 = ref64 + f64(c_init, dtype)
+    ref = O.narrow(ref64.astype(np.float32), CODE[dtype]) if dtype in ("float16", "bfloat16") else ref64.astype(
+        O.storage(CODE[dtype]))
+    check_close(got, ref, dtype, k * reduce, what=f"{dtype} m{m} k{k} n{n} b{batch} r{reduce} ta{ta} tb{tb}")
+    if reduce == 1 and c_init is None:
+        # same-dtype reference of the path: the oracle's restatement of rp_matmul
+        for bi in range(batch):
+            o = O.rp_matmul(np.ascontiguousarray(a[min(bi, a.shape[0] - 1), 0]),
+                            np.ascontiguousarray(b[min(bi, b.shape[0] - 1), 0]), CODE[dtype])
+            check_close(got[bi], o, dtype, k, what=f"vs oracle {dtype} m{m} k{k} n{n}")
+    return got
+
+
+SHAPES_SMALL = [(1, 1, 1), (3, 4, 5), (1, 7, 1), (16, 32, 8), (33, 65, 17), (64, 64, 64), (100, 130, 70), (128, 784, 256)]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "float64", "float16", "bfloat16"])
+@pytest.mark.parametrize("shape", SHAPES_SMALL)
+def test_simt_all_dtypes_all_layouts(lib, dtype, shape):
+    lib.rpb_force_kernel(_lib.KERNEL_SIMT)
+    m, k, n = shape
+    rng = np.random.default_rng(hash((dtype, shape)) % 2**32)
+    a = rand_operand(rng, (1, 1, m, k), dtype); b = rand_operand(rng, (1, 1, k, n), dtype, scale=1 / np.sqrt(k))
+    for ta, tb in [(False, False), (True, False), (False, True), (True, True)]:
+        run_ex(lib, dtype, a, b, ta=ta, tb=tb, pad_a=3 if ta else 0, pad_b=5 if tb else 0, expect=(_lib.KERNEL_SIMT,))
+    lib.rpb_force_kernel(0)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "float64"])
+def test_simt_large_tile_and_splitk(lib, dtype):
+    rng = np.random.default_rng(5)
+    for (m, k, n) in [(512, 96, 640), (64, 2048, 64), (700, 300, 520)]:
+        a = rand_operand(rng, (1, 1, m, k), dtype); b = rand_operand(rng, (1, 1, k, n), dtype, scale=1 / np.sqrt(k))
+        run_ex(lib, dtype, a, b, expect=(_lib.KERNEL_SIMT,))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "float64", "float16", "bfloat16"])
+def test_batch_reduce_accumulate_semantics(lib, dtype):
+    rng = np.random.default_rng(11)
+    m, k, n = 24, 40, 16
+    a = rand_operand(rng, (3, 2, m, k), dtype); b = rand_operand(rng, (3, 2, k, n), dtype, scale=0.2)
+    run_ex(lib, dtype, a, b)
+    # broadcast B over the batch, and over the summed problems
+    run_ex(lib, dtype, a, rand_operand(rng, (1, 1, k, n), dtype, scale=0.2))
+    run_ex(lib, dtype, rand_operand(rng, (1, 2, m, k), dtype), b)
+    c0 = rand_operand(rng, (3, m, n), dtype)
+    run_ex(lib, dtype, a, b, c_init=c0)
+    run_ex(lib, dtype, a, b, ta=True, tb=True, c_init=c0)
+
+
+UMMA = (_lib.KERNEL_UMMA, _lib.KERNEL_UMMA_SPLITK)
+
+
+@pytest.mark.parametrize("dtype", ["bfloat16", "float16"])
+@pytest.mark.parametrize("layout", [(False, False), (True, False), (False, True), (True, True)])
+def test_umma_layouts_and_ragged_edges(lib, dtype, layout):
+    """All four operand-major combinations (forward NN, dA = dC.B^T, dB = A^T.dC, and both
+    transposed), tile-aligned and ragged M/N/K.  Strides stay multiples of 8 elements (16 bytes)."""
+    ta, tb = layout
+    rng = np.random.default_rng(17)
+    for (m, k, n) in [(128, 64, 256), (128, 128, 64), (256, 512, 512), (136, 200, 72), (8, 8, 8), (264, 72, 520),
+                      (1000, 328, 136), (64, 512, 2048)]:
+        a = rand_operand(rng, (1, 1, m, k), dtype); b = rand_operand(rng, (1, 1, k, n), dtype, scale=1 / np.sqrt(k))
+        run_ex(lib, dtype, a, b, ta=ta, tb=tb, expect=UMMA)
+        run_ex(lib, dtype, a, b, ta=ta, tb=tb, pad_a=8, pad_b=16, expect=UMMA)
+
+
+@pytest.mark.parametrize("dtype", ["bfloat16", "float16"])
+def test_umma_splitk_batch_reduce_accumulate(lib, dtype):
+    rng = np.random.default_rng(23)
+    # skinny, long K -> split over CTAs
+    a = rand_operand(rng, (1, 1, 64, 4096), dtype); b = rand_operand(rng, (1, 1, 4096, 128), dtype, scale=1 / 64)
+    run_ex(lib, dtype, a, b, expect=(_lib.KERNEL_UMMA_SPLITK,))
+    run_ex(lib, dtype, a, b, ta=True, tb=False, expect=(_lib.KERNEL_UMMA_SPLITK,))
+    c0 = rand_operand(rng, (1, 64, 128), dtype)
+    run_ex(lib, dtype, a, b, c_init=c0, expect=(_lib.KERNEL_UMMA_SPLITK,))
+    # batched, broadcast, summed problems, accumulate into C
+    m, k, n = 72, 136, 200
+    a = rand_operand(rng, (5, 3, m, k), dtype); b = rand_operand(rng, (5, 3, k, n), dtype, scale=0.1)
+    run_ex(lib, dtype, a, b, expect=UMMA)
+    run_ex(lib, dtype, a, b, ta=True, tb=True, expect=UMMA)
+    run_ex(lib, dtype, a, rand_operand(rng, (1, 1, k, n), dtype, scale=0.1), expect=UMMA)
+    run_ex(lib, dtype, rand_operand(rng, (1, 3, m, k), dtype), b, expect=UMMA)
+    c0 = rand_operand(rng, (5, m, n), dtype)
+    run_ex(lib, dtype, a, b, c_init=c0, expect=UMMA)
+    # the broadcast-batched fp16 workload, reduced: A[16,512,64] x B[1,64,512]
+    a = rand_operand(rng, (16, 1, 512, 64), dtype); b = rand_operand(rng, (1, 1, 64, 512), dtype, scale=1 / 8)
+    run_ex(lib, dtype, a, b, expect=UMMA)
+
+
+@pytest.mark.parametrize("dtype", ["bfloat16", "float16"])
+def test_unaligned_half_operands_take_the_general_path(lib, dtype):
+    rng = np.random.default_rng(29)
+    a = rand_operand(rng, (1, 1, 33, 65), dtype); b = rand_operand(rng, (1, 1, 65, 17), dtype, scale=0.1)
+    run_ex(lib, dtype, a, b, expect=(_lib.KERNEL_SIMT,))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "float64", "float16", "bfloat16"])
+def test_rp_matmul_and_matmul_kernel_device(lib, dtype):
+    rng = np.random.default_rng(31)
+    for (m, k, n) in [(2, 3, 2), (64, 512, 256), (128, 784, 256)]:
+        a = rand_operand(rng, (m, k), dtype); b = rand_operand(rng, (k, n), dtype, scale=1 / np.sqrt(k))
+        ta, tb = dev(a, dtype), dev(b, dtype)
+        tc = dev(np.zeros((m, n), O.storage(CODE[dtype])), dtype)
+        args = (C.c_void_p(tc.data_ptr), C.c_void_p(ta.data_ptr), C.c_void_p(tb.data_ptr), m, k, n, CODE[dtype])
+        assert lib.rp_matmul(*args, 0) == 0
+        check_close(tc.to_numpy(), O.rp_matmul(a, b, CODE[dtype]), dtype, k, "rp_matmul")
+        tc2 = dev(np.zeros((m, n), O.storage(CODE[dtype])), dtype)
+        assert lib.matmul_kernel_device(C.c_void_p(tc2.data_ptr), *args[1:]) == 0
+        assert np.array_equal(tc2.to_numpy(), tc.to_numpy())
+    # reference tests/unit/test_functional.py:281-302 known answer
+    a = np.arange(1, 7, dtype=np.float32).reshape(2, 3); b = np.arange(1, 7, dtype=np.float32).reshape(3, 2)
+    ta, tb, tc = dev(a, "float32"), dev(b, "float32"), dev(np.zeros((2, 2), np.float32), "float32")
+    assert lib.rp_matmul(C.c_void_p(tc.data_ptr), C.c_void_p(ta.data_ptr), C.c_void_p(tb.data_ptr), 2, 3, 2, 0, 0) == 0
+    assert np.array_equal(tc.to_numpy(), np.array([[22, 28], [49, 64]], np.float32))
+
+
+def test_host_buffer_entry_point(lib):
+    rng = np.random.default_rng(37)
+    a = rand_operand(rng, (96, 160), "bfloat16"); b = rand_operand(rng, (160, 64), "bfloat16", scale=0.1)
+    c = np.zeros((96, 64), np.uint16)
+    assert lib.rp_matmul_host(c.ctypes.data_as(C.c_void_p), a.ctypes.data_as(C.c_void_p),
+                              b.ctypes.data_as(C.c_void_p), 96, 160, 64, O.BF16, 0) == 0
+    check_close(c, O.rp_matmul(a, b, O.BF16), "bfloat16", 160, "rp_matmul_host")
+
+
+def test_results_do_not_depend_on_scheduling(lib):
+    rng = np.random.default_rng(41)
+    a = rand_operand(rng, (1, 1, 64, 4096), "bfloat16"); b = rand_operand(rng, (1, 1, 4096, 128), "bfloat16", scale=1 / 64)
+    first = run_ex(lib, "bfloat16", a, b)
+    for _ in range(3):
+        assert np.array_equal(run_ex(lib, "bfloat16", a, b), first)

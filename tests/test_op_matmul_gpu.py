@@ -1,0 +1,144 @@
+"""GPU parity of op_matmul + backward_matmul_fn (the autograd node) through the C ABI,
+against fixtures produced by the unmodified reference and against the oracle."""
+import numpy as np
+import pytest
+
+import recpulse_b200 as rpb
+from recpulse_b200 import _lib
+from oracle import oracle as O
+from helpers import CODE, check_close, rand_operand
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def lib():
+    lib = rpb.load()
+    yield lib
+    lib.rpb_force_kernel(0)
+    assert lib.rpb_device_status(0) == 0
+
+
+def T(bits, dtype, grad=False):
+    return rpb.Tensor.from_numpy(np.ascontiguousarray(bits), dtype=dtype, requires_grad=grad)
+
+
+@pytest.mark.parametrize("family", [_lib.KERNEL_SIMT, 0])
+@pytest.mark.parametrize("dtype", ["float32", "float64", "float16", "bfloat16"])
+def test_reference_fixtures_forward_backward(lib, golden, dtype, family):
+    lib.rpb_force_kernel(family)
+    for (name, dt), case in golden.items():
+        if dt != dtype:
+            continue
+        m, k, n, ta, tb, twice = [int(v) for v in case["meta"]]
+        a = T(case["a"], dtype, grad=True); b = T(case["b"], dtype, grad=True); w = T(case["w"], dtype)
+        av = a.transpose(0, 1) if ta else a                 # views collect their own grads
+        bv = b.transpose(0, 1) if tb else b
+        y = av.op_matmul(bv)
+        assert y.shape == (m, n) and y.dtype == dtype
+        check_close(y.to_numpy(), case["c"], dtype, k, f"{name} fwd")
+        y.backward(w)
+        if twice:
+            y2 = av.op_matmul(bv)
+            y2.backward(w)                                  # accumulates into the existing grads
+        da = av.grad.to_numpy(); db = bv.grad.to_numpy()
+        # fixtures hold the leaf-layout grads; the gradient of a transposed view is their transpose
+        exp_da = case["da"].T if ta else case["da"]; exp_db = case["db"].T if tb else case["db"]
+        check_close(da, exp_da, dtype, n, f"{name} dA")
+        check_close(db, exp_db, dtype, m, f"{name} dB")
+    lib.rpb_force_kernel(0)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "float16", "bfloat16", "float64"])
+def test_mlp_and_lstm_gate_shapes(lib, dtype):
+    """The float32 MLP-layer GEMM X[128,784].W[784,256] and the LSTM gate GEMM H[64,512].W[512,2048],
+    the latter also with W given as the stride-swapped view of a [2048,512] buffer."""
+    rng = np.random.default_rng(0)
+    for (m, k, n, tview) in [(128, 784, 256, False), (64, 512, 2048, False), (64, 512, 2048, True)]:
+        x = rand_operand(rng, (m, k), dtype)
+        w = O.narrow(rng.uniform(-1, 1, (k, n)) / np.sqrt(k), CODE[dtype])
+        dy = rand_operand(rng, (m, n), dtype)
+        X = T(x, dtype, grad=True)
+        if tview:
+            Wbuf = T(np.ascontiguousarray(w.T), dtype, grad=True)
+            W = Wbuf.transpose(0, 1)
+        else:
+            W = T(w, dtype, grad=True)
+        y = X.op_matmul(W)
+        check_close(y.to_numpy(), O.rp_matmul(x, w, CODE[dtype]), dtype, k, "fwd")
+        y.backward(T(dy, dtype))
+        da, db = O.matmul_backward(x, w, dy, CODE[dtype])
+        check_close(X.grad.to_numpy(), da, dtype, n, "dX")
+        gw = W.grad.to_numpy()
+        check_close(gw, db, dtype, m, "dW")
+
+
+@pytest.mark.parametrize("dtype", ["float16", "bfloat16", "float32"])
+def test_batched_and_broadcast_batched(lib, dtype):
+    rng = np.random.default_rng(4)
+    # A[8,512,64] x B[1,64,512] (broadcast over the batch); dB is summed over the batch
+    a = rand_operand(rng, (8, 96, 64), dtype); b = rand_operand(rng, (1, 64, 128), dtype, scale=1 / 8)
+    dc = rand_operand(rng, (8, 96, 128), dtype)
+    A = T(a, dtype, grad=True); B = T(b, dtype, grad=True)
+    y = A.op_matmul(B)
+    assert y.shape == (8, 96, 128)
+    check_close(y.to_numpy(), O.bmm(a, b, CODE[dtype]), dtype, 64, "bmm fwd")
+    y.backward(T(dc, dtype))
+    da, db = O.bmm_backward(a, b, dc, CODE[dtype])
+    check_close(A.grad.to_numpy(), da, dtype, 128, "bmm dA")
+    assert B.grad.shape == (1, 64, 128)
+    check_close(B.grad.to_numpy(), db, dtype, 8 * 96, "bmm dB (summed over batch)")
+    # 2-D weight against a 3-D batch (Linear applied to [batch, seq, features])
+    b2 = rand_operand(rng, (64, 128), dtype, scale=1 / 8)
+    A = T(a, dtype, grad=True); B = T(b2, dtype, grad=True)
+    y = A.op_matmul(B)
+    check_close(y.to_numpy(), O.bmm(a, b2[None], CODE[dtype]), dtype, 64, "3d x 2d fwd")
+    y.backward(T(dc, dtype))
+    da, db = O.bmm_backward(a, b2[None], dc, CODE[dtype])
+    assert B.grad.shape == (64, 128)
+    check_close(B.grad.to_numpy(), db[0], dtype, 8 * 96, "3d x 2d dB")
+    # both batched, two leading dims, one of them broadcast in A
+    a4 = rand_operand(rng, (1, 3, 40, 24), dtype); b4 = rand_operand(rng, (2, 3, 24, 32), dtype, scale=0.2)
+    dc4 = rand_operand(rng, (2, 3, 40, 32), dtype)
+    A = T(a4, dtype, grad=True); B = T(b4, dtype, grad=True)
+    y = A.op_matmul(B)
+    assert y.shape == (2, 3, 40, 32)
+    from helpers import f64
+    ref = np.einsum("xymk,xykn->xymn", np.broadcast_to(f64(a4, dtype), (2, 3, 40, 24)), f64(b4, dtype))
+    assert np.linalg.norm(f64(y.to_numpy(), dtype) - ref) / np.linalg.norm(ref) < {"float32": 1e-5, "float16": 2e-3, "bfloat16": 1e-2}[dtype]
+    y.backward(T(dc4, dtype))
+    ref_da = np.einsum("xymn,xykn->ymk", f64(dc4, dtype), f64(b4, dtype))[None]
+    ref_db = np.einsum("ymk,xymn->xykn", f64(a4, dtype)[0], f64(dc4, dtype))
+    got_da = f64(A.grad.to_numpy(), dtype); got_db = f64(B.grad.to_numpy(), dtype)
+    assert A.grad.shape == (1, 3, 40, 24) and B.grad.shape == (2, 3, 24, 32)
+    tol = {"float32": 1e-5, "float16": 2e-3, "bfloat16": 1e-2}[dtype]
+    assert np.linalg.norm(got_da - ref_da) / np.linalg.norm(ref_da) < tol
+    assert np.linalg.norm(got_db - ref_db) / np.linalg.norm(ref_db) < tol
+
+
+def test_errors_match_reference_behaviour(lib):
+    a = T(np.zeros((2, 3), np.float32), "float32"); b = T(np.zeros((4, 5), np.float32), "float32")
+    with pytest.raises(RuntimeError, match="op_matmul operation failed"):
+        a.op_matmul(b)                                       # stress_edge_cases.py:41-42
+    b64 = T(np.zeros((3, 5), np.float64), "float64")
+    with pytest.raises(RuntimeError):
+        a.op_matmul(b64)
+    v = T(np.zeros((3,), np.float32), "float32")
+    with pytest.raises(RuntimeError):
+        v.op_matmul(b)
+
+
+def test_no_grad_no_node_and_refcounts(lib):
+    a = T(np.ones((4, 4), np.float32), "float32"); b = T(np.ones((4, 4), np.float32), "float32")
+    y = a.op_matmul(b)
+    assert not y._t.metadata                                 # ops.c:6851: node only if an input requires grad
+    assert np.array_equal(y.to_numpy(), np.full((4, 4), 4, np.float32))
+    a = T(np.ones((4, 4), np.float32), "float32", grad=True)
+    before = (a._t.refcount, b._t.refcount)
+    y = a.op_matmul(b)
+    assert y._t.metadata and y._t.metadata.contents.requires_grad and not y._t.metadata.contents.is_leaf
+    assert (a._t.refcount, b._t.refcount) == (before[0] + 1, before[1] + 1)   # grad_fn_attach retains inputs
+    y.backward(T(np.ones((4, 4), np.float32), "float32"))
+    assert (a._t.refcount, b._t.refcount) == before          # node freed, inputs released
+    assert a.grad is not None and b.grad is None             # only inputs that require grad get one
+    assert np.array_equal(a.grad.to_numpy(), np.full((4, 4), 4, np.float32))
