@@ -138,6 +138,25 @@ int rp_matmul_ex(void* C, const void* A, const void* B, const RpbGemm* g, DType 
 int rp_matmul_host(void* C, const void* A, const void* B, int m, int k, int n, DType dtype,
                    int device_id);
 
+/* No counterpart in RecPulse.  C[m,n] = A[m,k] . B[k,n] for packed row-major float16 / bfloat16
+ * operands, for callers that cannot let a library allocate: processes that have given all device
+ * memory to their own pool (a hidden cudaMalloc would fail or fragment it) and latency-critical
+ * sections where cudaMalloc / cudaFree, which stall the device, are off limits.  It is the K-split
+ * tcgen05 GEMM with its partial tiles kept in a fixed 16 MiB array inside the library image instead
+ * of an allocated buffer; it calls no cudaMalloc, cudaFree or other allocating routine.
+ *   - Limit: (number of K splits) x m x n x 4 bytes must fit in 16 MiB, else -1 with a message
+ *     (roughly m x n <= 2M elements for short K, less for long K).  Pointers 16-byte aligned, k and n
+ *     multiples of 8.  Every GPU that loads the library holds the 16 MiB until the process exits.
+ *   - The first call on a device looks up the device addresses of the built-in buffers; make that
+ *     first call before starting any stream capture on that device.
+ *   - All calls on a device share the one array: two calls that overlap on the GPU (different
+ *     streams, or different threads) race on it.  Serialise them.
+ *   - Runs on `stream` (NULL = legacy default stream).  With kernel_status == NULL it returns once the
+ *     work is queued.  With a pointer it waits for the result and stores the kernel's status word
+ *     (0 = ok; non-zero = a bounded wait inside the kernel ran out, result invalid, return -1). */
+int rp_matmul_noalloc(void* C, const void* A, const void* B, int m, int k, int n, DType dtype,
+                      int device_id, void* stream, int* kernel_status);
+
 /* ---- additive: diagnostics and tuning --------------------------------------*/
 
 enum {                              /* values of rpb_last_kernel()                           */

@@ -525,3 +525,178 @@ int rpb_device_status(int device_id) {
 }
 
 }  // extern "C"
+
+/* ====================================================================================
+ * rp_matmul_noalloc: the K-split tcgen05 GEMM for callers that must not allocate.
+ *
+ * Some users of this library cannot let it call cudaMalloc: a training process that has
+ * handed (nearly) all device memory to its own pool, so that an allocation made behind
+ * its back fails or fragments the pool; and code in a latency-critical section, where
+ * cudaMalloc / cudaFree stall the whole device.  The regular K-split path keeps its
+ * partial tiles in a cudaMalloc'ed buffer that grows on demand.  This variant keeps them
+ * in a fixed array that is part of the loaded library image instead, so nothing is ever
+ * allocated -- at the price of a size limit and of RPB_NOALLOC_SCRATCH_BYTES of device
+ * memory held by every GPU that loads the library, until the process exits.
+ * ==================================================================================== */
+
+#define RPB_NOALLOC_SCRATCH_BYTES (16u << 20)
+
+/* Partial fp32 tiles [splits][m][n] of the call in flight.  In host code this name is only a
+ * stand-in for the device object; the address a kernel can use comes from cudaGetSymbolAddress. */
+static __device__ __align__(256) unsigned char g_noalloc_scratch[RPB_NOALLOC_SCRATCH_BYTES];
+static __device__ int g_noalloc_status;
+
+namespace {
+
+struct NoAllocDevice {
+    bool ready = false;
+    float* scratch = nullptr;       /* device address of g_noalloc_scratch on this device */
+    int* status = nullptr;          /* device address of g_noalloc_status on this device */
+    int sm_count = 0;
+    int cc_major = 0;
+};
+NoAllocDevice g_noalloc_dev[MAX_DEVICES];
+
+/* Once per device, with that device current: resolve the device addresses of the static
+ * objects.  No allocation happens here or anywhere below. */
+int noalloc_setup(int device_id, NoAllocDevice** out) {
+    if (device_id < 0 || device_id >= MAX_DEVICES) {
+        fprintf(stderr, "recpulse_b200: invalid device id %d\n", device_id);
+        return -1;
+    }
+    NoAllocDevice& d = g_noalloc_dev[device_id];
+    if (!d.ready) {
+        std::lock_guard<std::mutex> lock(g_mutex);
+        if (!d.ready) {
+            void* p = nullptr;
+            RPB_CUDA(cudaGetSymbolAddress(&p, g_noalloc_scratch));
+            d.scratch = reinterpret_cast<float*>(p);
+            RPB_CUDA(cudaGetSymbolAddress(&p, g_noalloc_status));
+            d.status = reinterpret_cast<int*>(p);
+            RPB_CUDA(cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, device_id));
+            RPB_CUDA(cudaDeviceGetAttribute(&d.cc_major, cudaDevAttrComputeCapabilityMajor, device_id));
+            if (!g_encode) {
+                void* fn = nullptr;
+                cudaDriverEntryPointQueryResult qres;
+                RPB_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
+                if (!fn || qres != cudaDriverEntryPointSuccess) {
+                    fprintf(stderr, "recpulse_b200: cuTensorMapEncodeTiled not available\n");
+                    return -1;
+                }
+                g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+            }
+            d.ready = true;
+        }
+    }
+    *out = &d;
+    return 0;
+}
+
+template <typename T>
+int noalloc_launch(void* C, const void* A, const void* B, int m, int k, int n, int dtype, NoAllocDevice* d,
+                   cudaStream_t stream) {
+    OperandPlan pa = plan_operand(A, m, k, k, 1, 1, 0, 1, 0);
+    OperandPlan pb = plan_operand(B, n, k, 1, n, 1, 0, 1, 0);
+    if (!pa.ok || !pb.ok || (reinterpret_cast<uintptr_t>(C) & 15u)) {
+        fprintf(stderr, "recpulse_b200: rp_matmul_noalloc needs 16-byte aligned pointers and k, n multiples of 8\n");
+        return -1;
+    }
+    const int BN = n <= 64 ? 64 : (n <= 128 ? 128 : 256);
+    rpb_umma::Args a;
+    memset(&a, 0, sizeof(a));
+    a.m = m; a.n = n; a.k = k; a.batch = 1; a.reduce = 1;
+    a.k_blocks = (k + rpb_umma::BLOCK_K - 1) / rpb_umma::BLOCK_K;
+    a.k_iters = a.k_blocks;
+    a.tiles_m = (m + rpb_umma::BLOCK_M - 1) / rpb_umma::BLOCK_M;
+    a.tiles_n = (n + BN - 1) / BN;
+    const long long tiles = (long long)a.tiles_m * a.tiles_n;
+    /* always split K when there is anything to split: this entry point is the scratch-using variant */
+    long long splits = d->sm_count / tiles;
+    if (splits > a.k_iters) splits = a.k_iters;
+    if (splits > 128) splits = 128;
+    if (splits < 2) splits = a.k_iters >= 2 ? 2 : 1;
+    a.iters_per_split = (int)((a.k_iters + splits - 1) / splits);
+    a.splits = (a.k_iters + a.iters_per_split - 1) / a.iters_per_split;
+    const unsigned long long need = 4ull * a.splits * m * n;
+    if (a.splits > 1 && need > RPB_NOALLOC_SCRATCH_BYTES) {
+        fprintf(stderr,
+                "recpulse_b200: rp_matmul_noalloc: %d x %d output split %d ways needs %llu bytes of scratch, the "
+                "built-in buffer holds %u; use rp_matmul_ex for this size\n", m, n, a.splits, need,
+                (unsigned)RPB_NOALLOC_SCRATCH_BYTES);
+        return -1;
+    }
+    a.total_work = tiles * a.splits;
+    a.a_batch_mul = a.a_reduce_mul = a.b_batch_mul = a.b_reduce_mul = 1;
+    a.c = C; a.c_row = n; a.c_batch = 0; a.accumulate = 0;
+    a.partial = a.splits > 1 ? d->scratch : nullptr;
+    const bool bf16 = dtype == DTYPE_BFLOAT16;
+    const uint32_t fmt = bf16 ? 1u : 0u;
+    a.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((pa.mn_major ? 1u : 0u) << 15) | ((pb.mn_major ? 1u : 0u) << 16) |
+              ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(rpb_umma::BLOCK_M >> 4) << 24);
+    a.a_desc_base = smem_desc_base(pa.mn_major);
+    a.b_desc_base = smem_desc_base(pb.mn_major);
+    a.a_kstep = pa.mn_major ? (2 * 1024) >> 4 : 32 >> 4;
+    a.b_kstep = pb.mn_major ? (2 * 1024) >> 4 : 32 >> 4;
+    a.status = d->status;
+
+    CUtensorMap ma, mb;
+    const CUtensorMapDataType dt = bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    if (encode_map(&ma, A, pa, m, k, 1, 1, rpb_umma::BLOCK_M, dt)) return -1;
+    if (encode_map(&mb, B, pb, n, k, 1, 1, BN, dt)) return -1;
+
+    /* the array keeps the previous call's contents.  Every partial element that the reduction reads
+     * is overwritten by this call's GEMM first, so only the status word has to start at zero. */
+    RPB_CUDA(cudaMemsetAsync(d->status, 0, sizeof(int), stream));
+    const int grid = (int)(a.total_work < d->sm_count ? a.total_work : d->sm_count);
+    int rc;
+    if (BN == 64) rc = launch_umma_bn<T, 64>(pa.mn_major, pb.mn_major, ma, mb, a, grid, stream);
+    else if (BN == 128) rc = launch_umma_bn<T, 128>(pa.mn_major, pb.mn_major, ma, mb, a, grid, stream);
+    else rc = launch_umma_bn<T, 256>(pa.mn_major, pb.mn_major, ma, mb, a, grid, stream);
+    if (rc) return -1;
+    if (a.splits > 1) {
+        const long long elems = (long long)m * n;
+        int rb = (int)((elems + 255) / 256); if (rb > d->sm_count * 8) rb = d->sm_count * 8;
+        rpb_simt::splitk_reduce_kernel<T, float><<<rb, 256, 0, stream>>>(a.partial, reinterpret_cast<T*>(C), a.splits, 1,
+                                                                        m, n, n, 0, 0);
+        g_launches++;
+        RPB_CUDA(cudaGetLastError());
+    }
+    t_last_kernel = a.splits > 1 ? RPB_KERNEL_UMMA_SPLITK : RPB_KERNEL_UMMA;
+    return 0;
+}
+
+}  // namespace
+
+extern "C" int rp_matmul_noalloc(void* C, const void* A, const void* B, int m, int k, int n, DType dtype,
+                                 int device_id, void* stream, int* kernel_status) {
+    if (!C || !A || !B || m <= 0 || k <= 0 || n <= 0) return -1;
+    if (dtype != DTYPE_BFLOAT16 && dtype != DTYPE_FLOAT16) {
+        fprintf(stderr, "recpulse_b200: rp_matmul_noalloc handles float16 and bfloat16 only\n");
+        return -1;
+    }
+    int prev = -1;
+    RPB_CUDA(cudaGetDevice(&prev));
+    if (prev != device_id) RPB_CUDA(cudaSetDevice(device_id));
+    NoAllocDevice* d = nullptr;
+    int rc = noalloc_setup(device_id, &d);
+    if (!rc && d->cc_major != 10) {
+        fprintf(stderr, "recpulse_b200: rp_matmul_noalloc needs a compute capability 10.x device\n");
+        rc = -1;
+    }
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    if (!rc) {
+        rc = dtype == DTYPE_BFLOAT16 ? noalloc_launch<__nv_bfloat16>(C, A, B, m, k, n, (int)dtype, d, s)
+                                     : noalloc_launch<__half>(C, A, B, m, k, n, (int)dtype, d, s);
+    }
+    if (!rc && kernel_status) {
+        /* optional: wait for the result and hand back the kernel's status word (stack destination,
+         * nothing allocated) */
+        int v = -1;
+        if (cudaMemcpyAsync(&v, d->status, sizeof(int), cudaMemcpyDeviceToHost, s) != cudaSuccess ||
+            cudaStreamSynchronize(s) != cudaSuccess) rc = -1;
+        *kernel_status = v;
+        if (!rc && v != 0) rc = -1;
+    }
+    if (prev != device_id) cudaSetDevice(prev);
+    return rc;
+}
