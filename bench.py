@@ -59,6 +59,7 @@ def parse():
     p.add_argument("--e2e-steps", type=int, default=3)
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--no-e2e", action="store_true")
+    p.add_argument("--rows", type=int, default=0, help="override the row count M of the workload (profiling cases)")
     return p.parse_args()
 
 
@@ -216,6 +217,8 @@ def main():
     n_gpus = world
 
     dtype_name, batch, m, k, n, bcast_b, shards = WORKLOADS[args.workload]
+    if args.rows:
+        batch, m = 1, args.rows
     tdtype = {"bfloat16": torch.bfloat16, "float16": torch.float16, "float32": torch.float32, "float64": torch.float64}[dtype_name]
     es = torch.empty((), dtype=tdtype).element_size()
     rows_total = batch * m            # a broadcast-batched product folds its batch into the rows of A
@@ -258,22 +261,27 @@ def main():
         time.sleep(0.3)
     launches0 = lib.rpb_launch_count()
     stream = torch.cuda.current_stream(dev)
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    resident = (2 * rows * k + 2 * k * n + 2 * rows * n) * es
+    flush = None
+    if resident < (512 << 20):
+        flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)     # > 126 MB of L2
+    step_ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
     # per-launch events for the roofline of the dominant kernel (forward GEMM of every step)
-    fwd_ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    fwd_ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
     barrier()
-    ev0.record(stream)
     for i in range(args.steps):
-        fwd_ev[i][0].record(stream)
+        if flush is not None:
+            flush.fill_(i & 1)                      # evict the operands from L2 (outside the timed events)
+        step_ev[i][0].record(stream)
         op.forward(A, out=Cc)
-        fwd_ev[i][1].record(stream)
+        fwd_ev[i].record(stream)
         op.backward(A, dC, da_out=dA, db_out=dB)
-    ev1.record(stream)
+        step_ev[i][1].record(stream)
     barrier()
-    elapsed_ms = ev0.elapsed_time(ev1)
+    elapsed_ms = sum(a.elapsed_time(b) for a, b in step_ev)
     launches = lib.rpb_launch_count() - launches0
     clocks = sampler.stop() if rank == 0 else None
-    fwd_ms = sum(a.elapsed_time(b) for a, b in fwd_ev) / args.steps
+    fwd_ms = sum(step_ev[i][0].elapsed_time(fwd_ev[i]) for i in range(args.steps)) / args.steps
     if world > 1:
         t = torch.tensor([elapsed_ms], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -345,7 +353,8 @@ def main():
             "data": "synthetic",
             "config": {"workload": args.workload, "m": rows_total, "k": k, "n": n, "rows_per_gpu": rows,
                        "parallelism": f"rows of A over {n_gpus} GPU(s), B replicated, dB all-reduced" if n_gpus > 1 else "single GPU",
-                       "l2": "inputs larger than L2, no flush", "accumulate": "fp32"},
+                       "l2": "inputs larger than L2, no flush" if flush is None else "L2 flushed (256 MB write) before every step, outside the timed events",
+                       "accumulate": "fp32"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches), "roofline": roof, "cpu_baseline": cpu,
             "pct_of_nominal_dense_peak": value / (2250.0 * n_gpus) if half else None,
         }

@@ -253,6 +253,15 @@ uint64_t smem_desc_base(bool mn_major) {
     return (lbo << 16) | (sbo << 32) | (1ull << 46) | (2ull << 61);
 }
 
+/* n-tiles per rasterisation group: the CTAs in flight (one per SM) should cover a block of C whose
+ * A row panels and B column panels are about the same number of bytes: mt*128 = nt*BN, mt*nt = #SMs */
+int raster_group(int sm_count, int bn, int tiles_n) {
+    int g = 1;
+    while ((long long)(g + 1) * (g + 1) * bn <= (long long)sm_count * rpb_umma::BLOCK_M) ++g;
+    if (g > tiles_n) g = tiles_n;
+    return g < 1 ? 1 : g;
+}
+
 template <typename T, int BN, bool A_MN, bool B_MN>
 int launch_umma_inst(const CUtensorMap& ma, const CUtensorMap& mb, const rpb_umma::Args& args, int grid,
                      cudaStream_t stream) {
@@ -302,6 +311,7 @@ int launch_umma(const RpbProblem& p, void* C, const void* A, const void* B, Devi
     a.iters_per_split = (a.k_iters + splits - 1) / splits;
     a.splits = (a.k_iters + a.iters_per_split - 1) / a.iters_per_split;
     a.total_work = tiles * a.splits;
+    a.group_n = raster_group(d->sm_count, BN, a.tiles_n);
     a.a_batch_mul = pa.batch_mul; a.a_reduce_mul = pa.reduce_mul;
     a.b_batch_mul = pb.batch_mul; a.b_reduce_mul = pb.reduce_mul;
     a.c = C; a.c_row = p.c_row; a.c_batch = p.c_batch; a.accumulate = p.accumulate;
@@ -626,6 +636,7 @@ int noalloc_launch(void* C, const void* A, const void* B, int m, int k, int n, i
         return -1;
     }
     a.total_work = tiles * a.splits;
+    a.group_n = raster_group(d->sm_count, BN, a.tiles_n);
     a.a_batch_mul = a.a_reduce_mul = a.b_batch_mul = a.b_reduce_mul = 1;
     a.c = C; a.c_row = n; a.c_batch = 0; a.accumulate = 0;
     a.partial = a.splits > 1 ? d->scratch : nullptr;

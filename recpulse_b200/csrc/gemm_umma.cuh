@@ -54,6 +54,7 @@ struct Args {
     int splits;            /* CTAs sharing one output tile along K (1 = none) */
     int iters_per_split;
     int tiles_m, tiles_n;
+    int group_n;           /* n-tiles per rasterisation group */
     long long total_work;  /* tiles_m * tiles_n * batch * splits */
     int a_batch_mul, a_reduce_mul, b_batch_mul, b_reduce_mul;   /* 0 when that operand is broadcast */
     void* c;               /* output (T), or nullptr when splits > 1 */
@@ -203,11 +204,21 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     const long long work_begin = blockIdx.x;
     const long long work_step = gridDim.x;
 
+    /* Work items are dealt round-robin, so the ~gridDim.x items in flight are consecutive indices.
+     * Within one (batch, split) the output tiles are walked in column groups of `group_n` n-tiles,
+     * n fastest: the tiles in flight then cover a near-square block of C and share their A row
+     * panels and B column panels in L2 instead of streaming all of A once per wave. */
     auto decode = [&](long long w, int& mt, int& nt, int& split, int& bz) {
-        mt = (int)(w % args.tiles_m); w /= args.tiles_m;
-        nt = (int)(w % args.tiles_n); w /= args.tiles_n;
+        const int tiles_mn = args.tiles_m * args.tiles_n;
+        const int t = (int)(w % tiles_mn); w /= tiles_mn;
         split = (int)(w % args.splits);
         bz = (int)(w / args.splits);
+        const int per_group = args.group_n * args.tiles_m;
+        const int g = t / per_group;
+        const int r = t - g * per_group;
+        const int gn = min(args.group_n, args.tiles_n - g * args.group_n);
+        mt = r / gn;
+        nt = g * args.group_n + (r - mt * gn);
     };
 
     if (warp == 0) {
