@@ -253,34 +253,57 @@ uint64_t smem_desc_base(bool mn_major) {
     return (lbo << 16) | (sbo << 32) | (1ull << 46) | (2ull << 61);
 }
 
-/* n-tiles per rasterisation group: the CTAs in flight (one per SM) should cover a block of C whose
- * A row panels and B column panels are about the same number of bytes: mt*128 = nt*BN, mt*nt = #SMs */
-int raster_group(int sm_count, int bn, int tiles_n) {
+/* n-tiles per rasterisation group: the tiles in flight (one per CTA or per CTA pair) should cover a
+ * block of C whose A row panels and B column panels hold about the same number of bytes:
+ * mt * tile_m = nt * tile_n with mt * nt = tiles in flight */
+int raster_group(int in_flight, int tile_m, int tile_n, int tiles_n) {
     int g = 1;
-    while ((long long)(g + 1) * (g + 1) * bn <= (long long)sm_count * rpb_umma::BLOCK_M) ++g;
+    while ((long long)(g + 1) * (g + 1) * tile_n <= (long long)in_flight * tile_m) ++g;
     if (g > tiles_n) g = tiles_n;
     return g < 1 ? 1 : g;
 }
 
-template <typename T, int BN, bool A_MN, bool B_MN>
+template <typename T, int BN, bool A_MN, bool B_MN, bool PAIR>
 int launch_umma_inst(const CUtensorMap& ma, const CUtensorMap& mb, const rpb_umma::Args& args, int grid,
                      cudaStream_t stream) {
     using Cfg = rpb_umma::Config<BN>;
-    auto kern = rpb_umma::gemm_kernel<T, BN, A_MN, B_MN>;
+    auto kern = rpb_umma::gemm_kernel<T, BN, A_MN, B_MN, PAIR>;
     RPB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
-    kern<<<grid, rpb_umma::NUM_THREADS, Cfg::SMEM_BYTES, stream>>>(ma, mb, args);
+    if (PAIR) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)grid); cfg.blockDim = dim3(rpb_umma::NUM_THREADS);
+        cfg.dynamicSmemBytes = Cfg::SMEM_BYTES; cfg.stream = stream;
+        cudaLaunchAttribute attr;
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+        cfg.attrs = &attr; cfg.numAttrs = 1;
+        RPB_CUDA(cudaLaunchKernelEx(&cfg, kern, ma, mb, args));
+    } else {
+        kern<<<grid, rpb_umma::NUM_THREADS, Cfg::SMEM_BYTES, stream>>>(ma, mb, args);
+    }
     g_launches++;
     RPB_CUDA(cudaGetLastError());
     return 0;
 }
 
-template <typename T, int BN>
+template <typename T, int BN, bool PAIR = false>
 int launch_umma_bn(bool a_mn, bool b_mn, const CUtensorMap& ma, const CUtensorMap& mb, const rpb_umma::Args& args,
                    int grid, cudaStream_t stream) {
-    if (!a_mn && !b_mn) return launch_umma_inst<T, BN, false, false>(ma, mb, args, grid, stream);
-    if (!a_mn && b_mn) return launch_umma_inst<T, BN, false, true>(ma, mb, args, grid, stream);
-    if (a_mn && !b_mn) return launch_umma_inst<T, BN, true, false>(ma, mb, args, grid, stream);
-    return launch_umma_inst<T, BN, true, true>(ma, mb, args, grid, stream);
+    if (!a_mn && !b_mn) return launch_umma_inst<T, BN, false, false, PAIR>(ma, mb, args, grid, stream);
+    if (!a_mn && b_mn) return launch_umma_inst<T, BN, false, true, PAIR>(ma, mb, args, grid, stream);
+    if (a_mn && !b_mn) return launch_umma_inst<T, BN, true, false, PAIR>(ma, mb, args, grid, stream);
+    return launch_umma_inst<T, BN, true, true, PAIR>(ma, mb, args, grid, stream);
+}
+
+/* Two-CTA tiles (256 x 256 per cluster) pay off once every cluster has a tile to work on. */
+bool want_pair(int m, int n, int batch, int sm_count) {
+    static int env = -1;
+    if (env < 0) { const char* e = getenv("RPB_UMMA_PAIR"); env = e ? (atoi(e) ? 1 : 0) + 1 : 0; }
+    if (env == 1) return false;
+    if (n < 256 || m < 256) return false;
+    if (env == 2) return true;
+    const long long tiles = (long long)((m + 255) / 256) * ((n + 255) / 256) * batch;
+    return tiles >= sm_count / 2;
 }
 
 /* returns 1 when the problem cannot take the tcgen05 path (caller falls back to SIMT) */
@@ -291,17 +314,21 @@ int launch_umma(const RpbProblem& p, void* C, const void* A, const void* B, Devi
     OperandPlan pb = plan_operand(B, p.n, p.k, p.b_col, p.b_row, p.batch, p.b_batch, p.reduce, p.b_reduce);
     if (!pa.ok || !pb.ok) return 1;
 
-    const int BN = p.n <= 64 ? 64 : (p.n <= 128 ? 128 : 256);
+    const bool pair = want_pair(p.m, p.n, p.batch, d->sm_count);
+    /* BN = rows of B per CTA; a pair multiplies 256 x (2 BN) tiles */
+    const int BN = pair ? 128 : (p.n <= 64 ? 64 : (p.n <= 128 ? 128 : 256));
+    const int tile_m = pair ? 2 * rpb_umma::BLOCK_M : rpb_umma::BLOCK_M;
+    const int tile_n = pair ? 2 * BN : BN;
     rpb_umma::Args a;
     memset(&a, 0, sizeof(a));
     a.m = p.m; a.n = p.n; a.k = p.k; a.batch = p.batch; a.reduce = p.reduce;
     a.k_blocks = (p.k + rpb_umma::BLOCK_K - 1) / rpb_umma::BLOCK_K;
     a.k_iters = a.k_blocks * p.reduce;
-    a.tiles_m = (p.m + rpb_umma::BLOCK_M - 1) / rpb_umma::BLOCK_M;
-    a.tiles_n = (p.n + BN - 1) / BN;
+    a.tiles_m = (p.m + tile_m - 1) / tile_m;
+    a.tiles_n = (p.n + tile_n - 1) / tile_n;
     long long tiles = (long long)a.tiles_m * a.tiles_n * p.batch;
     int splits = 1;
-    if (tiles * 2 <= d->sm_count && a.k_iters >= 8) {
+    if (!pair && tiles * 2 <= d->sm_count && a.k_iters >= 8) {
         long long want = d->sm_count / tiles;
         long long cap = a.k_iters / 4;
         splits = (int)(want < cap ? want : cap);
@@ -311,7 +338,7 @@ int launch_umma(const RpbProblem& p, void* C, const void* A, const void* B, Devi
     a.iters_per_split = (a.k_iters + splits - 1) / splits;
     a.splits = (a.k_iters + a.iters_per_split - 1) / a.iters_per_split;
     a.total_work = tiles * a.splits;
-    a.group_n = raster_group(d->sm_count, BN, a.tiles_n);
+    a.group_n = raster_group(pair ? d->sm_count / 2 : d->sm_count, tile_m, tile_n, a.tiles_n);
     a.a_batch_mul = pa.batch_mul; a.a_reduce_mul = pa.reduce_mul;
     a.b_batch_mul = pb.batch_mul; a.b_reduce_mul = pb.reduce_mul;
     a.c = C; a.c_row = p.c_row; a.c_batch = p.c_batch; a.accumulate = p.accumulate;
@@ -325,7 +352,7 @@ int launch_umma(const RpbProblem& p, void* C, const void* A, const void* B, Devi
     const bool bf16 = p.dtype == DTYPE_BFLOAT16;
     const uint32_t fmt = bf16 ? 1u : 0u;
     a.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((pa.mn_major ? 1u : 0u) << 15) | ((pb.mn_major ? 1u : 0u) << 16) |
-              ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(rpb_umma::BLOCK_M >> 4) << 24);
+              ((uint32_t)(tile_n >> 3) << 17) | ((uint32_t)(tile_m >> 4) << 24);
     a.a_desc_base = smem_desc_base(pa.mn_major);
     a.b_desc_base = smem_desc_base(pb.mn_major);
     /* advance per K=16 step: K-major 32 bytes inside the swizzle row; MN-major two 8-row groups */
@@ -340,7 +367,11 @@ int launch_umma(const RpbProblem& p, void* C, const void* A, const void* B, Devi
 
     int grid = (int)(a.total_work < d->sm_count ? a.total_work : d->sm_count);
     int rc;
-    if (BN == 64) rc = launch_umma_bn<T, 64>(pa.mn_major, pb.mn_major, ma, mb, a, grid, stream);
+    if (pair) {
+        const long long clusters = a.total_work < d->sm_count / 2 ? a.total_work : d->sm_count / 2;
+        rc = launch_umma_bn<T, 128, true>(pa.mn_major, pb.mn_major, ma, mb, a, (int)clusters * 2, stream);
+    }
+    else if (BN == 64) rc = launch_umma_bn<T, 64>(pa.mn_major, pb.mn_major, ma, mb, a, grid, stream);
     else if (BN == 128) rc = launch_umma_bn<T, 128>(pa.mn_major, pb.mn_major, ma, mb, a, grid, stream);
     else rc = launch_umma_bn<T, 256>(pa.mn_major, pb.mn_major, ma, mb, a, grid, stream);
     if (rc) return -1;
@@ -636,7 +667,7 @@ int noalloc_launch(void* C, const void* A, const void* B, int m, int k, int n, i
         return -1;
     }
     a.total_work = tiles * a.splits;
-    a.group_n = raster_group(d->sm_count, BN, a.tiles_n);
+    a.group_n = raster_group(d->sm_count, rpb_umma::BLOCK_M, BN, a.tiles_n);
     a.a_batch_mul = a.a_reduce_mul = a.b_batch_mul = a.b_reduce_mul = 1;
     a.c = C; a.c_row = n; a.c_batch = 0; a.accumulate = 0;
     a.partial = a.splits > 1 ? d->scratch : nullptr;

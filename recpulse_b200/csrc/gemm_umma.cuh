@@ -43,7 +43,6 @@ template <int BN> struct Config {
     static constexpr int STAGES_RAW = (SMEM_LIMIT - 2048) / STAGE_BYTES;
     static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
-    static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;   /* power of two: BN in {32,64,128,256} */
 };
 
 struct Args {
@@ -113,27 +112,66 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     atomicCAS(status, 0, code);
     return false;
 }
+/* PAIR: the copy may signal an mbarrier in the other CTA of the pair (cta_group::2); never multicast */
+template <bool PAIR>
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
                                             int c0, int c1, int c2, int c3) {
-    asm volatile(
-        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes"
-        " [%0], [%1, {%3, %4, %5, %6}], [%2];"
-        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+    if (PAIR) {
+        asm volatile(
+            "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+            " [%0], [%1, {%3, %4, %5, %6}], [%2];"
+            ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+    } else {
+        asm volatile(
+            "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes"
+            " [%0], [%1, {%3, %4, %5, %6}], [%2];"
+            ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+    }
+}
+/* shared::cluster address of `addr` (a shared::cta address) in CTA `rank` of this cluster */
+__device__ __forceinline__ uint32_t cluster_addr(uint32_t addr, uint32_t rank) {
+    uint32_t out;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(out) : "r"(addr), "r"(rank));
+    return out;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+}
+__device__ __forceinline__ void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+template <bool PAIR>
 __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
                                          uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+    if (PAIR) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "setp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+    } else {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "setp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+    }
 }
-/* mbarrier arrives once every tcgen05.mma issued so far by this thread has completed */
+/* The mbarrier receives one arrival once every tcgen05.mma issued so far by this thread has
+ * completed; for a pair the arrival is delivered to the same barrier in both CTAs. */
+template <bool PAIR>
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
-                 ::"r"(bar) : "memory");
+    if (PAIR) {
+        const uint16_t mask = 3;
+        asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                     ::"r"(bar), "h"(mask) : "memory");
+    } else {
+        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+                     ::"r"(bar) : "memory");
+    }
 }
 __device__ __forceinline__ void tmem_load_32(uint32_t taddr, uint32_t (&v)[32]) {
     asm volatile(
@@ -161,12 +199,23 @@ template <typename T> __device__ __forceinline__ uint32_t pack2(float lo, float 
 
 /* ------------------------------------------------------------------ kernel */
 
-template <typename T, int BN, bool A_MN, bool B_MN>
+/* PAIR = false: one CTA per output tile of 128 x BN  (tcgen05 cta_group::1).
+ * PAIR = true : a cluster of two CTAs per output tile of 256 x 2BN (cta_group::2).  CTA r of the
+ *               pair loads rows [128r, 128r+128) of the A tile and columns [BN r, BN r + BN) of the
+ *               B tile, the leader CTA (rank 0) issues M=256, N=2BN instructions that read both
+ *               CTAs' shared memory, and each CTA's tensor memory receives its own 128 rows of the
+ *               accumulator.  Each operand byte is fetched from L2 by one SM only (no multicast), so
+ *               L2 traffic per FLOP drops by a third against PAIR = false at the same MMA shape per SM. */
+template <typename T, int BN, bool A_MN, bool B_MN, bool PAIR>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
             const Args args)
 {
     using Cfg = Config<BN>;
+    constexpr int ACC_N = PAIR ? 2 * BN : BN;              /* accumulator columns = instruction N */
+    constexpr int TILE_M = PAIR ? 2 * BLOCK_M : BLOCK_M;
+    constexpr uint32_t TMEM_COLS = 2 * ACC_N;
+    static_assert(TMEM_COLS <= 512 && (TMEM_COLS & (TMEM_COLS - 1)) == 0 && TMEM_COLS >= 32, "tensor memory columns");
     extern __shared__ uint8_t smem_raw[];
     /* the swizzle pattern and the descriptors' base_offset = 0 need 1024-byte aligned tiles */
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -182,32 +231,43 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    uint32_t cta_rank = 0;
+    if (PAIR) asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(cta_rank));
+    const bool leader = cta_rank == 0;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < Cfg::STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-        for (int i = 0; i < 2; ++i) { mbar_init(tfull_bar(i), 1); mbar_init(tempty_bar(i), 128); }
+        for (int i = 0; i < 2; ++i) { mbar_init(tfull_bar(i), 1); mbar_init(tempty_bar(i), PAIR ? 256 : 128); }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                     ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)Cfg::TMEM_COLS) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        if (PAIR) {
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
+                         ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+        } else {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                         ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
     }
     tc_fence_before();
     __syncthreads();
+    if (PAIR) { __syncwarp(); cluster_sync(); }   /* the peer's barriers are initialised before anyone signals them */
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    const long long work_begin = blockIdx.x;
-    const long long work_step = gridDim.x;
+    /* one work item per CTA (PAIR = false) or per cluster (PAIR = true) */
+    const long long work_begin = PAIR ? blockIdx.x / 2 : blockIdx.x;
+    const long long work_step = PAIR ? gridDim.x / 2 : gridDim.x;
 
-    /* Work items are dealt round-robin, so the ~gridDim.x items in flight are consecutive indices.
-     * Within one (batch, split) the output tiles are walked in column groups of `group_n` n-tiles,
-     * n fastest: the tiles in flight then cover a near-square block of C and share their A row
-     * panels and B column panels in L2 instead of streaming all of A once per wave. */
+    /* Work items are dealt round-robin, so the items in flight are consecutive indices.  Within one
+     * (batch, split) the output tiles are walked in column groups of `group_n` n-tiles, n fastest:
+     * the tiles in flight then cover a near-square block of C and share their A row panels and B
+     * column panels in L2 instead of streaming all of A once per wave. */
     auto decode = [&](long long w, int& mt, int& nt, int& split, int& bz) {
         const int tiles_mn = args.tiles_m * args.tiles_n;
         const int t = (int)(w % tiles_mn); w /= tiles_mn;
@@ -229,35 +289,44 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                 int mt, nt, split, bz; decode(w, mt, nt, split, bz);
                 const int it0 = split * args.iters_per_split;
                 const int it1 = min(it0 + args.iters_per_split, args.k_iters);
+                const int row0 = mt * TILE_M + (int)cta_rank * BLOCK_M;     /* this CTA's rows of A */
+                const int col0 = nt * ACC_N + (int)cta_rank * BN;           /* this CTA's columns of B */
                 for (int it = it0; it < it1; ++it) {
                     const int r = it / args.k_blocks;
                     const int k0 = (it - r * args.k_blocks) * BLOCK_K;
                     if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, args.status, 1)) { alive = false; break; }
                     const uint32_t sa = smem_base + stage * Cfg::STAGE_BYTES;
                     const uint32_t sb = sa + Cfg::A_BYTES;
-                    mbar_expect_tx(full_bar(stage), Cfg::STAGE_BYTES);
+                    /* both CTAs of a pair report their bytes to the leader's barrier */
+                    uint32_t fb = full_bar(stage);
+                    if (PAIR) {
+                        if (leader) mbar_expect_tx(fb, 2 * Cfg::STAGE_BYTES);
+                        fb = cluster_addr(fb, 0);
+                    } else {
+                        mbar_expect_tx(fb, Cfg::STAGE_BYTES);
+                    }
                     if (!A_MN) {
-                        tma_load_4d(sa, &map_a, full_bar(stage), k0, mt * BLOCK_M, r * args.a_reduce_mul, bz * args.a_batch_mul);
+                        tma_load_4d<PAIR>(sa, &map_a, fb, k0, row0, r * args.a_reduce_mul, bz * args.a_batch_mul);
                     } else {
 #pragma unroll
                         for (int c = 0; c < BLOCK_M / 64; ++c)
-                            tma_load_4d(sa + c * (BLOCK_K * 128), &map_a, full_bar(stage), mt * BLOCK_M + c * 64, k0,
-                                        r * args.a_reduce_mul, bz * args.a_batch_mul);
+                            tma_load_4d<PAIR>(sa + c * (BLOCK_K * 128), &map_a, fb, row0 + c * 64, k0,
+                                              r * args.a_reduce_mul, bz * args.a_batch_mul);
                     }
                     if (!B_MN) {
-                        tma_load_4d(sb, &map_b, full_bar(stage), k0, nt * BN, r * args.b_reduce_mul, bz * args.b_batch_mul);
+                        tma_load_4d<PAIR>(sb, &map_b, fb, k0, col0, r * args.b_reduce_mul, bz * args.b_batch_mul);
                     } else {
 #pragma unroll
                         for (int c = 0; c < BN / 64; ++c)
-                            tma_load_4d(sb + c * (BLOCK_K * 128), &map_b, full_bar(stage), nt * BN + c * 64, k0,
-                                        r * args.b_reduce_mul, bz * args.b_batch_mul);
+                            tma_load_4d<PAIR>(sb + c * (BLOCK_K * 128), &map_b, fb, col0 + c * 64, k0,
+                                              r * args.b_reduce_mul, bz * args.b_batch_mul);
                     }
                     if (++stage == Cfg::STAGES) { stage = 0; phase ^= 1u; }
                 }
             }
         }
     } else if (warp == 1) {
-        if (lane == 0) {
+        if (lane == 0 && leader) {
             int stage = 0; uint32_t phase = 0;
             uint32_t local_tile = 0;
             bool alive = true;
@@ -269,7 +338,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                 const uint32_t acc_phase = (local_tile >> 1) & 1u;
                 if (!mbar_wait(tempty_bar(ab), acc_phase ^ 1u, abort_flag, args.status, 2)) { alive = false; break; }
                 tc_fence_after();
-                const uint32_t d_tmem = tmem_base + ab * BN;
+                const uint32_t d_tmem = tmem_base + ab * ACC_N;
                 for (int it = it0; it < it1; ++it) {
                     if (!mbar_wait(full_bar(stage), phase, abort_flag, args.status, 3)) { alive = false; break; }
                     tc_fence_after();
@@ -279,13 +348,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                     const uint64_t db = args.b_desc_base | (uint64_t)((sb >> 4) & 0x3FFFu);
 #pragma unroll
                     for (int kk = 0; kk < BLOCK_K / UMMA_K; ++kk) {
-                        umma_f16(d_tmem, da + (uint64_t)(kk * args.a_kstep), db + (uint64_t)(kk * args.b_kstep),
-                                 args.idesc, (it > it0 || kk > 0) ? 1u : 0u);
+                        umma_f16<PAIR>(d_tmem, da + (uint64_t)(kk * args.a_kstep), db + (uint64_t)(kk * args.b_kstep),
+                                       args.idesc, (it > it0 || kk > 0) ? 1u : 0u);
                     }
-                    umma_commit(empty_bar(stage));            /* frees the stage when the MMAs have read it */
+                    umma_commit<PAIR>(empty_bar(stage));      /* frees the stage (in both CTAs of a pair) */
                     if (++stage == Cfg::STAGES) { stage = 0; phase ^= 1u; }
                 }
-                if (alive) umma_commit(tfull_bar(ab));        /* accumulator complete */
+                if (alive) umma_commit<PAIR>(tfull_bar(ab));  /* accumulator complete */
             }
         }
     } else {
@@ -302,14 +371,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             if (!mbar_wait(tfull_bar(ab), acc_phase, abort_flag, args.status, 4)) { alive = false; break; }
             __syncwarp();
             tc_fence_after();
-            const int row = mt * BLOCK_M + quarter * 32 + lane;
+            const int row = mt * TILE_M + (int)cta_rank * BLOCK_M + quarter * 32 + lane;
             const bool row_ok = row < args.m;
 #pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 32) {
+            for (int c0 = 0; c0 < ACC_N; c0 += 32) {
                 uint32_t v[32];
                 __syncwarp();                 /* tcgen05.ld is warp-collective */
-                tmem_load_32(tmem_base + ab * BN + c0 + lane_field, v);
-                const int col = nt * BN + c0;
+                tmem_load_32(tmem_base + ab * ACC_N + c0 + lane_field, v);
+                const int col = nt * ACC_N + c0;
                 if (!row_ok || col >= args.n) {
                     /* nothing to store for this lane */
                 } else if (args.splits > 1) {
@@ -349,7 +418,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                 }
             }
             tc_fence_before();
-            mbar_arrive(tempty_bar(ab));
+            if (PAIR) mbar_arrive_cluster(cluster_addr(tempty_bar(ab), 0));   /* the leader owns the accumulator hand-off */
+            else mbar_arrive(tempty_bar(ab));
         }
     }
 
@@ -359,11 +429,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     }
     tc_fence_before();
     __syncthreads();
+    if (PAIR) { __syncwarp(); cluster_sync(); }   /* neither CTA's shared or tensor memory goes away under the other */
     if (warp == 1) {
         __syncwarp();
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;"
-                     ::"r"(tmem_base), "r"((uint32_t)Cfg::TMEM_COLS) : "memory");
+        if (PAIR)
+            asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+        else
+            asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
     }
 }
 
