@@ -59,6 +59,7 @@ def parse():
     p.add_argument("--e2e-steps", type=int, default=3)
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--no-e2e", action="store_true")
+    p.add_argument("--compare", action="store_true", help="also time torch.matmul (cuBLAS, warm handle) on the same step")
     p.add_argument("--rows", type=int, default=0, help="override the row count M of the workload (profiling cases)")
     return p.parse_args()
 
@@ -293,6 +294,24 @@ def main():
     ms_per_step = elapsed_ms / args.steps
     value = flops_step / (ms_per_step * 1e-3) / 1e12
 
+    # ---- optional: the same three GEMMs through torch.matmul (cuBLAS with a warm handle), for context only
+    cublas = None
+    if args.compare and world == 1:
+        def cublas_step():
+            torch.matmul(A, Bm, out=Cc); torch.matmul(A.t(), dC, out=dB); torch.matmul(dC, Bm.t(), out=dA)
+        for _ in range(3):
+            cublas_step()
+        tot = 0.0
+        for i in range(args.steps):
+            if flush is not None:
+                flush.fill_(i & 1)
+            c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            c0.record(stream); cublas_step(); c1.record(stream)
+            torch.cuda.synchronize(dev)
+            tot += c0.elapsed_time(c1)
+        cublas = {"tflops": flops_step / (tot / args.steps * 1e-3) / 1e12, "ms_per_step": tot / args.steps,
+                  "what": "torch.matmul x3 (cuBLAS, warm handle, outputs preallocated)"}
+
     # ---- end to end from pinned host buffers through the C ABI
     e2e = None
     if not args.no_e2e:
@@ -358,6 +377,8 @@ def main():
             "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches), "roofline": roof, "cpu_baseline": cpu,
             "pct_of_nominal_dense_peak": value / (2250.0 * n_gpus) if half else None,
         }
+        if cublas:
+            line["cublas_same_step"] = cublas
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

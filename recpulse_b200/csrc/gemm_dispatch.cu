@@ -246,6 +246,21 @@ int encode_map(CUtensorMap* map, const void* base, const OperandPlan& o, int mn,
     return 0;
 }
 
+/* tensor map for the epilogue's stores: [cols, rows, planes], boxes of box_cols x 32 rows (128 bytes wide) */
+int encode_store_map(CUtensorMap* map, void* base, CUtensorMapDataType dt, int esize, long long cols, long long rows,
+                     long long planes, long long row_stride, long long plane_stride, int box_cols) {
+    cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)(planes > 0 ? planes : 1)};
+    unsigned long long s1 = (unsigned long long)row_stride * esize;
+    unsigned long long s2 = dims[2] > 1 ? (unsigned long long)plane_stride * esize : ((s1 * rows + 15ull) & ~15ull);
+    if (s1 % 16 || s2 % 16 || s1 >= (1ull << 40) || s2 >= (1ull << 40)) return -1;
+    cuuint64_t strides[2] = {s1, s2};
+    cuuint32_t box[3] = {(cuuint32_t)box_cols, 32, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = g_encode(map, dt, 3, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : -1;
+}
+
 /* shared-memory matrix descriptor without the start address (128-byte swizzle, version 1) */
 uint64_t smem_desc_base(bool mn_major) {
     const uint64_t sbo = 1024 >> 4;                                   /* next group of 8 rows */
@@ -264,8 +279,8 @@ int raster_group(int in_flight, int tile_m, int tile_n, int tiles_n) {
 }
 
 template <typename T, int BN, bool A_MN, bool B_MN, bool PAIR>
-int launch_umma_inst(const CUtensorMap& ma, const CUtensorMap& mb, const rpb_umma::Args& args, int grid,
-                     cudaStream_t stream) {
+int launch_umma_inst(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, const rpb_umma::Args& args,
+                     int grid, cudaStream_t stream) {
     using Cfg = rpb_umma::Config<BN>;
     auto kern = rpb_umma::gemm_kernel<T, BN, A_MN, B_MN, PAIR>;
     RPB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
@@ -277,9 +292,9 @@ int launch_umma_inst(const CUtensorMap& ma, const CUtensorMap& mb, const rpb_umm
         attr.id = cudaLaunchAttributeClusterDimension;
         attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
         cfg.attrs = &attr; cfg.numAttrs = 1;
-        RPB_CUDA(cudaLaunchKernelEx(&cfg, kern, ma, mb, args));
+        RPB_CUDA(cudaLaunchKernelEx(&cfg, kern, ma, mb, mc, args));
     } else {
-        kern<<<grid, rpb_umma::NUM_THREADS, Cfg::SMEM_BYTES, stream>>>(ma, mb, args);
+        kern<<<grid, rpb_umma::NUM_THREADS, Cfg::SMEM_BYTES, stream>>>(ma, mb, mc, args);
     }
     g_launches++;
     RPB_CUDA(cudaGetLastError());
@@ -287,12 +302,12 @@ int launch_umma_inst(const CUtensorMap& ma, const CUtensorMap& mb, const rpb_umm
 }
 
 template <typename T, int BN, bool PAIR = false>
-int launch_umma_bn(bool a_mn, bool b_mn, const CUtensorMap& ma, const CUtensorMap& mb, const rpb_umma::Args& args,
-                   int grid, cudaStream_t stream) {
-    if (!a_mn && !b_mn) return launch_umma_inst<T, BN, false, false, PAIR>(ma, mb, args, grid, stream);
-    if (!a_mn && b_mn) return launch_umma_inst<T, BN, false, true, PAIR>(ma, mb, args, grid, stream);
-    if (a_mn && !b_mn) return launch_umma_inst<T, BN, true, false, PAIR>(ma, mb, args, grid, stream);
-    return launch_umma_inst<T, BN, true, true, PAIR>(ma, mb, args, grid, stream);
+int launch_umma_bn(bool a_mn, bool b_mn, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc,
+                   const rpb_umma::Args& args, int grid, cudaStream_t stream) {
+    if (!a_mn && !b_mn) return launch_umma_inst<T, BN, false, false, PAIR>(ma, mb, mc, args, grid, stream);
+    if (!a_mn && b_mn) return launch_umma_inst<T, BN, false, true, PAIR>(ma, mb, mc, args, grid, stream);
+    if (a_mn && !b_mn) return launch_umma_inst<T, BN, true, false, PAIR>(ma, mb, mc, args, grid, stream);
+    return launch_umma_inst<T, BN, true, true, PAIR>(ma, mb, mc, args, grid, stream);
 }
 
 /* Two-CTA tiles (256 x 256 per cluster) pay off once every cluster has a tile to work on. */
@@ -365,15 +380,29 @@ int launch_umma(const RpbProblem& p, void* C, const void* A, const void* B, Devi
     if (encode_map(&ma, A, pa, p.m, p.k, p.batch, p.reduce, rpb_umma::BLOCK_M, dt)) return -1;
     if (encode_map(&mb, B, pb, p.n, p.k, p.batch, p.reduce, BN, dt)) return -1;
 
+    /* output through shared memory + TMA store when the destination is TMA-addressable; the register
+     * epilogue handles "C += AB" and odd alignments */
+    CUtensorMap mc = ma;
+    a.tma_store = 0;
+    if (a.splits > 1) {
+        if (p.n % 4 == 0 &&
+            encode_store_map(&mc, a.partial, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, p.n, p.m, (long long)a.splits * p.batch,
+                             p.n, (long long)p.m * p.n, 32) == 0)
+            a.tma_store = 1;
+    } else if (!p.accumulate && (reinterpret_cast<uintptr_t>(C) & 15u) == 0 && p.c_row % 8 == 0 &&
+               (p.batch == 1 || p.c_batch % 8 == 0)) {
+        if (encode_store_map(&mc, C, dt, 2, p.n, p.m, p.batch, p.c_row, p.c_batch, 64) == 0) a.tma_store = 1;
+    }
+
     int grid = (int)(a.total_work < d->sm_count ? a.total_work : d->sm_count);
     int rc;
     if (pair) {
         const long long clusters = a.total_work < d->sm_count / 2 ? a.total_work : d->sm_count / 2;
-        rc = launch_umma_bn<T, 128, true>(pa.mn_major, pb.mn_major, ma, mb, a, (int)clusters * 2, stream);
+        rc = launch_umma_bn<T, 128, true>(pa.mn_major, pb.mn_major, ma, mb, mc, a, (int)clusters * 2, stream);
     }
-    else if (BN == 64) rc = launch_umma_bn<T, 64>(pa.mn_major, pb.mn_major, ma, mb, a, grid, stream);
-    else if (BN == 128) rc = launch_umma_bn<T, 128>(pa.mn_major, pb.mn_major, ma, mb, a, grid, stream);
-    else rc = launch_umma_bn<T, 256>(pa.mn_major, pb.mn_major, ma, mb, a, grid, stream);
+    else if (BN == 64) rc = launch_umma_bn<T, 64>(pa.mn_major, pb.mn_major, ma, mb, mc, a, grid, stream);
+    else if (BN == 128) rc = launch_umma_bn<T, 128>(pa.mn_major, pb.mn_major, ma, mb, mc, a, grid, stream);
+    else rc = launch_umma_bn<T, 256>(pa.mn_major, pb.mn_major, ma, mb, mc, a, grid, stream);
     if (rc) return -1;
     if (a.splits > 1) {
         long long elems = (long long)p.batch * p.m * p.n;
@@ -689,11 +718,12 @@ int noalloc_launch(void* C, const void* A, const void* B, int m, int k, int n, i
     /* the array keeps the previous call's contents.  Every partial element that the reduction reads
      * is overwritten by this call's GEMM first, so only the status word has to start at zero. */
     RPB_CUDA(cudaMemsetAsync(d->status, 0, sizeof(int), stream));
+    const CUtensorMap mc = ma;          /* register epilogue (tma_store = 0): the third map is not read */
     const int grid = (int)(a.total_work < d->sm_count ? a.total_work : d->sm_count);
     int rc;
-    if (BN == 64) rc = launch_umma_bn<T, 64>(pa.mn_major, pb.mn_major, ma, mb, a, grid, stream);
-    else if (BN == 128) rc = launch_umma_bn<T, 128>(pa.mn_major, pb.mn_major, ma, mb, a, grid, stream);
-    else rc = launch_umma_bn<T, 256>(pa.mn_major, pb.mn_major, ma, mb, a, grid, stream);
+    if (BN == 64) rc = launch_umma_bn<T, 64>(pa.mn_major, pb.mn_major, ma, mb, mc, a, grid, stream);
+    else if (BN == 128) rc = launch_umma_bn<T, 128>(pa.mn_major, pb.mn_major, ma, mb, mc, a, grid, stream);
+    else rc = launch_umma_bn<T, 256>(pa.mn_major, pb.mn_major, ma, mb, mc, a, grid, stream);
     if (rc) return -1;
     if (a.splits > 1) {
         const long long elems = (long long)m * n;

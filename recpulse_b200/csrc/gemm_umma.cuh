@@ -40,9 +40,12 @@ template <int BN> struct Config {
     static constexpr int A_BYTES = BLOCK_M * BLOCK_K * 2;
     static constexpr int B_BYTES = BN * BLOCK_K * 2;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-    static constexpr int STAGES_RAW = (SMEM_LIMIT - 2048) / STAGE_BYTES;
+    /* epilogue staging for TMA stores: 4 warps x 2 buffers x (32 rows x 128 bytes) */
+    static constexpr int STORE_BUF_BYTES = 32 * 128;
+    static constexpr int STORE_BYTES = 4 * 2 * STORE_BUF_BYTES;
+    static constexpr int STAGES_RAW = (SMEM_LIMIT - 2048 - STORE_BYTES) / STAGE_BYTES;
     static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + STORE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
 };
 
 struct Args {
@@ -59,6 +62,7 @@ struct Args {
     void* c;               /* output (T), or nullptr when splits > 1 */
     long long c_row, c_batch;
     int accumulate;
+    int tma_store;         /* 1: the epilogue writes through shared memory + TMA store (map_c), 0: register stores */
     float* partial;        /* [splits][batch][m][n] fp32 when splits > 1 */
     uint32_t idesc;        /* tcgen05 instruction descriptor */
     uint64_t a_desc_base, b_desc_base;   /* shared-memory descriptors without start address */
@@ -127,6 +131,19 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map
             " [%0], [%1, {%3, %4, %5, %6}], [%2];"
             ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
     }
+}
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, uint32_t src, int c0, int c1, int c2) {
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+                 ::"l"(map), "r"(src), "r"(c0), "r"(c1), "r"(c2) : "memory");
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+/* at most `N` of this thread's bulk store groups may still be reading shared memory */
+template <int N> __device__ __forceinline__ void tma_store_wait_read() {
+    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
 /* shared::cluster address of `addr` (a shared::cta address) in CTA `rank` of this cluster */
 __device__ __forceinline__ uint32_t cluster_addr(uint32_t addr, uint32_t rank) {
@@ -209,7 +226,7 @@ template <typename T> __device__ __forceinline__ uint32_t pack2(float lo, float 
 template <typename T, int BN, bool A_MN, bool B_MN, bool PAIR>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-            const Args args)
+            const __grid_constant__ CUtensorMap map_c, const Args args)
 {
     using Cfg = Config<BN>;
     constexpr int ACC_N = PAIR ? 2 * BN : BN;              /* accumulator columns = instruction N */
@@ -220,13 +237,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     /* the swizzle pattern and the descriptors' base_offset = 0 need 1024-byte aligned tiles */
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
-    const uint32_t bar_base = smem_base + Cfg::STAGES * Cfg::STAGE_BYTES;
+    const uint32_t store_base = smem_base + Cfg::STAGES * Cfg::STAGE_BYTES;       /* 1024-aligned */
+    const uint32_t bar_base = store_base + Cfg::STORE_BYTES;
     /* barrier words: full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], then tmem ptr, abort flag */
     auto full_bar = [&](int s) { return bar_base + 8u * s; };
     auto empty_bar = [&](int s) { return bar_base + 8u * (Cfg::STAGES + s); };
     auto tfull_bar = [&](int i) { return bar_base + 8u * (2 * Cfg::STAGES + i); };
     auto tempty_bar = [&](int i) { return bar_base + 8u * (2 * Cfg::STAGES + 2 + i); };
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + Cfg::STAGES * Cfg::STAGE_BYTES + 8 * (2 * Cfg::STAGES + 4));
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + Cfg::STAGES * Cfg::STAGE_BYTES + Cfg::STORE_BYTES +
+                                                      8 * (2 * Cfg::STAGES + 4));
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5;
@@ -242,6 +261,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
+        if (args.tma_store) asm volatile("prefetch.tensormap [%0];" ::"l"(&map_c) : "memory");
     }
     if (warp == 1) {
         if (PAIR) {
@@ -373,6 +393,59 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             tc_fence_after();
             const int row = mt * TILE_M + (int)cta_rank * BLOCK_M + quarter * 32 + lane;
             const bool row_ok = row < args.m;
+            if (args.tma_store) {
+                /* Each warp stages 32 rows x 128 bytes in the 128-byte swizzle the store's tensor map
+                 * expects (16-byte chunk c of row r at position c ^ (r & 7)) and one lane hands the box to
+                 * the TMA engine, which writes whole lines and clips rows >= M / columns >= N itself.
+                 * Two buffers per warp: staging of chunk j+1 overlaps the store of chunk j. */
+                const int row_warp = mt * TILE_M + (int)cta_rank * BLOCK_M + quarter * 32;
+                const uint32_t buf0 = store_base + (uint32_t)quarter * 2u * Cfg::STORE_BUF_BYTES;
+                const uint32_t my_row = (uint32_t)lane * 128u;
+                const uint32_t sw = (uint32_t)lane & 7u;
+                const bool partial_out = args.splits > 1;
+                const int cols_per_box = partial_out ? 32 : 64;             /* 128 bytes of fp32 or of T */
+                const int zc = partial_out ? split * args.batch + bz : bz;
+                uint32_t parity = 0;
+#pragma unroll 1
+                for (int c0 = 0; c0 < ACC_N; c0 += cols_per_box) {
+                    const int col = nt * ACC_N + c0;
+                    uint32_t v[32], v2[32];
+                    __syncwarp();
+                    tmem_load_32(tmem_base + ab * ACC_N + c0 + lane_field, v);
+                    if (!partial_out) tmem_load_32(tmem_base + ab * ACC_N + c0 + 32 + lane_field, v2);
+                    if (col >= args.n || row_warp >= args.m) continue;      /* warp-uniform */
+                    const uint32_t buf = buf0 + parity * Cfg::STORE_BUF_BYTES;
+                    if (lane == 0) tma_store_wait_read<1>();                /* the store that last used `buf` has read it */
+                    __syncwarp();
+                    if (partial_out) {
+#pragma unroll
+                        for (uint32_t c = 0; c < 8; ++c)
+                            st_shared_v4(buf + my_row + ((c ^ sw) << 4), v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+                    } else {
+#pragma unroll
+                        for (uint32_t c = 0; c < 4; ++c) {
+                            st_shared_v4(buf + my_row + ((c ^ sw) << 4),
+                                         pack2<T>(__uint_as_float(v[8 * c]), __uint_as_float(v[8 * c + 1])),
+                                         pack2<T>(__uint_as_float(v[8 * c + 2]), __uint_as_float(v[8 * c + 3])),
+                                         pack2<T>(__uint_as_float(v[8 * c + 4]), __uint_as_float(v[8 * c + 5])),
+                                         pack2<T>(__uint_as_float(v[8 * c + 6]), __uint_as_float(v[8 * c + 7])));
+                            st_shared_v4(buf + my_row + (((c + 4) ^ sw) << 4),
+                                         pack2<T>(__uint_as_float(v2[8 * c]), __uint_as_float(v2[8 * c + 1])),
+                                         pack2<T>(__uint_as_float(v2[8 * c + 2]), __uint_as_float(v2[8 * c + 3])),
+                                         pack2<T>(__uint_as_float(v2[8 * c + 4]), __uint_as_float(v2[8 * c + 5])),
+                                         pack2<T>(__uint_as_float(v2[8 * c + 6]), __uint_as_float(v2[8 * c + 7])));
+                        }
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   /* generic writes -> async proxy */
+                    __syncwarp();
+                    if (lane == 0) tma_store_3d(&map_c, buf, col, row_warp, zc);
+                    parity ^= 1u;
+                }
+                tc_fence_before();
+                if (PAIR) mbar_arrive_cluster(cluster_addr(tempty_bar(ab), 0));
+                else mbar_arrive(tempty_bar(ab));
+                continue;
+            }
 #pragma unroll 1
             for (int c0 = 0; c0 < ACC_N; c0 += 32) {
                 uint32_t v[32];
@@ -422,6 +495,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             else mbar_arrive(tempty_bar(ab));
         }
     }
+
+    if (warp >= 2 && lane == 0 && args.tma_store) tma_store_wait_all();   /* staged rows have left shared memory */
 
     /* teardown: if a wait gave up, let copies that are still in flight land first */
     if (*abort_flag) {
