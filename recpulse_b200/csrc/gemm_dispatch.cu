@@ -13,6 +13,7 @@
 #include <dlfcn.h>
 #include <link.h>
 
+#include "gemm_dmma.cuh"
 #include "gemm_simt.cuh"
 #include "gemm_umma.cuh"
 #include "rpb_common.h"
@@ -168,6 +169,75 @@ int launch_simt_cfg(const RpbProblem& p, void* C, const void* A, const void* B, 
     }
     RPB_CUDA(cudaGetLastError());
     t_last_kernel = RPB_KERNEL_SIMT;
+    return 0;
+}
+
+/* ------------------------------------------------------------------ float64 tensor-core launch */
+
+template <bool A_MN, bool B_MN>
+int launch_dmma_inst(const rpb_simt::Args& a, long long blocks, cudaStream_t stream) {
+    auto kern = rpb_dmma::gemm_kernel<A_MN, B_MN>;
+    RPB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, rpb_dmma::SMEM_BYTES));
+    kern<<<(unsigned)blocks, rpb_dmma::THREADS, rpb_dmma::SMEM_BYTES, stream>>>(a);
+    g_launches++;
+    return 0;
+}
+
+/* returns 1 when the operands do not meet the kernel's layout requirements */
+int launch_dmma(const RpbProblem& p, void* C, const void* A, const void* B, DeviceState* d, cudaStream_t stream) {
+    auto even = [](long long s) { return s > 0 && s % 2 == 0; };
+    auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15u) == 0; };
+    bool a_mn, b_mn;
+    if (p.a_col == 1 && (p.m == 1 || even(p.a_row))) a_mn = false;
+    else if (p.a_row == 1 && (p.k == 1 || even(p.a_col))) a_mn = true;
+    else return 1;
+    if (p.b_col == 1 && (p.k == 1 || even(p.b_row))) b_mn = true;
+    else if (p.b_row == 1 && (p.n == 1 || even(p.b_col))) b_mn = false;
+    else return 1;
+    if (!al16(A) || !al16(B)) return 1;
+    if ((p.batch > 1 && (p.a_batch % 2 || p.b_batch % 2)) || (p.reduce > 1 && (p.a_reduce % 2 || p.b_reduce % 2))) return 1;
+    if ((long long)p.m * p.n < 64 * 64) return 1;             /* tiny outputs: the small-tile kernel */
+
+    rpb_simt::Args a;
+    a.a = A; a.b = B; a.c = C;
+    a.m = p.m; a.n = p.n; a.k = p.k; a.batch = p.batch; a.reduce = p.reduce;
+    a.a_row = p.a_row; a.a_col = p.a_col; a.a_batch = p.a_batch; a.a_reduce = p.a_reduce;
+    a.b_row = p.b_row; a.b_col = p.b_col; a.b_batch = p.b_batch; a.b_reduce = p.b_reduce;
+    a.c_row = p.c_row; a.c_batch = p.c_batch; a.accumulate = p.accumulate;
+    a.tiles_m = (p.m + rpb_dmma::BM - 1) / rpb_dmma::BM; a.tiles_n = (p.n + rpb_dmma::BN - 1) / rpb_dmma::BN;
+    a.k_blocks = (p.k + rpb_dmma::BK - 1) / rpb_dmma::BK;
+    a.k_iters = a.k_blocks * p.reduce;
+    const long long tiles = (long long)a.tiles_m * a.tiles_n * p.batch;
+    int splits = 1;
+    if (tiles * 2 <= d->sm_count && a.k_iters >= 16) {
+        long long want = d->sm_count / tiles, cap = a.k_iters / 8;
+        splits = (int)(want < cap ? want : cap);
+        if (splits > 64) splits = 64;
+        if (splits < 1) splits = 1;
+    }
+    a.iters_per_split = (a.k_iters + splits - 1) / splits;
+    a.splits = (a.k_iters + a.iters_per_split - 1) / a.iters_per_split;
+    a.partial = nullptr;
+    const long long blocks = tiles * a.splits;
+    if (blocks > 0x7fffffffLL) return 1;
+    if (a.splits > 1 && get_scratch(d, sizeof(double) * (size_t)a.splits * p.batch * p.m * p.n, stream, &a.partial)) return -1;
+    int rc;
+    if (!a_mn && !b_mn) rc = launch_dmma_inst<false, false>(a, blocks, stream);
+    else if (!a_mn && b_mn) rc = launch_dmma_inst<false, true>(a, blocks, stream);
+    else if (a_mn && !b_mn) rc = launch_dmma_inst<true, false>(a, blocks, stream);
+    else rc = launch_dmma_inst<true, true>(a, blocks, stream);
+    if (rc) return -1;
+    if (a.splits > 1) {
+        long long elems = (long long)p.batch * p.m * p.n;
+        int rb = (int)((elems + 255) / 256); if (rb > d->sm_count * 8) rb = d->sm_count * 8;
+        rpb_simt::splitk_reduce_kernel<double, double><<<rb, 256, 0, stream>>>(
+            reinterpret_cast<const double*>(a.partial), reinterpret_cast<double*>(C), a.splits, p.batch, p.m, p.n,
+            p.c_row, p.c_batch, p.accumulate);
+        g_launches++;
+        if (release_scratch(d, stream)) return -1;
+    }
+    RPB_CUDA(cudaGetLastError());
+    t_last_kernel = RPB_KERNEL_DMMA;
     return 0;
 }
 
@@ -464,7 +534,13 @@ int run_gemm(const RpbProblem& in, void* C, const void* A, const void* B, int de
     }
     switch (p.dtype) {
         case DTYPE_FLOAT32: return launch_simt<float, float>(p, C, A, B, d, stream);
-        case DTYPE_FLOAT64: return launch_simt<double, double>(p, C, A, B, d, stream);
+        case DTYPE_FLOAT64: {
+            if (forced != RPB_KERNEL_SIMT) {
+                int rc = launch_dmma(p, C, A, B, d, stream);
+                if (rc <= 0) return rc;
+            }
+            return launch_simt<double, double>(p, C, A, B, d, stream);
+        }
         case DTYPE_FLOAT16: return launch_simt<__half, float>(p, C, A, B, d, stream);
         case DTYPE_BFLOAT16: return launch_simt<__nv_bfloat16, float>(p, C, A, B, d, stream);
     }

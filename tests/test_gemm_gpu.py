@@ -100,7 +100,24 @@ def test_simt_large_tile_and_splitk(lib, dtype):
     rng = np.random.default_rng(5)
     for (m, k, n) in [(512, 96, 640), (64, 2048, 64), (700, 300, 520)]:
         a = rand_operand(rng, (1, 1, m, k), dtype); b = rand_operand(rng, (1, 1, k, n), dtype, scale=1 / np.sqrt(k))
-        run_ex(lib, dtype, a, b, expect=(_lib.KERNEL_SIMT,))
+        run_ex(lib, dtype, a, b, expect=(_lib.KERNEL_SIMT, _lib.KERNEL_DMMA))
+
+
+@pytest.mark.parametrize("layout", [(False, False), (True, False), (False, True), (True, True)])
+def test_fp64_tensor_core_kernel(lib, layout):
+    """mma.sync f64 kernel: all operand orientations, ragged and odd extents, long K (split over CTAs),
+    batches, summed problems and the accumulate epilogue.  Leading dimensions stay even (16 bytes)."""
+    ta, tb = layout
+    dtype = "float64"
+    rng = np.random.default_rng(43)
+    for (m, k, n) in [(128, 16, 128), (256, 64, 384), (100, 130, 70), (129, 35, 131), (64, 2048, 64), (300, 17, 260)]:
+        a = rand_operand(rng, (1, 1, m, k), dtype, dist="uniform"); b = rand_operand(rng, (1, 1, k, n), dtype, dist="uniform")
+        pa = (m % 2) if ta else (k % 2)          # make the stored leading dimension even
+        pb = (k % 2) if tb else (n % 2)
+        run_ex(lib, dtype, a, b, ta=ta, tb=tb, pad_a=pa, pad_b=pb, expect=(_lib.KERNEL_DMMA,))
+    a = rand_operand(rng, (3, 2, 96, 40), dtype); b = rand_operand(rng, (3, 2, 40, 72), dtype)
+    run_ex(lib, dtype, a, b, ta=ta, tb=tb, expect=(_lib.KERNEL_DMMA,))
+    run_ex(lib, dtype, a, b, ta=ta, tb=tb, c_init=rand_operand(rng, (3, 96, 72), dtype), expect=(_lib.KERNEL_DMMA,))
 
 
 @pytest.mark.parametrize("dtype", ["float32", "float64", "float16", "bfloat16"])
