@@ -164,7 +164,8 @@ enum {                              /* values of rpb_last_kernel()              
     RPB_KERNEL_SIMT = 1,            /* FFMA / DFMA tiled kernel                              */
     RPB_KERNEL_UMMA = 2,            /* tcgen05 + TMEM + TMA kernel (f16 / bf16)              */
     RPB_KERNEL_UMMA_SPLITK = 3,     /* the same with K split over CTAs + reduction pass      */
-    RPB_KERNEL_DMMA = 4             /* float64 tensor-core kernel (mma.sync m16n8k8 f64)     */
+    RPB_KERNEL_DMMA = 4,            /* float64 tensor-core kernel (mma.sync m16n8k8 f64)     */
+    RPB_KERNEL_TF32X3 = 5           /* float32 on tensor cores, 3xTF32 split (mma.sync tf32) */
 };
 /* Which kernel family the last GEMM issued by the calling thread used. */
 int rpb_last_kernel(void);

@@ -15,7 +15,7 @@ DTYPE_CODE = {"float32": F32, "float64": F64, "float16": F16, "bfloat16": BF16}
 DTYPE_NAME = {v: k for k, v in DTYPE_CODE.items()}
 DTYPE_SIZE = {F32: 4, F64: 8, F16: 2, BF16: 2}
 
-KERNEL_NONE, KERNEL_SIMT, KERNEL_UMMA, KERNEL_UMMA_SPLITK, KERNEL_DMMA = 0, 1, 2, 3, 4
+KERNEL_NONE, KERNEL_SIMT, KERNEL_UMMA, KERNEL_UMMA_SPLITK, KERNEL_DMMA, KERNEL_TF32X3 = 0, 1, 2, 3, 4, 5
 
 
 class Meta(C.Structure):

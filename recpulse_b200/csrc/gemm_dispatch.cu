@@ -15,6 +15,7 @@
 
 #include "gemm_dmma.cuh"
 #include "gemm_simt.cuh"
+#include "gemm_tf32x3.cuh"
 #include "gemm_umma.cuh"
 #include "rpb_common.h"
 
@@ -159,11 +160,8 @@ int launch_simt_cfg(const RpbProblem& p, void* C, const void* A, const void* B, 
     rpb_simt::gemm_kernel<T, Acc, BM, BN, BK, TM, TN><<<(unsigned)blocks, NT, 0, stream>>>(a);
     g_launches++;
     if (a.splits > 1) {
-        long long elems = (long long)p.batch * p.m * p.n;
-        int rb = (int)((elems + 255) / 256); if (rb > d->sm_count * 8) rb = d->sm_count * 8;
-        rpb_simt::splitk_reduce_kernel<T, Acc><<<rb, 256, 0, stream>>>(
-            reinterpret_cast<const Acc*>(a.partial), reinterpret_cast<T*>(C), a.splits, p.batch, p.m, p.n,
-            p.c_row, p.c_batch, p.accumulate);
+        rpb_simt::launch_splitk_reduce<T, Acc>(reinterpret_cast<const Acc*>(a.partial), reinterpret_cast<T*>(C), a.splits,
+                                               p.batch, p.m, p.n, p.c_row, p.c_batch, p.accumulate, d->sm_count, stream);
         g_launches++;
         if (release_scratch(d, stream)) return -1;
     }
@@ -228,17 +226,90 @@ int launch_dmma(const RpbProblem& p, void* C, const void* A, const void* B, Devi
     else rc = launch_dmma_inst<true, true>(a, blocks, stream);
     if (rc) return -1;
     if (a.splits > 1) {
-        long long elems = (long long)p.batch * p.m * p.n;
-        int rb = (int)((elems + 255) / 256); if (rb > d->sm_count * 8) rb = d->sm_count * 8;
-        rpb_simt::splitk_reduce_kernel<double, double><<<rb, 256, 0, stream>>>(
-            reinterpret_cast<const double*>(a.partial), reinterpret_cast<double*>(C), a.splits, p.batch, p.m, p.n,
-            p.c_row, p.c_batch, p.accumulate);
+        rpb_simt::launch_splitk_reduce<double, double>(reinterpret_cast<const double*>(a.partial), reinterpret_cast<double*>(C),
+                                                       a.splits, p.batch, p.m, p.n, p.c_row, p.c_batch, p.accumulate,
+                                                       d->sm_count, stream);
         g_launches++;
         if (release_scratch(d, stream)) return -1;
     }
     RPB_CUDA(cudaGetLastError());
     t_last_kernel = RPB_KERNEL_DMMA;
     return 0;
+}
+
+/* ------------------------------------------------------------------ float32 3xTF32 launch */
+
+template <int BM, int BN, int WM, int WN, bool A_MN, bool B_MN>
+int launch_tf32_inst(const rpb_simt::Args& a, long long blocks, cudaStream_t stream) {
+    auto kern = rpb_tf32::gemm_kernel<BM, BN, WM, WN, A_MN, B_MN>;
+    constexpr int smem = rpb_tf32::Cfg<BM, BN>::SMEM_BYTES;
+    RPB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    kern<<<(unsigned)blocks, WM * WN * 32, smem, stream>>>(a);
+    g_launches++;
+    return 0;
+}
+
+template <int BM, int BN, int WM, int WN>
+int launch_tf32_cfg(const RpbProblem& p, void* C, const void* A, const void* B, bool a_mn, bool b_mn, DeviceState* d,
+                    cudaStream_t stream) {
+    rpb_simt::Args a;
+    a.a = A; a.b = B; a.c = C;
+    a.m = p.m; a.n = p.n; a.k = p.k; a.batch = p.batch; a.reduce = p.reduce;
+    a.a_row = p.a_row; a.a_col = p.a_col; a.a_batch = p.a_batch; a.a_reduce = p.a_reduce;
+    a.b_row = p.b_row; a.b_col = p.b_col; a.b_batch = p.b_batch; a.b_reduce = p.b_reduce;
+    a.c_row = p.c_row; a.c_batch = p.c_batch; a.accumulate = p.accumulate;
+    a.tiles_m = (p.m + BM - 1) / BM; a.tiles_n = (p.n + BN - 1) / BN;
+    a.k_blocks = (p.k + rpb_tf32::BK - 1) / rpb_tf32::BK;
+    a.k_iters = a.k_blocks * p.reduce;
+    const long long tiles = (long long)a.tiles_m * a.tiles_n * p.batch;
+    int splits = 1;
+    if (tiles * 2 <= d->sm_count && a.k_iters >= 8) {
+        long long want = d->sm_count / tiles, cap = a.k_iters / 4;
+        splits = (int)(want < cap ? want : cap);
+        if (splits > 64) splits = 64;
+        if (splits < 1) splits = 1;
+    }
+    a.iters_per_split = (a.k_iters + splits - 1) / splits;
+    a.splits = (a.k_iters + a.iters_per_split - 1) / a.iters_per_split;
+    a.partial = nullptr;
+    const long long blocks = tiles * a.splits;
+    if (blocks > 0x7fffffffLL) return 1;
+    if (a.splits > 1 && get_scratch(d, sizeof(float) * (size_t)a.splits * p.batch * p.m * p.n, stream, &a.partial)) return -1;
+    int rc;
+    if (!a_mn && !b_mn) rc = launch_tf32_inst<BM, BN, WM, WN, false, false>(a, blocks, stream);
+    else if (!a_mn && b_mn) rc = launch_tf32_inst<BM, BN, WM, WN, false, true>(a, blocks, stream);
+    else if (a_mn && !b_mn) rc = launch_tf32_inst<BM, BN, WM, WN, true, false>(a, blocks, stream);
+    else rc = launch_tf32_inst<BM, BN, WM, WN, true, true>(a, blocks, stream);
+    if (rc) return -1;
+    if (a.splits > 1) {
+        rpb_simt::launch_splitk_reduce<float, float>(reinterpret_cast<const float*>(a.partial), reinterpret_cast<float*>(C),
+                                                     a.splits, p.batch, p.m, p.n, p.c_row, p.c_batch, p.accumulate,
+                                                     d->sm_count, stream);
+        g_launches++;
+        if (release_scratch(d, stream)) return -1;
+    }
+    RPB_CUDA(cudaGetLastError());
+    t_last_kernel = RPB_KERNEL_TF32X3;
+    return 0;
+}
+
+/* returns 1 when the operands do not meet the kernel's layout requirements */
+int launch_tf32(const RpbProblem& p, void* C, const void* A, const void* B, DeviceState* d, cudaStream_t stream) {
+    auto mult4 = [](long long s) { return s > 0 && s % 4 == 0; };
+    auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15u) == 0; };
+    bool a_mn, b_mn;
+    if (p.a_col == 1 && (p.m == 1 || mult4(p.a_row))) a_mn = false;
+    else if (p.a_row == 1 && (p.k == 1 || mult4(p.a_col))) a_mn = true;
+    else return 1;
+    if (p.b_col == 1 && (p.k == 1 || mult4(p.b_row))) b_mn = true;
+    else if (p.b_row == 1 && (p.n == 1 || mult4(p.b_col))) b_mn = false;
+    else return 1;
+    if (!al16(A) || !al16(B)) return 1;
+    if ((p.batch > 1 && (p.a_batch % 4 || p.b_batch % 4)) || (p.reduce > 1 && (p.a_reduce % 4 || p.b_reduce % 4))) return 1;
+    if ((long long)p.m * p.n < 32 * 32) return 1;
+    const long long big_tiles = (long long)((p.m + 127) / 128) * ((p.n + 127) / 128) * p.batch;
+    if (big_tiles >= d->sm_count / 2) return launch_tf32_cfg<128, 128, 2, 4>(p, C, A, B, a_mn, b_mn, d, stream);
+    return launch_tf32_cfg<64, 64, 2, 2>(p, C, A, B, a_mn, b_mn, d, stream);
 }
 
 template <typename T, typename Acc>
@@ -475,10 +546,8 @@ int launch_umma(const RpbProblem& p, void* C, const void* A, const void* B, Devi
     else rc = launch_umma_bn<T, 256>(pa.mn_major, pb.mn_major, ma, mb, mc, a, grid, stream);
     if (rc) return -1;
     if (a.splits > 1) {
-        long long elems = (long long)p.batch * p.m * p.n;
-        int rb = (int)((elems + 255) / 256); if (rb > d->sm_count * 8) rb = d->sm_count * 8;
-        rpb_simt::splitk_reduce_kernel<T, float><<<rb, 256, 0, stream>>>(a.partial, reinterpret_cast<T*>(C), a.splits,
-                                                                        p.batch, p.m, p.n, p.c_row, p.c_batch, p.accumulate);
+        rpb_simt::launch_splitk_reduce<T, float>(a.partial, reinterpret_cast<T*>(C), a.splits, p.batch, p.m, p.n, p.c_row,
+                                                 p.c_batch, p.accumulate, d->sm_count, stream);
         g_launches++;
         RPB_CUDA(cudaGetLastError());
         if (release_scratch(d, stream)) return -1;
@@ -533,7 +602,13 @@ int run_gemm(const RpbProblem& in, void* C, const void* A, const void* B, int de
         }
     }
     switch (p.dtype) {
-        case DTYPE_FLOAT32: return launch_simt<float, float>(p, C, A, B, d, stream);
+        case DTYPE_FLOAT32: {
+            if (forced != RPB_KERNEL_SIMT) {
+                int rc = launch_tf32(p, C, A, B, d, stream);
+                if (rc <= 0) return rc;
+            }
+            return launch_simt<float, float>(p, C, A, B, d, stream);
+        }
         case DTYPE_FLOAT64: {
             if (forced != RPB_KERNEL_SIMT) {
                 int rc = launch_dmma(p, C, A, B, d, stream);

@@ -163,5 +163,76 @@ __global__ void splitk_reduce_kernel(const Acc* __restrict__ partial, T* c, int 
     }
 }
 
+/* Same reduction for n % 4 == 0: 4 consecutive outputs per thread (one 16/32-byte load per split)
+ * and the splits dealt over 8 thread groups, so many loads are in flight even when the output is small
+ * (a skinny dB with K in the tens of thousands).  Group g adds splits g, g+8, ... in order, then the
+ * eight group sums are added in group order: a fixed association, independent of scheduling. */
+template <typename T, typename Acc>
+__global__ void __launch_bounds__(256)
+splitk_reduce_vec_kernel(const Acc* __restrict__ partial, T* c, int splits, int batch, int m, int n,
+                         long long c_row, long long c_batch, int accumulate)
+{
+    constexpr int GROUPS = 8, VECS = 32;
+    __shared__ Acc red[GROUPS][VECS][4];
+    const long long per_split = (long long)batch * m * n;
+    const long long nvec = per_split / 4;
+    const int vec_in_block = threadIdx.x % VECS, grp = threadIdx.x / VECS;
+    for (long long v0 = (long long)blockIdx.x * VECS; v0 < nvec; v0 += (long long)gridDim.x * VECS) {
+        const long long v = v0 + vec_in_block;
+        Acc s[4] = {Acc(0), Acc(0), Acc(0), Acc(0)};
+        if (v < nvec) {
+#pragma unroll 4
+            for (int sp = grp; sp < splits; sp += GROUPS) {
+                const Acc* src = partial + sp * per_split + v * 4;
+                if (sizeof(Acc) == 4) {
+                    const float4 x = *reinterpret_cast<const float4*>(src);
+                    s[0] += x.x; s[1] += x.y; s[2] += x.z; s[3] += x.w;
+                } else {
+                    const double2 x = *reinterpret_cast<const double2*>(src);
+                    const double2 y = *reinterpret_cast<const double2*>(src + 2);
+                    s[0] += x.x; s[1] += x.y; s[2] += y.x; s[3] += y.y;
+                }
+            }
+        }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) red[grp][vec_in_block][e] = s[e];
+        __syncthreads();
+        if (grp == 0 && v < nvec) {
+#pragma unroll
+            for (int g = 1; g < GROUPS; ++g)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) s[e] += red[g][vec_in_block][e];
+            const long long i = v * 4;
+            const int col = (int)(i % n);
+            const long long t = i / n;
+            const int row = (int)(t % m);
+            const int bz = (int)(t / m);
+            T* dst = c + bz * c_batch + (long long)row * c_row + col;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                Acc x = s[e];
+                if (accumulate) x += widen<Acc, T>(dst[e]);
+                dst[e] = narrow<T, Acc>(x);
+            }
+        }
+        __syncthreads();
+    }
+}
+
+template <typename T, typename Acc>
+inline void launch_splitk_reduce(const Acc* partial, T* c, int splits, int batch, int m, int n, long long c_row,
+                                 long long c_batch, int accumulate, int sm_count, cudaStream_t stream) {
+    const long long elems = (long long)batch * m * n;
+    if (n % 4 == 0 && splits >= 4) {
+        long long blocks = (elems / 4 + 31) / 32;
+        if (blocks > sm_count * 8) blocks = sm_count * 8;
+        splitk_reduce_vec_kernel<T, Acc><<<(unsigned)blocks, 256, 0, stream>>>(partial, c, splits, batch, m, n, c_row, c_batch, accumulate);
+    } else {
+        long long blocks = (elems + 255) / 256;
+        if (blocks > sm_count * 8) blocks = sm_count * 8;
+        splitk_reduce_kernel<T, Acc><<<(unsigned)blocks, 256, 0, stream>>>(partial, c, splits, batch, m, n, c_row, c_batch, accumulate);
+    }
+}
+
 }  // namespace rpb_simt
 #endif

@@ -100,7 +100,7 @@ def test_simt_large_tile_and_splitk(lib, dtype):
     rng = np.random.default_rng(5)
     for (m, k, n) in [(512, 96, 640), (64, 2048, 64), (700, 300, 520)]:
         a = rand_operand(rng, (1, 1, m, k), dtype); b = rand_operand(rng, (1, 1, k, n), dtype, scale=1 / np.sqrt(k))
-        run_ex(lib, dtype, a, b, expect=(_lib.KERNEL_SIMT, _lib.KERNEL_DMMA))
+        run_ex(lib, dtype, a, b, expect=(_lib.KERNEL_SIMT, _lib.KERNEL_DMMA, _lib.KERNEL_TF32X3))
 
 
 @pytest.mark.parametrize("layout", [(False, False), (True, False), (False, True), (True, True)])
@@ -118,6 +118,24 @@ def test_fp64_tensor_core_kernel(lib, layout):
     a = rand_operand(rng, (3, 2, 96, 40), dtype); b = rand_operand(rng, (3, 2, 40, 72), dtype)
     run_ex(lib, dtype, a, b, ta=ta, tb=tb, expect=(_lib.KERNEL_DMMA,))
     run_ex(lib, dtype, a, b, ta=ta, tb=tb, c_init=rand_operand(rng, (3, 96, 72), dtype), expect=(_lib.KERNEL_DMMA,))
+
+
+@pytest.mark.parametrize("layout", [(False, False), (True, False), (False, True), (True, True)])
+def test_fp32_3xtf32_kernel(lib, layout):
+    """float32 on tensor cores (3xTF32): must meet the same fp32 bound as the strict-fp32 reference,
+    in every operand orientation, with ragged extents, K splits, batches and accumulation."""
+    ta, tb = layout
+    dtype = "float32"
+    rng = np.random.default_rng(47)
+    for (m, k, n) in [(64, 32, 64), (128, 784, 256), (64, 512, 2048), (100, 132, 68), (129, 37, 131), (32, 4096, 64),
+                      (1500, 100, 1300)]:
+        a = rand_operand(rng, (1, 1, m, k), dtype); b = rand_operand(rng, (1, 1, k, n), dtype, scale=1 / np.sqrt(k))
+        pa = (-m % 4) if ta else (-k % 4)        # stored leading dimension a multiple of 4 floats
+        pb = (-k % 4) if tb else (-n % 4)
+        run_ex(lib, dtype, a, b, ta=ta, tb=tb, pad_a=pa, pad_b=pb, expect=(_lib.KERNEL_TF32X3,))
+    a = rand_operand(rng, (3, 2, 96, 40), dtype); b = rand_operand(rng, (3, 2, 40, 72), dtype)
+    run_ex(lib, dtype, a, b, ta=ta, tb=tb, expect=(_lib.KERNEL_TF32X3,))
+    run_ex(lib, dtype, a, b, ta=ta, tb=tb, c_init=rand_operand(rng, (3, 96, 72), dtype), expect=(_lib.KERNEL_TF32X3,))
 
 
 @pytest.mark.parametrize("dtype", ["float32", "float64", "float16", "bfloat16"])
