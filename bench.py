@@ -64,6 +64,15 @@ def parse():
     return p.parse_args()
 
 
+# DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) of ONE forward-GEMM launch, from the ncu
+# captures summarised under profiles/.  The default workload is too large to capture under the size rule,
+# so its figure is the 8192-row capture scaled by the row count (A, C and the per-row-block re-reads of B
+# all grow with the rows).
+NCU_TRAFFIC_BYTES = {
+    "rowsharded_65536x8192x8192": lambda rows: 1.2236e9 * rows / 8192.0,
+}
+
+
 def peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -349,11 +358,15 @@ def main():
         pk = peaks()
         half = dtype_name in ("bfloat16", "float16")
         flops_fwd = 2.0 * rows * k * n                               # one launch of the dominant kernel on this rank
+        traffic_fn = NCU_TRAFFIC_BYTES.get(args.workload)
+        traffic = traffic_fn(rows) if traffic_fn else None
         if half and args.workload != "bmm_fp16":
             achieved = flops_fwd / (fwd_ms * 1e-3) / 1e12
             roof = {"bound": "tensor", "kernel": "rpb_umma::gemm_kernel (forward GEMM launch)", "achieved": achieved,
                     "peak": pk["tflops"], "unit": "TFLOP/s", "frac": achieved / pk["tflops"],
-                    "peak_source": pk["src"] + " cuBLAS bf16, sustained", "traffic": None,
+                    "peak_source": pk["src"] + " cuBLAS bf16, sustained", "traffic": traffic,
+                    "traffic_note": "ncu DRAM bytes of one forward launch at 8192 rows, scaled by rows" if traffic else None,
+                    "algorithmic_bytes": (rows * k + k * n + rows * n) * es,
                     "avg_launch_ms": fwd_ms}
         else:
             bytes_fwd = (rows * k + k * n + rows * n) * es

@@ -451,13 +451,16 @@ int launch_umma_bn(bool a_mn, bool b_mn, const CUtensorMap& ma, const CUtensorMa
     return launch_umma_inst<T, BN, true, true, PAIR>(ma, mb, mc, args, grid, stream);
 }
 
-/* Two-CTA tiles (256 x 256 per cluster) pay off once every cluster has a tile to work on. */
-bool want_pair(int m, int n, int batch, int sm_count) {
+/* Two-CTA tiles (256 x 256 per cluster) pay off once every cluster has a tile to work on and the
+ * main loop is long enough to hide the pair's cross-CTA hand-offs (measured: at K = 64 the one-CTA
+ * kernel is 1.3-1.5x faster, at K >= 512 the pair wins). */
+bool want_pair(int m, int n, long long k_total, int batch, int sm_count) {
     static int env = -1;
     if (env < 0) { const char* e = getenv("RPB_UMMA_PAIR"); env = e ? (atoi(e) ? 1 : 0) + 1 : 0; }
     if (env == 1) return false;
     if (n < 256 || m < 256) return false;
     if (env == 2) return true;
+    if (k_total < 512) return false;
     const long long tiles = (long long)((m + 255) / 256) * ((n + 255) / 256) * batch;
     return tiles >= sm_count / 2;
 }
@@ -470,7 +473,7 @@ int launch_umma(const RpbProblem& p, void* C, const void* A, const void* B, Devi
     OperandPlan pb = plan_operand(B, p.n, p.k, p.b_col, p.b_row, p.batch, p.b_batch, p.reduce, p.b_reduce);
     if (!pa.ok || !pb.ok) return 1;
 
-    const bool pair = want_pair(p.m, p.n, p.batch, d->sm_count);
+    const bool pair = want_pair(p.m, p.n, (long long)p.k * p.reduce, p.batch, d->sm_count);
     /* BN = rows of B per CTA; a pair multiplies 256 x (2 BN) tiles */
     const int BN = pair ? 128 : (p.n <= 64 ? 64 : (p.n <= 128 ? 128 : 256));
     const int tile_m = pair ? 2 * rpb_umma::BLOCK_M : rpb_umma::BLOCK_M;

@@ -1,11 +1,13 @@
 /*
  * tcgen05 GEMM for float16 / bfloat16 (fp32 accumulation in tensor memory).
  *
- * One persistent CTA per SM, 6 warps:
+ * One persistent CTA per SM, 10 warps:
  *   warp 0      TMA producer: 128B-swizzled tiles of A and B into a shared-memory ring
  *   warp 1      owns tensor memory; one lane issues tcgen05.mma (M=128, N=BN, K=16)
- *   warps 2..5  epilogue: tcgen05.ld of the fp32 accumulator, optional "+= C", rounding,
- *               global stores (or fp32 partial tiles when K is split across CTAs)
+ *   warps 2..9  epilogue: tcgen05.ld of the fp32 accumulator, rounding, staging in shared memory
+ *               and TMA stores (or register stores with optional "+= C"); fp32 partial tiles
+ *               when K is split across CTAs.  Two warps share each tensor-memory lane quarter
+ *               and take alternate column chunks.
  * Two accumulators (2 x BN tensor-memory columns) let the epilogue of tile i overlap
  * the main loop of tile i+1.
  *
@@ -32,17 +34,18 @@ namespace rpb_umma {
 constexpr int BLOCK_M = 128;
 constexpr int BLOCK_K = 64;             /* 64 x 2 bytes = one 128-byte swizzle row */
 constexpr int UMMA_K = 16;
-constexpr int NUM_THREADS = 192;
-constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;   /* 2 s per wait */
+constexpr int EPI_WARPS = 8;           /* two per tensor-memory lane quarter: even / odd column chunks */
+constexpr int NUM_THREADS = (2 + EPI_WARPS) * 32;
+constexpr long long WAIT_LIMIT_CYCLES = 4000000000ll;   /* about 2 s of SM clock per wait */
 constexpr int SMEM_LIMIT = 227 * 1024;
 
 template <int BN> struct Config {
     static constexpr int A_BYTES = BLOCK_M * BLOCK_K * 2;
     static constexpr int B_BYTES = BN * BLOCK_K * 2;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-    /* epilogue staging for TMA stores: 4 warps x 2 buffers x (32 rows x 128 bytes) */
+    /* epilogue staging for TMA stores: one buffer of 32 rows x 128 bytes per epilogue warp */
     static constexpr int STORE_BUF_BYTES = 32 * 128;
-    static constexpr int STORE_BYTES = 4 * 2 * STORE_BUF_BYTES;
+    static constexpr int STORE_BYTES = EPI_WARPS * STORE_BUF_BYTES;
     static constexpr int STAGES_RAW = (SMEM_LIMIT - 2048 - STORE_BYTES) / STAGE_BYTES;
     static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + STORE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
@@ -93,23 +96,17 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
         : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok;
 }
-__device__ __forceinline__ unsigned long long global_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    return t;
-}
-/* Bounded wait: gives up after WAIT_LIMIT_NS of wall time.  false = gave up (or another role
- * already did): the caller leaves its main loop and the kernel tears down. */
+/* Bounded wait: gives up after WAIT_LIMIT_CYCLES of the SM clock (about 2 s).  false = gave up (or
+ * another role already did): the caller leaves its main loop and the kernel tears down. */
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                           int* status, int code) {
-    unsigned long long t0 = 0;
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
     for (uint32_t i = 0;; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((i & 63u) == 63u) {
+        if ((i & 255u) == 255u) {
             if (*abort_flag) return false;
-            const unsigned long long now = global_ns();
-            if (t0 == 0) t0 = now;
-            else if (now - t0 > WAIT_LIMIT_NS) break;
+            if (clock64() - t0 > WAIT_LIMIT_CYCLES) break;
         }
     }
     *abort_flag = 1;
@@ -203,15 +200,33 @@ __device__ __forceinline__ void tmem_load_32(uint32_t taddr, uint32_t (&v)[32]) 
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+__device__ __forceinline__ void tmem_load_32_nowait(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+          "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+          "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_load_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
 template <typename T> __device__ __forceinline__ float to_f32(T v);
 template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
 template <> __device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
 template <typename T> __device__ __forceinline__ T from_f32(float v);
 template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
 template <> __device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half_rn(v); }
-template <typename T> __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
-    T a = from_f32<T>(lo), b = from_f32<T>(hi);
-    return (uint32_t) * reinterpret_cast<uint16_t*>(&a) | ((uint32_t) * reinterpret_cast<uint16_t*>(&b) << 16);
+template <typename T> __device__ __forceinline__ uint32_t pack2(float lo, float hi);
+template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);          /* .x = lo in the low half */
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+template <> __device__ __forceinline__ uint32_t pack2<__half>(float lo, float hi) {
+    const __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
 }
 
 /* ------------------------------------------------------------------ kernel */
@@ -256,7 +271,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < Cfg::STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-        for (int i = 0; i < 2; ++i) { mbar_init(tfull_bar(i), 1); mbar_init(tempty_bar(i), PAIR ? 256 : 128); }
+        for (int i = 0; i < 2; ++i) { mbar_init(tfull_bar(i), 1); mbar_init(tempty_bar(i), (PAIR ? 2 : 1) * EPI_WARPS); }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
@@ -380,6 +395,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     } else {
         /* epilogue: warp w may touch tensor-memory lanes 32*(w%4) .. +31 */
         const int quarter = warp & 3;
+        const int half = (warp - 2) >> 2;                 /* 0: even column chunks, 1: odd ones */
         const uint32_t lane_field = (uint32_t)(quarter * 32) << 16;
         uint32_t local_tile = 0;
         bool alive = true;
@@ -397,25 +413,25 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                 /* Each warp stages 32 rows x 128 bytes in the 128-byte swizzle the store's tensor map
                  * expects (16-byte chunk c of row r at position c ^ (r & 7)) and one lane hands the box to
                  * the TMA engine, which writes whole lines and clips rows >= M / columns >= N itself.
-                 * Two buffers per warp: staging of chunk j+1 overlaps the store of chunk j. */
+                 * One 4 KB buffer per warp; the two warps of a lane quarter take alternate chunks. */
                 const int row_warp = mt * TILE_M + (int)cta_rank * BLOCK_M + quarter * 32;
-                const uint32_t buf0 = store_base + (uint32_t)quarter * 2u * Cfg::STORE_BUF_BYTES;
+                const uint32_t buf = store_base + (uint32_t)(warp - 2) * Cfg::STORE_BUF_BYTES;
                 const uint32_t my_row = (uint32_t)lane * 128u;
                 const uint32_t sw = (uint32_t)lane & 7u;
                 const bool partial_out = args.splits > 1;
                 const int cols_per_box = partial_out ? 32 : 64;             /* 128 bytes of fp32 or of T */
                 const int zc = partial_out ? split * args.batch + bz : bz;
-                uint32_t parity = 0;
 #pragma unroll 1
-                for (int c0 = 0; c0 < ACC_N; c0 += cols_per_box) {
+                for (int c0 = half * cols_per_box; c0 < ACC_N; c0 += 2 * cols_per_box) {
                     const int col = nt * ACC_N + c0;
                     uint32_t v[32], v2[32];
                     __syncwarp();
-                    tmem_load_32(tmem_base + ab * ACC_N + c0 + lane_field, v);
-                    if (!partial_out) tmem_load_32(tmem_base + ab * ACC_N + c0 + 32 + lane_field, v2);
+                    /* the accumulator reads of this chunk overlap the TMA engine draining the previous one */
+                    tmem_load_32_nowait(tmem_base + ab * ACC_N + c0 + lane_field, v);
+                    if (!partial_out) tmem_load_32_nowait(tmem_base + ab * ACC_N + c0 + 32 + lane_field, v2);
+                    tmem_load_wait();
                     if (col >= args.n || row_warp >= args.m) continue;      /* warp-uniform */
-                    const uint32_t buf = buf0 + parity * Cfg::STORE_BUF_BYTES;
-                    if (lane == 0) tma_store_wait_read<1>();                /* the store that last used `buf` has read it */
+                    if (lane == 0) tma_store_wait_read<0>();                /* the previous store has read `buf` */
                     __syncwarp();
                     if (partial_out) {
 #pragma unroll
@@ -439,15 +455,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   /* generic writes -> async proxy */
                     __syncwarp();
                     if (lane == 0) tma_store_3d(&map_c, buf, col, row_warp, zc);
-                    parity ^= 1u;
                 }
                 tc_fence_before();
-                if (PAIR) mbar_arrive_cluster(cluster_addr(tempty_bar(ab), 0));
-                else mbar_arrive(tempty_bar(ab));
+                __syncwarp();                 /* every lane's accumulator reads are done: one arrival per warp */
+                if (lane == 0) {
+                    if (PAIR) mbar_arrive_cluster(cluster_addr(tempty_bar(ab), 0));
+                    else mbar_arrive(tempty_bar(ab));
+                }
                 continue;
             }
 #pragma unroll 1
-            for (int c0 = 0; c0 < ACC_N; c0 += 32) {
+            for (int c0 = half * 32; c0 < ACC_N; c0 += 64) {
                 uint32_t v[32];
                 __syncwarp();                 /* tcgen05.ld is warp-collective */
                 tmem_load_32(tmem_base + ab * ACC_N + c0 + lane_field, v);
@@ -491,8 +509,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                 }
             }
             tc_fence_before();
-            if (PAIR) mbar_arrive_cluster(cluster_addr(tempty_bar(ab), 0));   /* the leader owns the accumulator hand-off */
-            else mbar_arrive(tempty_bar(ab));
+            __syncwarp();
+            if (lane == 0) {
+                if (PAIR) mbar_arrive_cluster(cluster_addr(tempty_bar(ab), 0));   /* the leader owns the accumulator hand-off */
+                else mbar_arrive(tempty_bar(ab));
+            }
         }
     }
 
