@@ -152,6 +152,63 @@ def run_reference_arm(args, rank):
     print(json.dumps(line), flush=True)
 
 
+def reference_gpu_as_shipped(dtype_name, m, k, n, steps):
+    """The unmodified reference (oracle/_ref) on the GPU, as shipped: op_matmul + backward_matmul_fn through
+    its own C entry points (cuBLAS handle created and destroyed per call, transposes materialised,
+    cudaMalloc + memset per output).  Operand values are zeros; returns ms per fwd+bwd step, or None."""
+    so = os.path.join(ROOT, "oracle", "_ref", "recpulse_cuda.so")
+    if not os.path.exists(so):
+        return None
+    from recpulse_b200._lib import CTensor, GradFn, Meta
+    ref = C.CDLL(so)
+    libc = C.CDLL(None)
+    libc.calloc.restype = C.c_void_p
+    libc.calloc.argtypes = [C.c_size_t, C.c_size_t]
+    TP = C.POINTER(CTensor)
+    ref.zeros_tensor.restype = TP
+    ref.zeros_tensor.argtypes = [C.c_int, C.c_int, C.c_int, C.POINTER(C.c_int), C.c_void_p]
+    ref.op_matmul.restype = TP
+    ref.op_matmul.argtypes = [TP, TP]
+    ref.backward_matmul_fn.restype = None
+    ref.backward_matmul_fn.argtypes = [C.POINTER(GradFn), TP]
+    ref.free_tensor.restype = None
+    ref.free_tensor.argtypes = [TP]
+    code = {"float32": 0, "float64": 1, "float16": 2, "bfloat16": 3}[dtype_name]
+
+    def make(shape, grad):
+        meta = None
+        if grad:
+            meta = libc.calloc(1, C.sizeof(Meta))
+            mm = C.cast(meta, C.POINTER(Meta)).contents
+            mm.is_leaf = True; mm.requires_grad = True
+        return ref.zeros_tensor(code, 0, 2, (C.c_int * 2)(*shape), meta)
+
+    a, b, g = make((m, k), True), make((k, n), True), make((m, n), False)
+    if not a or not b or not g:
+        return None
+
+    def step():
+        out = ref.op_matmul(a, b)
+        ref.backward_matmul_fn(out.contents.metadata.contents.grad_fn, g)
+        ref.free_tensor(out)
+        for t in (a, b):                                   # drop the grads so every step allocates like the first
+            mt = t.contents.metadata.contents
+            if mt.grad:
+                ref.free_tensor(mt.grad)
+                mt.grad = None
+
+    import torch
+    step(); torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    torch.cuda.synchronize()
+    dt = (time.perf_counter() - t0) / steps * 1e3
+    for t in (a, b, g):
+        ref.free_tensor(t)
+    return dt
+
+
 # --------------------------------------------------------------------------- clocks
 
 class ClockSampler:
@@ -320,6 +377,28 @@ def main():
             tot += c0.elapsed_time(c1)
         cublas = {"tflops": flops_step / (tot / args.steps * 1e-3) / 1e12, "ms_per_step": tot / args.steps,
                   "what": "torch.matmul x3 (cuBLAS, warm handle, outputs preallocated)"}
+        ref_ms = reference_gpu_as_shipped(dtype_name, rows, k, n, min(args.steps, 5))
+        if ref_ms:
+            cublas["reference_as_shipped_ms_per_step"] = ref_ms
+            cublas["reference_as_shipped_tflops"] = flops_step / (ref_ms * 1e-3) / 1e12
+        # the same step through this library's autograd node (allocation + synchronisation included)
+        import recpulse_b200 as rpb
+        dn = dtype_name
+        hA = rpb.Tensor.from_numpy(np.zeros((rows, k), np.uint16 if es == 2 else (np.float32 if es == 4 else np.float64)), dtype=dn, requires_grad=True)
+        hB = rpb.Tensor.from_numpy(np.zeros((k, n), np.uint16 if es == 2 else (np.float32 if es == 4 else np.float64)), dtype=dn, requires_grad=True)
+        hG = rpb.Tensor.from_numpy(np.zeros((rows, n), np.uint16 if es == 2 else (np.float32 if es == 4 else np.float64)), dtype=dn)
+        def node_step():
+            y = hA.op_matmul(hB); y.backward(hG)
+            for t in (hA, hB):
+                mt = t._t.metadata.contents
+                if mt.grad:
+                    lib.rpb_tensor_release(mt.grad); mt.grad = None
+        node_step(); torch.cuda.synchronize(dev)
+        t0 = time.perf_counter()
+        for _ in range(min(args.steps, 5)):
+            node_step()
+        torch.cuda.synchronize(dev)
+        cublas["this_library_node_ms_per_step"] = (time.perf_counter() - t0) / min(args.steps, 5) * 1e3
 
     # ---- end to end from pinned host buffers through the C ABI
     e2e = None
@@ -331,20 +410,29 @@ def main():
         hdA = torch.empty((rows, k), dtype=tdtype).pin_memory()
         hdB = torch.empty((k, n), dtype=tdtype).pin_memory()
 
+        code = {"float32": 0, "float64": 1, "float16": 2, "bfloat16": 3}[dtype_name]
+        ptr = lambda t: C.c_void_p(t.data_ptr())
+
         def e2e_step():
-            A.copy_(hA, non_blocking=True); Bm.copy_(hB, non_blocking=True); dC.copy_(hdC, non_blocking=True)
-            step()
-            hC.copy_(Cc, non_blocking=True); hdA.copy_(dA, non_blocking=True); hdB.copy_(dB, non_blocking=True)
+            # the library's host-buffer entry point: chunked H2D of A and dC, GEMMs and D2H of C and dA
+            # overlapped on three streams, dB as one GEMM at the end; returns when the host buffers are filled
+            rc = lib.rp_matmul_fwdbwd_host(ptr(hC), ptr(hdA), ptr(hdB), ptr(hA), ptr(hB), ptr(hdC), rows, k, n, code,
+                                           local_rank, 0)
+            if rc != 0:
+                raise SystemExit("bench.py: rp_matmul_fwdbwd_host failed")
+            if world > 1:                          # dB partials of the ranks are summed on the host-visible copy
+                dB.copy_(hdB, non_blocking=True)
+                dist.all_reduce(dB)
+                hdB.copy_(dB, non_blocking=True)
+                torch.cuda.synchronize(dev)
 
         e2e_step()
         barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(stream)
+        t0 = time.perf_counter()
         for _ in range(args.e2e_steps):
             e2e_step()
-        e1.record(stream)
         barrier()
-        e2e_ms = e0.elapsed_time(e1) / args.e2e_steps
+        e2e_ms = (time.perf_counter() - t0) / args.e2e_steps * 1e3
         if world > 1:
             t = torch.tensor([e2e_ms], device=dev, dtype=torch.float64)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -352,7 +440,8 @@ def main():
         h2d = (rows * k + k * n + rows * n) * es
         d2h = (rows * n + rows * k + k * n) * es
         e2e = {"value": flops_step / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "h2d_bytes_per_step": int(h2d),
-               "d2h_bytes_per_step": int(d2h), "ms_per_step": e2e_ms, "steps": args.e2e_steps}
+               "d2h_bytes_per_step": int(d2h), "ms_per_step": e2e_ms, "steps": args.e2e_steps,
+               "api": "rp_matmul_fwdbwd_host (C ABI, pinned host buffers, wall clock around the synchronous call)"}
 
     if rank == 0:
         pk = peaks()

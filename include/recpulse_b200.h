@@ -138,6 +138,18 @@ int rp_matmul_ex(void* C, const void* A, const void* B, const RpbGemm* g, DType 
 int rp_matmul_host(void* C, const void* A, const void* B, int m, int k, int n, DType dtype,
                    int device_id);
 
+/* Forward + backward of one matmul whose six matrices live in HOST memory (packed row-major):
+ * C = A.B, dA = dC.B^T, dB = A^T.dC.  Any of C, dA, dB may be NULL (not wanted); dC is needed for dA / dB.
+ * RecPulse copies whole tensors synchronously before it multiplies (tensor_copy_device,
+ * core/tensor_device.cu:295-372); this call streams row chunks of A and dC so that the host-to-device
+ * copies, the GEMMs and the device-to-host copies of the results overlap on three streams.  Pinned host
+ * memory is needed for the overlap (pageable memory works, slower).  chunk_rows = 0 picks a chunk size.
+ * Synchronous: results are in the host buffers on return.  Device buffers are cached per device;
+ * rpb_release_host_pipeline frees them.  0 on success, -1 on error. */
+int rp_matmul_fwdbwd_host(void* C, void* dA, void* dB, const void* A, const void* B, const void* dC,
+                          int m, int k, int n, DType dtype, int device_id, int chunk_rows);
+int rpb_release_host_pipeline(int device_id);
+
 /* No counterpart in RecPulse.  C[m,n] = A[m,k] . B[k,n] for packed row-major float16 / bfloat16
  * operands, for callers that cannot let a library allocate: processes that have given all device
  * memory to their own pool (a hidden cudaMalloc would fail or fragment it) and latency-critical

@@ -57,6 +57,9 @@ SYMBOLS = {
     "rpb_gemm_packed": (None, [C.POINTER(RpbGemm), C.c_int, C.c_int, C.c_int]),
     "rp_matmul_ex": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(RpbGemm), C.c_int, C.c_int, C.c_void_p]),
     "rp_matmul_host": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
+    "rp_matmul_fwdbwd_host": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                        C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
+    "rpb_release_host_pipeline": (C.c_int, [C.c_int]),
     "rp_matmul_noalloc": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
                                     C.c_void_p, C.POINTER(C.c_int)]),
     "rpb_last_kernel": (C.c_int, []),

@@ -228,6 +228,34 @@ def test_host_buffer_entry_point(lib):
     check_close(c, O.rp_matmul(a, b, O.BF16), "bfloat16", 160, "rp_matmul_host")
 
 
+@pytest.mark.parametrize("dtype", ["bfloat16", "float16", "float32", "float64"])
+def test_streamed_host_forward_backward(lib, dtype):
+    """rp_matmul_fwdbwd_host: row chunks streamed through three streams; ragged last chunk; optional outputs."""
+    rng = np.random.default_rng(53)
+    m, k, n = 1000, 136, 264
+    a = rand_operand(rng, (m, k), dtype); b = rand_operand(rng, (k, n), dtype, scale=1 / np.sqrt(k))
+    dc = rand_operand(rng, (m, n), dtype)
+    st = O.storage(CODE[dtype])
+    c = np.zeros((m, n), st); da = np.zeros((m, k), st); db = np.zeros((k, n), st)
+    p = lambda x: x.ctypes.data_as(C.c_void_p)
+    for chunk in (0, 256, 300, 4096):
+        c[:] = 0; da[:] = 0; db[:] = 0
+        assert lib.rp_matmul_fwdbwd_host(p(c), p(da), p(db), p(a), p(b), p(dc), m, k, n, CODE[dtype], 0, chunk) == 0
+        check_close(c, O.rp_matmul(a, b, CODE[dtype]), dtype, k, f"C chunk={chunk}")
+        oda, odb = O.matmul_backward(a, b, dc, CODE[dtype])
+        check_close(da, oda, dtype, n, f"dA chunk={chunk}")
+        check_close(db, odb, dtype, m, f"dB chunk={chunk}")
+    # forward only, and backward-of-B only
+    c[:] = 0
+    assert lib.rp_matmul_fwdbwd_host(p(c), None, None, p(a), p(b), None, m, k, n, CODE[dtype], 0, 0) == 0
+    check_close(c, O.rp_matmul(a, b, CODE[dtype]), dtype, k, "forward only")
+    db[:] = 0
+    assert lib.rp_matmul_fwdbwd_host(None, None, p(db), p(a), p(b), p(dc), m, k, n, CODE[dtype], 0, 0) == 0
+    check_close(db, O.matmul_backward(a, b, dc, CODE[dtype])[1], dtype, m, "dB only")
+    assert lib.rp_matmul_fwdbwd_host(None, None, p(db), p(a), p(b), None, m, k, n, CODE[dtype], 0, 0) == -1
+    assert lib.rpb_release_host_pipeline(0) == 0
+
+
 def test_results_do_not_depend_on_scheduling(lib):
     rng = np.random.default_rng(41)
     a = rand_operand(rng, (1, 1, 64, 4096), "bfloat16"); b = rand_operand(rng, (1, 1, 4096, 128), "bfloat16", scale=1 / 64)
