@@ -106,6 +106,22 @@ Tensor* op_matmul(Tensor* a, Tensor* b);
  * untouched (the function is void, as in RecPulse). */
 void backward_matmul_fn(GradFn* self, Tensor* grad_output);
 
+/* ---- additive: Linear as one node ------------------------------------------*/
+
+/* y = x . w + bias with the bias added in the GEMM epilogue (one rounding), as ONE autograd node.
+ * RecPulse's Linear.forward (recpulse/module.py:110-114) is op_matmul followed by a broadcast op_add
+ * (ops/ops.c:129-210) whose backward reduces dY on the host (reduce_grad_to_shape,
+ * ops/ops.c:6970-7101).  Here the backward computes dX and dW as op_matmul's does and
+ * dbias = column sums of dY on the device.  x: [..., k]; w: [k, n] (or batched like op_matmul);
+ * bias: n elements (shape [n] or [1, ..., n]), same dtype and device.  bias may be NULL (= op_matmul). */
+Tensor* op_linear(Tensor* x, Tensor* w, Tensor* bias);
+void backward_linear_fn(GradFn* self, Tensor* grad_output);
+
+/* out[j] (+)= sum over i < rows of in[i * row_stride + j], j < cols; fp32 (fp64 for float64) sums in a
+ * fixed order, one rounding.  Runs on `stream` without synchronising. */
+int rp_colsum_ex(void* out, const void* in, long long rows, int cols, long long row_stride, DType dtype,
+                 int accumulate, int device_id, void* stream);
+
 /* ---- additive: strided / batched GEMM on raw pointers ----------------------*/
 
 typedef struct {
@@ -120,6 +136,8 @@ typedef struct {
     long long c_row;                /* row stride of C; its column stride is 1               */
     long long c_batch;
     int accumulate;                 /* 0: C = AB ; 1: C = C + AB (one rounding of the sum)   */
+    const void* bias;               /* NULL, or n values of the GEMM's dtype added to every  */
+                                    /* row of every batch before the rounding (device memory)*/
 } RpbGemm;
 
 /* Fills `g` for a packed row-major m x k times k x n product (batch = reduce = 1). */

@@ -295,3 +295,38 @@ int orc_bmm_backward(void* dA, void* dB, const void* A, const void* B, const voi
     }
     return rc;
 }
+
+/* recpulse/module.py:110-114 + ops/ops.c:129-210 */
+int orc_linear_forward(void* Y, const void* X, const void* W, const void* bias, int m, int k, int n, int dtype) {
+    int rc = orc_rp_matmul(Y, X, W, m, k, n, dtype);
+    if (rc || !bias) return rc;
+    for (int i = 0; i < m; i++) {
+        if (dtype == ORC_F32) { float* y = (float*)Y + (size_t)i * n; const float* b = (const float*)bias; for (int j = 0; j < n; j++) y[j] = y[j] + b[j]; }
+        else if (dtype == ORC_F64) { double* y = (double*)Y + (size_t)i * n; const double* b = (const double*)bias; for (int j = 0; j < n; j++) y[j] = y[j] + b[j]; }
+        else grad_add((uint16_t*)Y + (size_t)i * n, bias, (size_t)n, dtype);   /* widen, add, narrow per element */
+    }
+    return 0;
+}
+
+/* ops/ops.c:6970-7101 */
+int orc_bias_grad(void* dbias, const void* dY, long long rows, int n, int dtype) {
+    if (!dbias || !dY || rows <= 0 || n <= 0) return -1;
+    if (dtype == ORC_F64) {
+        double* r = (double*)dbias; const double* g = (const double*)dY;
+        for (int j = 0; j < n; j++) r[j] = 0.0;
+        for (long long i = 0; i < rows; i++) for (int j = 0; j < n; j++) { volatile double t = r[j] + g[i * n + j]; r[j] = t; }
+        return 0;
+    }
+    float* acc = (float*)calloc((size_t)n, sizeof(float));
+    if (!acc) return -1;
+    for (long long i = 0; i < rows; i++)
+        for (int j = 0; j < n; j++) {
+            float g;
+            if (dtype == ORC_F32) g = ((const float*)dY)[i * n + j];
+            else orc_widen((const uint16_t*)dY + i * n + j, &g, 1, dtype);
+            volatile float t = acc[j] + g; acc[j] = t;
+        }
+    if (dtype == ORC_F32) memcpy(dbias, acc, (size_t)n * 4); else orc_narrow(acc, dbias, (size_t)n, dtype);
+    free(acc);
+    return 0;
+}

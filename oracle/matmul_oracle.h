@@ -67,6 +67,14 @@ int orc_bmm_backward(void* dA, void* dB, const void* A, const void* B, const voi
                      int batch, size_t a_bstride, size_t b_bstride,
                      int m, int k, int n, int dtype);
 
+/* Linear layer as RecPulse composes it (recpulse/module.py:110-114): Y = op_add(op_matmul(X, W), bias),
+ * i.e. the product is rounded to the storage dtype, then the broadcast add (ops/ops.c:129-210; f16/bf16:
+ * widen, add in fp32, narrow) rounds again.  bias has n elements. */
+int orc_linear_forward(void* Y, const void* X, const void* W, const void* bias, int m, int k, int n, int dtype);
+/* Bias gradient, reduce_grad_to_shape (ops/ops.c:6970-7101): dY summed over rows in row order in fp32
+ * (fp64 for float64), one narrowing at the end. */
+int orc_bias_grad(void* dbias, const void* dY, long long rows, int n, int dtype);
+
 #ifdef __cplusplus
 }
 #endif

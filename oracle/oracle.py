@@ -150,3 +150,28 @@ def bmm_backward(a, b, dc, dtype):
     if rc != 0:
         raise RuntimeError("orc_bmm_backward failed")
     return da, db
+
+
+def linear_forward(x, w, bias, dtype):
+    """RecPulse's Linear.forward composition: op_add(op_matmul(x, w), bias)."""
+    x = np.ascontiguousarray(x, _NP[dtype]); w = np.ascontiguousarray(w, _NP[dtype])
+    bias = np.ascontiguousarray(bias, _NP[dtype]).reshape(-1)
+    lead = x.shape[:-1]
+    k = x.shape[-1]; n = w.shape[1]
+    m = int(np.prod(lead))
+    y = np.empty((m, n), _NP[dtype])
+    rc = lib().orc_linear_forward(_p(y), _p(x.reshape(m, k)), _p(w), _p(bias), m, k, n, dtype)
+    if rc != 0:
+        raise RuntimeError("orc_linear_forward failed")
+    return y.reshape(lead + (n,))
+
+
+def bias_grad(dy, dtype):
+    """Sum of dY over every leading index (reduce_grad_to_shape)."""
+    dy = np.ascontiguousarray(dy, _NP[dtype])
+    n = dy.shape[-1]; rows = dy.size // n
+    out = np.empty((n,), _NP[dtype])
+    rc = lib().orc_bias_grad(_p(out), _p(dy), C.c_longlong(rows), n, dtype)
+    if rc != 0:
+        raise RuntimeError("orc_bias_grad failed")
+    return out

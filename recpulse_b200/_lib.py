@@ -44,7 +44,7 @@ class RpbGemm(C.Structure):
     _fields_ = [("m", C.c_int), ("n", C.c_int), ("k", C.c_int), ("batch", C.c_int), ("reduce", C.c_int),
                 ("a_row", C.c_longlong), ("a_col", C.c_longlong), ("a_batch", C.c_longlong), ("a_reduce", C.c_longlong),
                 ("b_row", C.c_longlong), ("b_col", C.c_longlong), ("b_batch", C.c_longlong), ("b_reduce", C.c_longlong),
-                ("c_row", C.c_longlong), ("c_batch", C.c_longlong), ("accumulate", C.c_int)]
+                ("c_row", C.c_longlong), ("c_batch", C.c_longlong), ("accumulate", C.c_int), ("bias", C.c_void_p)]
 
 
 # every symbol include/recpulse_b200.h declares: name -> (restype, argtypes)
@@ -54,6 +54,10 @@ SYMBOLS = {
     "rp_matmul": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
     "op_matmul": (TP, [TP, TP]),
     "backward_matmul_fn": (None, [C.POINTER(GradFn), TP]),
+    "op_linear": (TP, [TP, TP, TP]),
+    "backward_linear_fn": (None, [C.POINTER(GradFn), TP]),
+    "rp_colsum_ex": (C.c_int, [C.c_void_p, C.c_void_p, C.c_longlong, C.c_int, C.c_longlong, C.c_int, C.c_int, C.c_int,
+                               C.c_void_p]),
     "rpb_gemm_packed": (None, [C.POINTER(RpbGemm), C.c_int, C.c_int, C.c_int]),
     "rp_matmul_ex": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(RpbGemm), C.c_int, C.c_int, C.c_void_p]),
     "rp_matmul_host": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),

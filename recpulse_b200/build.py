@@ -16,7 +16,7 @@ PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, "csrc")
 LIB = os.path.join(PKG, "librecpulse_b200.so")
 SOURCES = ["gemm_dispatch.cu", "host_pipeline.cu", "op_matmul.c"]
-HEADERS = ["gemm_simt.cuh", "gemm_umma.cuh", "gemm_dmma.cuh", "gemm_tf32x3.cuh", "rpb_common.h",
+HEADERS = ["gemm_simt.cuh", "gemm_umma.cuh", "gemm_dmma.cuh", "gemm_tf32x3.cuh", "reduce_cols.cuh", "rpb_common.h",
            os.path.join("..", "..", "include", "recpulse_b200.h")]
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 

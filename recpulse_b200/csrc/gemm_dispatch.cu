@@ -16,6 +16,7 @@
 #include "gemm_dmma.cuh"
 #include "gemm_simt.cuh"
 #include "gemm_tf32x3.cuh"
+#include "reduce_cols.cuh"
 #include "gemm_umma.cuh"
 #include "rpb_common.h"
 
@@ -134,7 +135,7 @@ int launch_simt_cfg(const RpbProblem& p, void* C, const void* A, const void* B, 
     a.m = p.m; a.n = p.n; a.k = p.k; a.batch = p.batch; a.reduce = p.reduce;
     a.a_row = p.a_row; a.a_col = p.a_col; a.a_batch = p.a_batch; a.a_reduce = p.a_reduce;
     a.b_row = p.b_row; a.b_col = p.b_col; a.b_batch = p.b_batch; a.b_reduce = p.b_reduce;
-    a.c_row = p.c_row; a.c_batch = p.c_batch; a.accumulate = p.accumulate;
+    a.c_row = p.c_row; a.c_batch = p.c_batch; a.accumulate = p.accumulate; a.bias = p.bias;
     a.tiles_m = (p.m + BM - 1) / BM; a.tiles_n = (p.n + BN - 1) / BN;
     a.k_blocks = (p.k + BK - 1) / BK;
     a.k_iters = a.k_blocks * p.reduce;
@@ -161,7 +162,7 @@ int launch_simt_cfg(const RpbProblem& p, void* C, const void* A, const void* B, 
     g_launches++;
     if (a.splits > 1) {
         rpb_simt::launch_splitk_reduce<T, Acc>(reinterpret_cast<const Acc*>(a.partial), reinterpret_cast<T*>(C), a.splits,
-                                               p.batch, p.m, p.n, p.c_row, p.c_batch, p.accumulate, d->sm_count, stream);
+                                               p.batch, p.m, p.n, p.c_row, p.c_batch, p.accumulate, p.bias, d->sm_count, stream);
         g_launches++;
         if (release_scratch(d, stream)) return -1;
     }
@@ -201,7 +202,7 @@ int launch_dmma(const RpbProblem& p, void* C, const void* A, const void* B, Devi
     a.m = p.m; a.n = p.n; a.k = p.k; a.batch = p.batch; a.reduce = p.reduce;
     a.a_row = p.a_row; a.a_col = p.a_col; a.a_batch = p.a_batch; a.a_reduce = p.a_reduce;
     a.b_row = p.b_row; a.b_col = p.b_col; a.b_batch = p.b_batch; a.b_reduce = p.b_reduce;
-    a.c_row = p.c_row; a.c_batch = p.c_batch; a.accumulate = p.accumulate;
+    a.c_row = p.c_row; a.c_batch = p.c_batch; a.accumulate = p.accumulate; a.bias = p.bias;
     a.tiles_m = (p.m + rpb_dmma::BM - 1) / rpb_dmma::BM; a.tiles_n = (p.n + rpb_dmma::BN - 1) / rpb_dmma::BN;
     a.k_blocks = (p.k + rpb_dmma::BK - 1) / rpb_dmma::BK;
     a.k_iters = a.k_blocks * p.reduce;
@@ -228,7 +229,7 @@ int launch_dmma(const RpbProblem& p, void* C, const void* A, const void* B, Devi
     if (a.splits > 1) {
         rpb_simt::launch_splitk_reduce<double, double>(reinterpret_cast<const double*>(a.partial), reinterpret_cast<double*>(C),
                                                        a.splits, p.batch, p.m, p.n, p.c_row, p.c_batch, p.accumulate,
-                                                       d->sm_count, stream);
+                                                       p.bias, d->sm_count, stream);
         g_launches++;
         if (release_scratch(d, stream)) return -1;
     }
@@ -257,7 +258,7 @@ int launch_tf32_cfg(const RpbProblem& p, void* C, const void* A, const void* B, 
     a.m = p.m; a.n = p.n; a.k = p.k; a.batch = p.batch; a.reduce = p.reduce;
     a.a_row = p.a_row; a.a_col = p.a_col; a.a_batch = p.a_batch; a.a_reduce = p.a_reduce;
     a.b_row = p.b_row; a.b_col = p.b_col; a.b_batch = p.b_batch; a.b_reduce = p.b_reduce;
-    a.c_row = p.c_row; a.c_batch = p.c_batch; a.accumulate = p.accumulate;
+    a.c_row = p.c_row; a.c_batch = p.c_batch; a.accumulate = p.accumulate; a.bias = p.bias;
     a.tiles_m = (p.m + BM - 1) / BM; a.tiles_n = (p.n + BN - 1) / BN;
     a.k_blocks = (p.k + rpb_tf32::BK - 1) / rpb_tf32::BK;
     a.k_iters = a.k_blocks * p.reduce;
@@ -284,7 +285,7 @@ int launch_tf32_cfg(const RpbProblem& p, void* C, const void* A, const void* B, 
     if (a.splits > 1) {
         rpb_simt::launch_splitk_reduce<float, float>(reinterpret_cast<const float*>(a.partial), reinterpret_cast<float*>(C),
                                                      a.splits, p.batch, p.m, p.n, p.c_row, p.c_batch, p.accumulate,
-                                                     d->sm_count, stream);
+                                                     p.bias, d->sm_count, stream);
         g_launches++;
         if (release_scratch(d, stream)) return -1;
     }
@@ -501,6 +502,7 @@ int launch_umma(const RpbProblem& p, void* C, const void* A, const void* B, Devi
     a.a_batch_mul = pa.batch_mul; a.a_reduce_mul = pa.reduce_mul;
     a.b_batch_mul = pb.batch_mul; a.b_reduce_mul = pb.reduce_mul;
     a.c = C; a.c_row = p.c_row; a.c_batch = p.c_batch; a.accumulate = p.accumulate;
+    a.bias = p.bias;
     a.partial = nullptr;
     if (a.splits > 1) {
         void* ws = nullptr;
@@ -550,7 +552,7 @@ int launch_umma(const RpbProblem& p, void* C, const void* A, const void* B, Devi
     if (rc) return -1;
     if (a.splits > 1) {
         rpb_simt::launch_splitk_reduce<T, float>(a.partial, reinterpret_cast<T*>(C), a.splits, p.batch, p.m, p.n, p.c_row,
-                                                 p.c_batch, p.accumulate, d->sm_count, stream);
+                                                 p.c_batch, p.accumulate, p.bias, d->sm_count, stream);
         g_launches++;
         RPB_CUDA(cudaGetLastError());
         if (release_scratch(d, stream)) return -1;
@@ -625,6 +627,29 @@ int run_gemm(const RpbProblem& in, void* C, const void* A, const void* B, int de
     return -1;
 }
 
+template <typename T, typename Acc>
+int run_colsum(void* out, const void* in, long long rows, int cols, long long ld, int accumulate, DeviceState* d,
+               cudaStream_t stream) {
+    const int col_blocks = (cols + rpb_cols::COLS - 1) / rpb_cols::COLS;
+    long long slabs = (4LL * d->sm_count + col_blocks - 1) / col_blocks;
+    const long long max_slabs = (rows + 31) / 32;
+    if (slabs > max_slabs) slabs = max_slabs;
+    if (slabs > 4096) slabs = 4096;
+    if (slabs < 1) slabs = 1;
+    const long long rows_per_block = (rows + slabs - 1) / slabs;
+    slabs = (rows + rows_per_block - 1) / rows_per_block;
+    void* scratch = nullptr;
+    if (get_scratch(d, sizeof(Acc) * (size_t)slabs * cols, stream, &scratch)) return -1;
+    rpb_cols::partial_kernel<T, Acc><<<dim3(col_blocks, (unsigned)slabs), rpb_cols::COLS * rpb_cols::LANES, 0, stream>>>(
+        reinterpret_cast<const T*>(in), reinterpret_cast<Acc*>(scratch), rows, cols, ld, rows_per_block);
+    rpb_cols::final_kernel<T, Acc><<<(cols + 127) / 128, 128, 0, stream>>>(
+        reinterpret_cast<const Acc*>(scratch), reinterpret_cast<T*>(out), (int)slabs, cols, accumulate);
+    g_launches += 2;
+    if (release_scratch(d, stream)) return -1;
+    RPB_CUDA(cudaGetLastError());
+    return 0;
+}
+
 /* The unmodified RecPulse extension, when one is loaded in this process (host tensors are its job). */
 void* reference_symbol(const char* name) {
     static void* handle = nullptr;
@@ -668,10 +693,33 @@ int rp_matmul_ex(void* C, const void* A, const void* B, const RpbGemm* g, DType 
     p.a_row = g->a_row; p.a_col = g->a_col; p.a_batch = g->a_batch; p.a_reduce = g->a_reduce;
     p.b_row = g->b_row; p.b_col = g->b_col; p.b_batch = g->b_batch; p.b_reduce = g->b_reduce;
     p.c_row = g->c_row; p.c_batch = g->c_batch; p.accumulate = g->accumulate; p.dtype = (int)dtype;
+    p.bias = g->bias;
     int prev = -1;
     RPB_CUDA(cudaGetDevice(&prev));
     if (prev != device_id) RPB_CUDA(cudaSetDevice(device_id));
     int rc = run_gemm(p, C, A, B, device_id, reinterpret_cast<cudaStream_t>(stream));
+    if (prev != device_id) cudaSetDevice(prev);
+    return rc;
+}
+
+int rp_colsum_ex(void* out, const void* in, long long rows, int cols, long long row_stride, DType dtype,
+                 int accumulate, int device_id, void* stream) {
+    if (!out || !in || rows <= 0 || cols <= 0 || row_stride < cols || device_id < 0) return -1;
+    int prev = -1;
+    RPB_CUDA(cudaGetDevice(&prev));
+    if (prev != device_id) RPB_CUDA(cudaSetDevice(device_id));
+    DeviceState* d = nullptr;
+    int rc = device_state(device_id, &d);
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    if (!rc) {
+        switch ((int)dtype) {
+            case DTYPE_FLOAT32: rc = run_colsum<float, float>(out, in, rows, cols, row_stride, accumulate, d, s); break;
+            case DTYPE_FLOAT64: rc = run_colsum<double, double>(out, in, rows, cols, row_stride, accumulate, d, s); break;
+            case DTYPE_FLOAT16: rc = run_colsum<__half, float>(out, in, rows, cols, row_stride, accumulate, d, s); break;
+            case DTYPE_BFLOAT16: rc = run_colsum<__nv_bfloat16, float>(out, in, rows, cols, row_stride, accumulate, d, s); break;
+            default: rc = -1;
+        }
+    }
     if (prev != device_id) cudaSetDevice(prev);
     return rc;
 }
@@ -686,7 +734,7 @@ int matmul_kernel_device(void* C, const void* A, const void* B, int m, int k, in
     p.m = m; p.n = n; p.k = k; p.batch = 1; p.reduce = 1;
     p.a_row = g.a_row; p.a_col = 1; p.a_batch = 0; p.a_reduce = 0;
     p.b_row = g.b_row; p.b_col = 1; p.b_batch = 0; p.b_reduce = 0;
-    p.c_row = n; p.c_batch = 0; p.accumulate = 0; p.dtype = (int)dtype;
+    p.c_row = n; p.c_batch = 0; p.accumulate = 0; p.dtype = (int)dtype; p.bias = nullptr;
     if (run_gemm(p, C, A, B, dev, nullptr)) return -1;
     RPB_CUDA(cudaStreamSynchronize(nullptr));
     return 0;
@@ -883,7 +931,7 @@ int noalloc_launch(void* C, const void* A, const void* B, int m, int k, int n, i
         const long long elems = (long long)m * n;
         int rb = (int)((elems + 255) / 256); if (rb > d->sm_count * 8) rb = d->sm_count * 8;
         rpb_simt::splitk_reduce_kernel<T, float><<<rb, 256, 0, stream>>>(a.partial, reinterpret_cast<T*>(C), a.splits, 1,
-                                                                        m, n, n, 0, 0);
+                                                                        m, n, n, 0, 0, nullptr);
         g_launches++;
         RPB_CUDA(cudaGetLastError());
     }

@@ -38,6 +38,7 @@ struct Args {
     int tiles_m, tiles_n;
     int k_blocks, k_iters, splits, iters_per_split;
     void* partial;          /* [splits][batch][m][n] in the accumulation type, when splits > 1 */
+    const void* bias;       /* n values of T added to every output row (applied by the reduction when K is split) */
 };
 
 template <typename T, typename Acc, int BM, int BN, int BK, int TM, int TN>
@@ -136,6 +137,7 @@ gemm_kernel(const Args p)
                 if (gj >= p.n) continue;
                 T* dst = C + (long long)gi * p.c_row + gj;
                 Acc v = acc[i][j];
+                if (p.bias) v += widen<Acc, T>(reinterpret_cast<const T*>(p.bias)[gj]);
                 if (p.accumulate) v += widen<Acc, T>(*dst);
                 *dst = narrow<T, Acc>(v);
             }
@@ -146,7 +148,7 @@ gemm_kernel(const Args p)
 /* Adds the partial tiles of a K-split GEMM in split order and writes C (or C += sum). */
 template <typename T, typename Acc>
 __global__ void splitk_reduce_kernel(const Acc* __restrict__ partial, T* c, int splits, int batch,
-                                     int m, int n, long long c_row, long long c_batch, int accumulate)
+                                     int m, int n, long long c_row, long long c_batch, int accumulate, const T* bias)
 {
     const long long per_split = (long long)batch * m * n;
     const long long stride = (long long)gridDim.x * blockDim.x;
@@ -158,6 +160,7 @@ __global__ void splitk_reduce_kernel(const Acc* __restrict__ partial, T* c, int 
         const int row = (int)(t % m);
         const int bz = (int)(t / m);
         T* dst = c + bz * c_batch + (long long)row * c_row + col;
+        if (bias) s += widen<Acc, T>(bias[col]);
         if (accumulate) s += widen<Acc, T>(*dst);
         *dst = narrow<T, Acc>(s);
     }
@@ -170,7 +173,7 @@ __global__ void splitk_reduce_kernel(const Acc* __restrict__ partial, T* c, int 
 template <typename T, typename Acc>
 __global__ void __launch_bounds__(256)
 splitk_reduce_vec_kernel(const Acc* __restrict__ partial, T* c, int splits, int batch, int m, int n,
-                         long long c_row, long long c_batch, int accumulate)
+                         long long c_row, long long c_batch, int accumulate, const T* bias)
 {
     constexpr int GROUPS = 8, VECS = 32;
     __shared__ Acc red[GROUPS][VECS][4];
@@ -211,6 +214,7 @@ splitk_reduce_vec_kernel(const Acc* __restrict__ partial, T* c, int splits, int 
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 Acc x = s[e];
+                if (bias) x += widen<Acc, T>(bias[col + e]);
                 if (accumulate) x += widen<Acc, T>(dst[e]);
                 dst[e] = narrow<T, Acc>(x);
             }
@@ -221,16 +225,17 @@ splitk_reduce_vec_kernel(const Acc* __restrict__ partial, T* c, int splits, int 
 
 template <typename T, typename Acc>
 inline void launch_splitk_reduce(const Acc* partial, T* c, int splits, int batch, int m, int n, long long c_row,
-                                 long long c_batch, int accumulate, int sm_count, cudaStream_t stream) {
+                                 long long c_batch, int accumulate, const void* bias_v, int sm_count, cudaStream_t stream) {
+    const T* bias = reinterpret_cast<const T*>(bias_v);
     const long long elems = (long long)batch * m * n;
     if (n % 4 == 0 && splits >= 4) {
         long long blocks = (elems / 4 + 31) / 32;
         if (blocks > sm_count * 8) blocks = sm_count * 8;
-        splitk_reduce_vec_kernel<T, Acc><<<(unsigned)blocks, 256, 0, stream>>>(partial, c, splits, batch, m, n, c_row, c_batch, accumulate);
+        splitk_reduce_vec_kernel<T, Acc><<<(unsigned)blocks, 256, 0, stream>>>(partial, c, splits, batch, m, n, c_row, c_batch, accumulate, bias);
     } else {
         long long blocks = (elems + 255) / 256;
         if (blocks > sm_count * 8) blocks = sm_count * 8;
-        splitk_reduce_kernel<T, Acc><<<(unsigned)blocks, 256, 0, stream>>>(partial, c, splits, batch, m, n, c_row, c_batch, accumulate);
+        splitk_reduce_kernel<T, Acc><<<(unsigned)blocks, 256, 0, stream>>>(partial, c, splits, batch, m, n, c_row, c_batch, accumulate, bias);
     }
 }
 

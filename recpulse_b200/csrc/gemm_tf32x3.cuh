@@ -189,6 +189,7 @@ gemm_kernel(const rpb_simt::Args p)
                     if (to_partial) P[(long long)r * p.n + c + e] = v;
                     else {
                         float* dst = Cout + (long long)r * p.c_row + c + e;
+                        if (p.bias) v += reinterpret_cast<const float*>(p.bias)[c + e];
                         if (p.accumulate) v += *dst;
                         *dst = v;
                     }

@@ -67,6 +67,7 @@ struct Args {
     int accumulate;
     int tma_store;         /* 1: the epilogue writes through shared memory + TMA store (map_c), 0: register stores */
     float* partial;        /* [splits][batch][m][n] fp32 when splits > 1 */
+    const void* bias;      /* n values of T added to every row (by the reduction pass when K is split), or null */
     uint32_t idesc;        /* tcgen05 instruction descriptor */
     uint64_t a_desc_base, b_desc_base;   /* shared-memory descriptors without start address */
     uint32_t a_kstep, b_kstep;           /* descriptor advance per UMMA_K, in 16-byte units */
@@ -227,6 +228,25 @@ template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, f
 template <> __device__ __forceinline__ uint32_t pack2<__half>(float lo, float hi) {
     const __half2 v = __floats2half2_rn(lo, hi);
     return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+/* v[j] += bias[col + j] for the 32 columns a thread holds; columns >= n are left alone */
+template <typename T>
+__device__ __forceinline__ void add_bias_32(uint32_t (&v)[32], const T* bias, int col, int n) {
+    const T* bp = bias + col;
+    if (col + 32 <= n && (reinterpret_cast<uintptr_t>(bp) & 15u) == 0) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const uint4 raw = __ldg(reinterpret_cast<const uint4*>(bp) + q);
+            const T* b8 = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[8 * q + e] = __float_as_uint(__uint_as_float(v[8 * q + e]) + to_f32<T>(b8[e]));
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+            if (col + j < n) v[j] = __float_as_uint(__uint_as_float(v[j]) + to_f32<T>(bp[j]));
+    }
 }
 
 /* ------------------------------------------------------------------ kernel */
@@ -431,6 +451,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                     if (!partial_out) tmem_load_32_nowait(tmem_base + ab * ACC_N + c0 + 32 + lane_field, v2);
                     tmem_load_wait();
                     if (col >= args.n || row_warp >= args.m) continue;      /* warp-uniform */
+                    if (args.bias && !partial_out) {
+                        add_bias_32<T>(v, reinterpret_cast<const T*>(args.bias), col, args.n);
+                        add_bias_32<T>(v2, reinterpret_cast<const T*>(args.bias), col + 32, args.n);
+                    }
                     if (lane == 0) tma_store_wait_read<0>();                /* the previous store has read `buf` */
                     __syncwarp();
                     if (partial_out) {
@@ -483,6 +507,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                     }
                 } else {
                     T* dst = cT + bz * args.c_batch + (long long)row * args.c_row + col;
+                    if (args.bias) add_bias_32<T>(v, reinterpret_cast<const T*>(args.bias), col, args.n);
                     if (col + 32 <= args.n && ((reinterpret_cast<uintptr_t>(dst) & 15u) == 0)) {
 #pragma unroll
                         for (int j = 0; j < 32; j += 8) {

@@ -254,7 +254,14 @@ static long long batch_stride(const Tensor* t, int nd, int i) {
 
 /* ------------------------------------------------------------------ autograd node */
 
-Tensor* op_matmul(Tensor* a, Tensor* b) {
+static bool bias_ok(const Tensor* bias, const Tensor* a, int n) {
+    if (bias->dtype != a->dtype || bias->device_id != a->device_id) return false;
+    if ((int)bias->size != n || bias->shape[bias->ndim - 1] != n || bias->strides[bias->ndim - 1] != 1) return false;
+    return true;
+}
+
+/* shared by op_matmul (bias == NULL) and op_linear */
+static Tensor* matmul_node(Tensor* a, Tensor* b, Tensor* bias) {
     if (!a || !b) return NULL;
     if (a->ndim < 2 || b->ndim < 2) return NULL;
     if (a->shape[a->ndim - 1] != b->shape[b->ndim - 2]) return NULL;
@@ -263,10 +270,11 @@ Tensor* op_matmul(Tensor* a, Tensor* b) {
         /* host tensors stay with RecPulse's own implementation when it is loaded */
         typedef Tensor* (*Fn)(Tensor*, Tensor*);
         Fn ref = (Fn)rpb_reference_symbol("op_matmul");
-        if (ref && ref != &op_matmul) return ref(a, b);
-        fprintf(stderr, "recpulse_b200: op_matmul on host tensors: this library has no CPU path\n");
+        if (!bias && ref && ref != &op_matmul) return ref(a, b);
+        fprintf(stderr, "recpulse_b200: matmul on host tensors: this library has no CPU path\n");
         return NULL;
     }
+    if (bias && !bias_ok(bias, a, b->shape[b->ndim - 1])) return NULL;
 
     const int m = a->shape[a->ndim - 2], k = a->shape[a->ndim - 1], n = b->shape[b->ndim - 1];
     int nd = 0, oshape[RPB_MAX_BATCH_DIMS + 2];
@@ -281,6 +289,7 @@ Tensor* op_matmul(Tensor* a, Tensor* b) {
     g.a_row = a->strides[a->ndim - 2]; g.a_col = a->strides[a->ndim - 1];
     g.b_row = b->strides[b->ndim - 2]; g.b_col = b->strides[b->ndim - 1];
     g.a_batch = g.b_batch = g.c_batch = 0;
+    g.bias = bias ? bias->data : NULL;
     BatchDim bd[RPB_MAX_BATCH_DIMS];
     int nbd = 0;
     for (int i = 0; i < nd; i++) {
@@ -294,22 +303,25 @@ Tensor* op_matmul(Tensor* a, Tensor* b) {
     if (rc == 0 && cudaStreamSynchronize(NULL) != cudaSuccess) rc = -1;
     if (rc != 0) { rpb_tensor_release(out); return NULL; }
 
-    const bool needs_grad = (a->metadata && a->metadata->requires_grad) || (b->metadata && b->metadata->requires_grad);
+    const bool needs_grad = (a->metadata && a->metadata->requires_grad) || (b->metadata && b->metadata->requires_grad) ||
+                            (bias && bias->metadata && bias->metadata->requires_grad);
     if (needs_grad) {
+        const int n_in = bias ? 3 : 2;
         out->metadata = (Meta*)calloc(1, sizeof(Meta));
         GradFn* fn = (GradFn*)calloc(1, sizeof(GradFn));
-        Tensor** inputs = (Tensor**)malloc(2 * sizeof(Tensor*));
+        Tensor** inputs = (Tensor**)malloc(n_in * sizeof(Tensor*));
         if (!out->metadata || !fn || !inputs) { free(fn); free(inputs); rpb_tensor_release(out); return NULL; }
         out->metadata->requires_grad = true;
         out->metadata->is_leaf = false;
-        fn->backward = backward_matmul_fn;
-        fn->num_inputs = 2;
+        fn->backward = bias ? backward_linear_fn : backward_matmul_fn;
+        fn->num_inputs = n_in;
         fn->inputs = inputs;
         inputs[0] = a; inputs[1] = b;
+        if (bias) inputs[2] = bias;
         fn->saved_data = NULL;
         /* grad_fn_attach, ops/ops.c:11-19 */
         fn->owner = out;
-        for (int i = 0; i < 2; i++) if (inputs[i] != out) inputs[i]->refcount++;
+        for (int i = 0; i < n_in; i++) if (inputs[i] != out) inputs[i]->refcount++;
         out->metadata->grad_fn = fn;
     }
     return out;
@@ -379,6 +391,23 @@ static int grad_into(Tensor* x, const Tensor* other, const Tensor* grad_output, 
     return 0;
 }
 
+Tensor* op_matmul(Tensor* a, Tensor* b) { return matmul_node(a, b, NULL); }
+
+Tensor* op_linear(Tensor* x, Tensor* w, Tensor* bias) { return matmul_node(x, w, bias); }
+
+/* dA and dB of a device matmul node; 0 when grad_output matches the node */
+static int matmul_grads(Tensor* a, Tensor* b, Tensor* grad_output) {
+    int nd = 0, oshape[RPB_MAX_BATCH_DIMS + 2];
+    if (broadcast_batch(a, b, &nd, oshape)) return -1;
+    if (grad_output->ndim != nd + 2 || grad_output->dtype != a->dtype || grad_output->device_id != a->device_id) {
+        fprintf(stderr, "recpulse_b200: matmul backward: upstream gradient does not match the output\n");
+        return -1;
+    }
+    if (a->metadata && a->metadata->requires_grad) grad_into(a, b, grad_output, 0, nd, oshape);
+    if (b->metadata && b->metadata->requires_grad) grad_into(b, a, grad_output, 1, nd, oshape);
+    return 0;
+}
+
 void backward_matmul_fn(GradFn* self, Tensor* grad_output) {
     if (!self || !grad_output || self->num_inputs != 2 || !self->inputs) return;
     Tensor* a = self->inputs[0];
@@ -390,14 +419,37 @@ void backward_matmul_fn(GradFn* self, Tensor* grad_output) {
         if (ref && ref != &backward_matmul_fn) ref(self, grad_output);
         return;
     }
-    int nd = 0, oshape[RPB_MAX_BATCH_DIMS + 2];
-    if (broadcast_batch(a, b, &nd, oshape)) return;
-    if (grad_output->ndim != nd + 2 || grad_output->dtype != a->dtype || grad_output->device_id != a->device_id) {
-        fprintf(stderr, "recpulse_b200: backward_matmul_fn: upstream gradient does not match the output\n");
+    matmul_grads(a, b, grad_output);
+}
+
+/* dX and dW as for op_matmul; dbias = sum of dY over every leading index (assigned, or accumulated
+ * into an existing grad with one rounding) */
+void backward_linear_fn(GradFn* self, Tensor* grad_output) {
+    if (!self || !grad_output || self->num_inputs != 3 || !self->inputs) return;
+    Tensor* x = self->inputs[0];
+    Tensor* w = self->inputs[1];
+    Tensor* bias = self->inputs[2];
+    if (!x || !w || !bias || x->device_id < 0) return;
+    if (matmul_grads(x, w, grad_output)) return;
+    if (!(bias->metadata && bias->metadata->requires_grad)) return;
+    if (!is_contiguous(grad_output)) {
+        fprintf(stderr, "recpulse_b200: backward_linear_fn: upstream gradient must be packed for the bias gradient\n");
         return;
     }
-    if (a->metadata && a->metadata->requires_grad) grad_into(a, b, grad_output, 0, nd, oshape);
-    if (b->metadata && b->metadata->requires_grad) grad_into(b, a, grad_output, 1, nd, oshape);
+    const int n = grad_output->shape[grad_output->ndim - 1];
+    const long long rows = (long long)(grad_output->size / (size_t)n);
+    Tensor* grad = bias->metadata->grad;
+    const bool fresh = grad == NULL;
+    if (fresh) {
+        grad = rpb_tensor_empty(bias->dtype, bias->ndim, bias->shape, bias->device_id);
+        if (!grad) return;
+    } else if (!is_contiguous(grad) || grad->size != bias->size) {
+        return;
+    }
+    int rc = rp_colsum_ex(grad->data, grad_output->data, rows, n, n, bias->dtype, fresh ? 0 : 1, bias->device_id, NULL);
+    if (rc == 0 && cudaStreamSynchronize(NULL) != cudaSuccess) rc = -1;
+    if (rc != 0) { if (fresh) rpb_tensor_release(grad); return; }
+    if (fresh) bias->metadata->grad = grad;
 }
 
 int rpb_backward_node(Tensor* out, Tensor* grad_output) {

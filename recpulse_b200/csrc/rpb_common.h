@@ -16,6 +16,7 @@ struct RpbProblem {
     long long c_row, c_batch;
     int accumulate;
     int dtype;                 /* DType code */
+    const void* bias;          /* n values of dtype, or NULL */
 };
 
 static inline size_t rpb_dtype_size(int dtype) {

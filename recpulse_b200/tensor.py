@@ -145,6 +145,13 @@ class Tensor:
             raise RuntimeError("op_matmul operation failed")     # python/tensor_python.c:2293-2297
         return Tensor(p, keepalive=(self, other))
 
+    def op_linear(self, weight: "Tensor", bias: "Tensor | None") -> "Tensor":
+        """y = self . weight + bias as one node (bias added in the GEMM epilogue)."""
+        p = _lib.load().op_linear(self._p, weight._p, bias._p if bias is not None else None)
+        if not p:
+            raise RuntimeError("op_linear operation failed")
+        return Tensor(p, keepalive=(self, weight, bias))
+
     def backward(self, grad_output: "Tensor") -> None:
         """Run this node's backward with an explicit upstream gradient and free the node."""
         if _lib.load().rpb_backward_node(self._p, grad_output._p) != 0:

@@ -22,3 +22,14 @@ def golden():
         name, dtype, field = key.split("/")
         cases.setdefault((name, dtype), {})[field] = z[key]
     return cases
+
+
+@pytest.fixture(scope="session")
+def linear_golden():
+    import numpy as np
+    z = np.load(os.path.join(ROOT, "tests", "golden", "linear_golden.npz"))
+    cases = {}
+    for key in z.files:
+        name, dtype, field = key.split("/")
+        cases.setdefault((name, dtype), {})[field] = z[key]
+    return cases

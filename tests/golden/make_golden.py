@@ -67,6 +67,21 @@ def run_case(name, dtype, m, k, n, rng, ta=False, tb=False, twice=False, scale=1
     return {f"{name}/{dtype}/{key}": val for key, val in out.items()}
 
 
+def run_linear(name, dtype, m, k, n, rng):
+    """x @ W + b exactly as recpulse/module.py:110-114 composes it, with loss = sum(y * w)."""
+    x64 = rng.uniform(-1, 1, (m, k)); w64 = rng.uniform(-1, 1, (k, n)) / np.sqrt(k)
+    b64 = rng.uniform(-1, 1, (n,)); g64 = rng.uniform(-1, 1, (m, n))
+    x = to_rp(x64, dtype); w = to_rp(w64, dtype); b = to_rp(b64, dtype); g = to_rp(g64, dtype)
+    for t in (x, w, b):
+        t.requires_grad_(True)
+    y = x.op_matmul(w).op_add(b)
+    loss = y.op_mul(g).op_sum_all()
+    loss.backward()
+    out = {"x": bits(x), "w": bits(w), "b": bits(b), "g": bits(g), "y": bits(y),
+           "dx": bits(x.grad), "dw": bits(w.grad), "db": bits(b.grad)}
+    return {f"{name}/{dtype}/{key}": val for key, val in out.items()}
+
+
 def main():
     rng = np.random.default_rng(20240607)
     store = {}
@@ -81,6 +96,13 @@ def main():
         store.update(run_case("big_40x130x50", dtype, 40, 130, 50, rng, scale=4.0))
     np.savez_compressed(os.path.join(HERE, "matmul_golden.npz"), **store)
     print("cases:", len(store) // 7)
+    lin = {}
+    rng = np.random.default_rng(20240608)
+    for dtype in DT:
+        for (m, k, n) in [(5, 7, 3), (32, 48, 16), (17, 33, 40)]:
+            lin.update(run_linear(f"linear_{m}x{k}x{n}", dtype, m, k, n, rng))
+    np.savez_compressed(os.path.join(HERE, "linear_golden.npz"), **lin)
+    print("linear cases:", len(lin) // 8)
 
 
 if __name__ == "__main__":

@@ -142,3 +142,64 @@ def test_no_grad_no_node_and_refcounts(lib):
     assert (a._t.refcount, b._t.refcount) == before          # node freed, inputs released
     assert a.grad is not None and b.grad is None             # only inputs that require grad get one
     assert np.array_equal(a.grad.to_numpy(), np.full((4, 4), 4, np.float32))
+
+
+@pytest.mark.parametrize("family", [_lib.KERNEL_SIMT, 0])
+@pytest.mark.parametrize("dtype", ["float32", "float64", "float16", "bfloat16"])
+def test_linear_node_vs_reference_fixtures(lib, linear_golden, dtype, family):
+    """op_linear (bias in the GEMM epilogue, bias gradient on the device) against the reference's
+    op_matmul + op_add composition."""
+    lib.rpb_force_kernel(family)
+    for (name, dt), case in linear_golden.items():
+        if dt != dtype:
+            continue
+        m, k = case["x"].shape; n = case["w"].shape[1]
+        x = T(case["x"], dtype, True); w = T(case["w"], dtype, True); b = T(case["b"], dtype, True)
+        y = x.op_linear(w, b)
+        check_close(y.to_numpy(), case["y"], dtype, k, f"{name} y")
+        y.backward(T(case["g"], dtype))
+        check_close(x.grad.to_numpy(), case["dx"], dtype, n, f"{name} dx")
+        check_close(w.grad.to_numpy(), case["dw"], dtype, m, f"{name} dw")
+        assert b.grad.shape == (n,)
+        check_close(b.grad.to_numpy(), case["db"], dtype, m, f"{name} dbias")
+    lib.rpb_force_kernel(0)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "float64", "float16", "bfloat16"])
+def test_linear_node_larger_shapes_and_accumulation(lib, dtype):
+    rng = np.random.default_rng(61)
+    for lead, k, n in [((512,), 256, 384), ((4, 96), 64, 128), ((1000,), 136, 264), ((64,), 4096, 136)]:
+        x = rand_operand(rng, lead + (k,), dtype); w = rand_operand(rng, (k, n), dtype, scale=1 / np.sqrt(k))
+        b = rand_operand(rng, (n,), dtype); g = rand_operand(rng, lead + (n,), dtype)
+        X = T(x, dtype, True); W = T(w, dtype, True); B = T(b, dtype, True)
+        y = X.op_linear(W, B)
+        assert y.shape == lead + (n,)
+        check_close(y.to_numpy(), O.linear_forward(x, w, b, CODE[dtype]), dtype, k, "y")
+        y.backward(T(g, dtype))
+        rows = int(np.prod(lead))
+        check_close(B.grad.to_numpy(), O.bias_grad(g, CODE[dtype]), dtype, rows, "dbias")
+        dx, dw = O.matmul_backward(x.reshape(rows, k), w, g.reshape(rows, n), CODE[dtype])
+        check_close(X.grad.to_numpy().reshape(rows, k), dx, dtype, n, "dx")
+        check_close(W.grad.to_numpy(), dw, dtype, rows, "dw")
+        # a second use of the same parameters accumulates into the existing grads (weight sharing)
+        y2 = X.op_linear(W, B)
+        y2.backward(T(g, dtype))
+        from helpers import f64
+        got = f64(B.grad.to_numpy(), dtype); ref = 2 * f64(O.bias_grad(g, CODE[dtype]), dtype)
+        tol = {"float32": 1e-5, "float64": 1e-12, "float16": 2e-3, "bfloat16": 1e-2}[dtype]
+        assert np.linalg.norm(got - ref) / np.linalg.norm(ref) < tol
+    # bias of the wrong length or dtype is rejected
+    with pytest.raises(RuntimeError):
+        T(x, dtype).op_linear(T(w, dtype), T(rand_operand(rng, (n + 1,), dtype), dtype))
+
+
+def test_colsum_entry_point(lib):
+    import ctypes as C
+    rng = np.random.default_rng(67)
+    for dtype in ("float32", "bfloat16", "float64"):
+        for rows, cols, pad in [(1, 5, 0), (33, 70, 2), (5000, 130, 6), (70000, 64, 0)]:
+            x = rand_operand(rng, (rows, cols + pad), dtype)
+            tin = T(x, dtype); tout = T(np.zeros((cols,), O.storage(CODE[dtype])), dtype)
+            assert lib.rp_colsum_ex(C.c_void_p(tout.data_ptr), C.c_void_p(tin.data_ptr), rows, cols, cols + pad, CODE[dtype],
+                                    0, 0, None) == 0
+            check_close(tout.to_numpy(), O.bias_grad(np.ascontiguousarray(x[:, :cols]), CODE[dtype]), dtype, rows, "colsum")

@@ -132,3 +132,19 @@ def test_against_compiled_reference_rp_matmul():
                                b.ctypes.data_as(ctypes.c_void_p), m, k, n, dtype, -1)
             assert rc == 0
             assert np.array_equal(O.rp_matmul(a, b, dtype), exp), (dtype, m, k, n)
+
+
+@pytest.mark.parametrize("dtype", list(CODE))
+def test_linear_composition_bit_exact_vs_reference_fixtures(linear_golden, dtype):
+    """x @ W + b and its three gradients as the reference composes them (module.py:110-114)."""
+    seen = 0
+    for (name, dt), case in linear_golden.items():
+        if dt != dtype:
+            continue
+        seen += 1
+        code = CODE[dtype]
+        assert np.array_equal(O.linear_forward(case["x"], case["w"], case["b"], code), case["y"]), name
+        dx, dw = O.matmul_backward(case["x"], case["w"], case["g"], code)
+        assert np.array_equal(dx, case["dx"]) and np.array_equal(dw, case["dw"]), name
+        assert np.array_equal(O.bias_grad(case["g"], code), case["db"]), name
+    assert seen == 3
