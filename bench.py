@@ -59,6 +59,7 @@ def parse():
     p.add_argument("--e2e-steps", type=int, default=3)
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--no-e2e", action="store_true")
+    p.add_argument("--no-graph", action="store_true", help="do not replay the step from a CUDA graph on launch-bound workloads")
     p.add_argument("--compare", action="store_true", help="also time torch.matmul (cuBLAS, warm handle) on the same step")
     p.add_argument("--rows", type=int, default=0, help="override the row count M of the workload (profiling cases)")
     return p.parse_args()
@@ -332,6 +333,22 @@ def main():
     flush = None
     if resident < (512 << 20):
         flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)     # > 126 MB of L2
+    # Launch-bound workloads (a few microseconds of GPU work per launch) are replayed from a CUDA graph, the way
+    # a training loop would run them: the host cost of issuing each launch disappears from the timed region.
+    graph = None
+    launches_per_step = None
+    if flush is not None and world == 1 and not args.no_graph:
+        side = torch.cuda.Stream(dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        n0 = lib.rpb_launch_count()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            step()
+        launches_per_step = lib.rpb_launch_count() - n0
+        torch.cuda.synchronize(dev)
+        for _ in range(3):
+            graph.replay()
+        torch.cuda.synchronize(dev)
     step_ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
     # per-launch events for the roofline of the dominant kernel (forward GEMM of every step)
     fwd_ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
@@ -340,15 +357,23 @@ def main():
         if flush is not None:
             flush.fill_(i & 1)                      # evict the operands from L2 (outside the timed events)
         step_ev[i][0].record(stream)
-        op.forward(A, out=Cc)
-        fwd_ev[i].record(stream)
-        op.backward(A, dC, da_out=dA, db_out=dB)
+        if graph is not None:
+            graph.replay()
+            fwd_ev[i].record(stream)
+        else:
+            op.forward(A, out=Cc)
+            fwd_ev[i].record(stream)
+            op.backward(A, dC, da_out=dA, db_out=dB)
         step_ev[i][1].record(stream)
     barrier()
     elapsed_ms = sum(a.elapsed_time(b) for a, b in step_ev)
     launches = lib.rpb_launch_count() - launches0
+    if graph is not None:
+        launches = launches_per_step * args.steps          # counted while capturing; each replay re-issues them
     clocks = sampler.stop() if rank == 0 else None
     fwd_ms = sum(step_ev[i][0].elapsed_time(fwd_ev[i]) for i in range(args.steps)) / args.steps
+    if graph is not None:
+        fwd_ms = elapsed_ms / args.steps        # the replayed step is one unit: the roofline below is per STEP
     if world > 1:
         t = torch.tensor([elapsed_ms], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -447,20 +472,23 @@ def main():
         pk = peaks()
         half = dtype_name in ("bfloat16", "float16")
         flops_fwd = 2.0 * rows * k * n                               # one launch of the dominant kernel on this rank
+        bytes_unit = (rows * k + k * n + rows * n) * es              # algorithmic bytes of that launch
+        unit = "forward GEMM launch"
+        if graph is not None:                                        # whole replayed step: three GEMMs
+            flops_fwd *= 3; bytes_unit *= 3; unit = "fwd+bwd step replayed from a CUDA graph"
         traffic_fn = NCU_TRAFFIC_BYTES.get(args.workload)
         traffic = traffic_fn(rows) if traffic_fn else None
         if half and args.workload != "bmm_fp16":
             achieved = flops_fwd / (fwd_ms * 1e-3) / 1e12
-            roof = {"bound": "tensor", "kernel": "rpb_umma::gemm_kernel (forward GEMM launch)", "achieved": achieved,
+            roof = {"bound": "tensor", "kernel": "rpb_umma::gemm_kernel (" + unit + ")", "achieved": achieved,
                     "peak": pk["tflops"], "unit": "TFLOP/s", "frac": achieved / pk["tflops"],
                     "peak_source": pk["src"] + " cuBLAS bf16, sustained", "traffic": traffic,
                     "traffic_note": "ncu DRAM bytes of one forward launch at 8192 rows, scaled by rows" if traffic else None,
-                    "algorithmic_bytes": (rows * k + k * n + rows * n) * es,
+                    "algorithmic_bytes": bytes_unit,
                     "avg_launch_ms": fwd_ms}
         else:
-            bytes_fwd = (rows * k + k * n + rows * n) * es
-            achieved = bytes_fwd / (fwd_ms * 1e-3) / 1e9
-            roof = {"bound": "hbm", "kernel": "forward GEMM launch", "achieved": achieved, "peak": pk["hbm"], "unit": "GB/s",
+            achieved = bytes_unit / (fwd_ms * 1e-3) / 1e9
+            roof = {"bound": "hbm", "kernel": unit, "achieved": achieved, "peak": pk["hbm"], "unit": "GB/s",
                     "frac": achieved / pk["hbm"], "peak_source": pk["src"] + " copy bandwidth", "traffic": None,
                     "avg_launch_ms": fwd_ms}
         cpu = None
@@ -475,7 +503,7 @@ def main():
             "config": {"workload": args.workload, "m": rows_total, "k": k, "n": n, "rows_per_gpu": rows,
                        "parallelism": f"rows of A over {n_gpus} GPU(s), B replicated, dB all-reduced" if n_gpus > 1 else "single GPU",
                        "l2": "inputs larger than L2, no flush" if flush is None else "L2 flushed (256 MB write) before every step, outside the timed events",
-                       "accumulate": "fp32"},
+                       "accumulate": "fp32", "cuda_graph": graph is not None},
             "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches), "roofline": roof, "cpu_baseline": cpu,
             "pct_of_nominal_dense_peak": value / (2250.0 * n_gpus) if half else None,
         }

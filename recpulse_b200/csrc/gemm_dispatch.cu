@@ -56,6 +56,41 @@ EncodeTiledFn g_encode = nullptr;
         }                                                                                       \
     } while (0)
 
+/* The dynamic shared-memory limit of a kernel is set once per device, not once per launch.  `done` is a
+ * static array owned by the launcher of that one kernel instantiation. */
+template <typename K>
+cudaError_t smem_attr_once(K kern, int bytes, std::atomic<bool>* done) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev >= 0 && dev < MAX_DEVICES && done[dev].load(std::memory_order_acquire)) return cudaSuccess;
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e == cudaSuccess && dev >= 0 && dev < MAX_DEVICES) done[dev].store(true, std::memory_order_release);
+    return e;
+}
+
+/* Encoded tensor maps are reused while the same operand (address, extents, strides, box) comes back,
+ * which is the common case in a training loop: encoding costs about a microsecond per map. */
+struct MapKey {
+    const void* base; unsigned long long d[4], s[3]; unsigned box[4]; int dt, rank, swz;
+    bool operator==(const MapKey& o) const { return memcmp(this, &o, sizeof(MapKey)) == 0; }
+};
+struct MapCache {
+    static constexpr int N = 64;
+    MapKey key[N]; CUtensorMap map[N]; bool used[N] = {}; int next = 0;
+    std::mutex mu;
+    bool get(const MapKey& k, CUtensorMap* out) {
+        std::lock_guard<std::mutex> lock(mu);
+        for (int i = 0; i < N; ++i) if (used[i] && key[i] == k) { *out = map[i]; return true; }
+        return false;
+    }
+    void put(const MapKey& k, const CUtensorMap& m) {
+        std::lock_guard<std::mutex> lock(mu);
+        key[next] = k; map[next] = m; used[next] = true; next = (next + 1) % N;
+    }
+};
+MapCache g_maps;
+
 int forced_family() {
     int f = g_force.load();
     if (f >= 0) return f;
@@ -104,22 +139,35 @@ int device_state(int device_id, DeviceState** out) {
 
 /* Scratch for K-split partial tiles: one buffer per device, grown on demand.  A launch on a
  * stream other than the previous user's first waits for that user's reduction to finish. */
+bool capturing(cudaStream_t stream) {
+    cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+    return cudaStreamIsCapturing(stream, &st) == cudaSuccess && st != cudaStreamCaptureStatusNone;
+}
+
 int get_scratch(DeviceState* d, size_t bytes, cudaStream_t stream, void** out) {
     std::lock_guard<std::mutex> lock(g_mutex);
+    const bool cap = capturing(stream);
     if (bytes > d->scratch_bytes) {
+        if (cap) {
+            fprintf(stderr, "recpulse_b200: the K-split scratch would have to grow during stream capture; run the same "
+                            "shapes once before capturing\n");
+            return -1;
+        }
         if (d->scratch) RPB_CUDA(cudaFree(d->scratch));       /* synchronises the device */
         d->scratch = nullptr; d->scratch_bytes = 0; d->scratch_used = false;
         size_t want = bytes < (size_t(32) << 20) ? (size_t(32) << 20) : bytes + bytes / 4;
         RPB_CUDA(cudaMalloc(&d->scratch, want));
         d->scratch_bytes = want;
     }
-    if (d->scratch_used && d->scratch_stream != stream)
+    /* inside a capture the graph's own edges order the users of the scratch; the guard event stays out of it */
+    if (!cap && d->scratch_used && d->scratch_stream != stream)
         RPB_CUDA(cudaStreamWaitEvent(stream, d->scratch_free, 0));
     *out = d->scratch;
     return 0;
 }
 int release_scratch(DeviceState* d, cudaStream_t stream) {
     std::lock_guard<std::mutex> lock(g_mutex);
+    if (capturing(stream)) return 0;
     RPB_CUDA(cudaEventRecord(d->scratch_free, stream));
     d->scratch_stream = stream;
     d->scratch_used = true;
@@ -176,7 +224,8 @@ int launch_simt_cfg(const RpbProblem& p, void* C, const void* A, const void* B, 
 template <bool A_MN, bool B_MN>
 int launch_dmma_inst(const rpb_simt::Args& a, long long blocks, cudaStream_t stream) {
     auto kern = rpb_dmma::gemm_kernel<A_MN, B_MN>;
-    RPB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, rpb_dmma::SMEM_BYTES));
+    static std::atomic<bool> attr_done[MAX_DEVICES];
+    RPB_CUDA(smem_attr_once(kern, rpb_dmma::SMEM_BYTES, attr_done));
     kern<<<(unsigned)blocks, rpb_dmma::THREADS, rpb_dmma::SMEM_BYTES, stream>>>(a);
     g_launches++;
     return 0;
@@ -244,7 +293,8 @@ template <int BM, int BN, int WM, int WN, bool A_MN, bool B_MN>
 int launch_tf32_inst(const rpb_simt::Args& a, long long blocks, cudaStream_t stream) {
     auto kern = rpb_tf32::gemm_kernel<BM, BN, WM, WN, A_MN, B_MN>;
     constexpr int smem = rpb_tf32::Cfg<BM, BN>::SMEM_BYTES;
-    RPB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    static std::atomic<bool> attr_done[MAX_DEVICES];
+    RPB_CUDA(smem_attr_once(kern, smem, attr_done));
     kern<<<(unsigned)blocks, WM * WN * 32, smem, stream>>>(a);
     g_launches++;
     return 0;
@@ -376,9 +426,16 @@ int encode_map(CUtensorMap* map, const void* base, const OperandPlan& o, int mn,
     box[0] = 64;                                    /* 64 x 2 bytes = the 128-byte swizzle span */
     box[1] = o.mn_major ? rpb_umma::BLOCK_K : box_mn_rows;
     box[2] = 1; box[3] = 1;
+    MapKey key;
+    memset(&key, 0, sizeof(key));
+    key.base = base; key.dt = (int)dt; key.rank = 4; key.swz = 1;
+    for (int i = 0; i < 4; ++i) { key.d[i] = dims[i]; key.box[i] = box[i]; }
+    for (int i = 0; i < 3; ++i) key.s[i] = strides[i];
+    if (g_maps.get(key, map)) return 0;
     CUresult r = g_encode(map, dt, 4, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r == CUDA_SUCCESS) g_maps.put(key, *map);
     if (r != CUDA_SUCCESS) {
         fprintf(stderr, "recpulse_b200: cuTensorMapEncodeTiled failed (%d) dims=[%llu,%llu,%llu,%llu] strides=[%llu,%llu,%llu]\n",
                 (int)r, (unsigned long long)dims[0], (unsigned long long)dims[1], (unsigned long long)dims[2],
@@ -398,8 +455,15 @@ int encode_store_map(CUtensorMap* map, void* base, CUtensorMapDataType dt, int e
     cuuint64_t strides[2] = {s1, s2};
     cuuint32_t box[3] = {(cuuint32_t)box_cols, 32, 1};
     cuuint32_t estr[3] = {1, 1, 1};
+    MapKey key;
+    memset(&key, 0, sizeof(key));
+    key.base = base; key.dt = (int)dt; key.rank = 3; key.swz = 2;
+    for (int i = 0; i < 3; ++i) { key.d[i] = dims[i]; key.box[i] = box[i]; }
+    for (int i = 0; i < 2; ++i) key.s[i] = strides[i];
+    if (g_maps.get(key, map)) return 0;
     CUresult r = g_encode(map, dt, 3, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r == CUDA_SUCCESS) g_maps.put(key, *map);
     return r == CUDA_SUCCESS ? 0 : -1;
 }
 
@@ -425,7 +489,8 @@ int launch_umma_inst(const CUtensorMap& ma, const CUtensorMap& mb, const CUtenso
                      int grid, cudaStream_t stream) {
     using Cfg = rpb_umma::Config<BN>;
     auto kern = rpb_umma::gemm_kernel<T, BN, A_MN, B_MN, PAIR>;
-    RPB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+    static std::atomic<bool> attr_done[MAX_DEVICES];
+    RPB_CUDA(smem_attr_once(kern, Cfg::SMEM_BYTES, attr_done));
     if (PAIR) {
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3((unsigned)grid); cfg.blockDim = dim3(rpb_umma::NUM_THREADS);
