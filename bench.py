@@ -61,6 +61,7 @@ def parse():
     p.add_argument("--no-e2e", action="store_true")
     p.add_argument("--no-graph", action="store_true", help="do not replay the step from a CUDA graph on launch-bound workloads")
     p.add_argument("--compare", action="store_true", help="also time torch.matmul (cuBLAS, warm handle) on the same step")
+    p.add_argument("--comm-sms", type=int, default=16, help="SMs the dA GEMM leaves to the dB all-reduce (N > 1)")
     p.add_argument("--rows", type=int, default=0, help="override the row count M of the workload (profiling cases)")
     return p.parse_args()
 
@@ -305,7 +306,7 @@ def main():
     dA = torch.empty((rows, k), device=dev, dtype=tdtype)
     dB = torch.empty((k, n), device=dev, dtype=tdtype)
 
-    op = RowShardedMatmul(Bm, gemm=cuda_gemm)
+    op = RowShardedMatmul(Bm, gemm=cuda_gemm, comm_sms=args.comm_sms)
 
     def step():
         op.forward(A, out=Cc)

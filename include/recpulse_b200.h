@@ -138,6 +138,9 @@ typedef struct {
     int accumulate;                 /* 0: C = AB ; 1: C = C + AB (one rounding of the sum)   */
     const void* bias;               /* NULL, or n values of the GEMM's dtype added to every  */
                                     /* row of every batch before the rounding (device memory)*/
+    int max_sms;                    /* 0 = use every SM; otherwise the persistent tensor-core */
+                                    /* kernels occupy at most this many SMs, leaving the rest */
+                                    /* to work that runs beside the GEMM (a collective)       */
 } RpbGemm;
 
 /* Fills `g` for a packed row-major m x k times k x n product (batch = reduce = 1). */

@@ -605,10 +605,12 @@ int launch_umma(const RpbProblem& p, void* C, const void* A, const void* B, Devi
         if (encode_store_map(&mc, C, dt, 2, p.n, p.m, p.batch, p.c_row, p.c_batch, 64) == 0) a.tma_store = 1;
     }
 
-    int grid = (int)(a.total_work < d->sm_count ? a.total_work : d->sm_count);
+    int sms = d->sm_count;
+    if (p.max_sms > 0 && p.max_sms < sms) sms = p.max_sms < 2 ? 2 : p.max_sms;
+    int grid = (int)(a.total_work < sms ? a.total_work : sms);
     int rc;
     if (pair) {
-        const long long clusters = a.total_work < d->sm_count / 2 ? a.total_work : d->sm_count / 2;
+        const long long clusters = a.total_work < sms / 2 ? a.total_work : sms / 2;
         rc = launch_umma_bn<T, 128, true>(pa.mn_major, pb.mn_major, ma, mb, mc, a, (int)clusters * 2, stream);
     }
     else if (BN == 64) rc = launch_umma_bn<T, 64>(pa.mn_major, pb.mn_major, ma, mb, mc, a, grid, stream);
@@ -758,7 +760,7 @@ int rp_matmul_ex(void* C, const void* A, const void* B, const RpbGemm* g, DType 
     p.a_row = g->a_row; p.a_col = g->a_col; p.a_batch = g->a_batch; p.a_reduce = g->a_reduce;
     p.b_row = g->b_row; p.b_col = g->b_col; p.b_batch = g->b_batch; p.b_reduce = g->b_reduce;
     p.c_row = g->c_row; p.c_batch = g->c_batch; p.accumulate = g->accumulate; p.dtype = (int)dtype;
-    p.bias = g->bias;
+    p.bias = g->bias; p.max_sms = g->max_sms;
     int prev = -1;
     RPB_CUDA(cudaGetDevice(&prev));
     if (prev != device_id) RPB_CUDA(cudaSetDevice(device_id));
@@ -799,7 +801,7 @@ int matmul_kernel_device(void* C, const void* A, const void* B, int m, int k, in
     p.m = m; p.n = n; p.k = k; p.batch = 1; p.reduce = 1;
     p.a_row = g.a_row; p.a_col = 1; p.a_batch = 0; p.a_reduce = 0;
     p.b_row = g.b_row; p.b_col = 1; p.b_batch = 0; p.b_reduce = 0;
-    p.c_row = n; p.c_batch = 0; p.accumulate = 0; p.dtype = (int)dtype; p.bias = nullptr;
+    p.c_row = n; p.c_batch = 0; p.accumulate = 0; p.dtype = (int)dtype; p.bias = nullptr; p.max_sms = 0;
     if (run_gemm(p, C, A, B, dev, nullptr)) return -1;
     RPB_CUDA(cudaStreamSynchronize(nullptr));
     return 0;

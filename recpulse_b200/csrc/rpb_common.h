@@ -17,6 +17,7 @@ struct RpbProblem {
     int accumulate;
     int dtype;                 /* DType code */
     const void* bias;          /* n values of dtype, or NULL */
+    int max_sms;               /* 0 = all */
 };
 
 static inline size_t rpb_dtype_size(int dtype) {

@@ -38,7 +38,8 @@ def row_partition(rows: int, world: int, rank: int) -> tuple[int, int]:
     return begin, begin + base + (1 if rank < extra else 0)
 
 
-def cuda_gemm(c: torch.Tensor, a: torch.Tensor, b: torch.Tensor, trans_a=False, trans_b=False, accumulate=False) -> None:
+def cuda_gemm(c: torch.Tensor, a: torch.Tensor, b: torch.Tensor, trans_a=False, trans_b=False, accumulate=False,
+              max_sms: int = 0) -> None:
     """c (+)= op(a) . op(b) on c's device and the current torch stream, through the C ABI.
     2-D tensors with a unit stride in one dimension; op() is expressed as swapped strides (no copy)."""
     if not c.is_cuda:
@@ -55,6 +56,7 @@ def cuda_gemm(c: torch.Tensor, a: torch.Tensor, b: torch.Tensor, trans_a=False, 
     g.b_row, g.b_col = bv.stride(0), bv.stride(1)
     g.c_row = c.stride(0)
     g.accumulate = int(accumulate)
+    g.max_sms = int(max_sms)
     stream = torch.cuda.current_stream(c.device).cuda_stream
     rc = lib.rp_matmul_ex(C.c_void_p(c.data_ptr()), C.c_void_p(a.data_ptr()), C.c_void_p(b.data_ptr()), C.byref(g),
                           _TORCH_CODE[c.dtype], c.device.index, C.c_void_p(stream))
@@ -65,10 +67,11 @@ def cuda_gemm(c: torch.Tensor, a: torch.Tensor, b: torch.Tensor, trans_a=False, 
 class RowShardedMatmul:
     """Forward + backward of C = A.B with A's rows split over the ranks of ``group``."""
 
-    def __init__(self, b: torch.Tensor, group=None, gemm: Callable = cuda_gemm, src: int = 0):
+    def __init__(self, b: torch.Tensor, group=None, gemm: Callable = cuda_gemm, src: int = 0, comm_sms: int = 16):
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.gemm = gemm
+        self.comm_sms = comm_sms
         self.b = b
         if self.world > 1:
             dist.broadcast(self.b, src=src, group=group)        # replicate B into local memory once
@@ -96,7 +99,14 @@ class RowShardedMatmul:
                     work = dist.all_reduce(db_out, group=self.group, async_op=True)
             else:
                 work = dist.all_reduce(db_out, group=self.group, async_op=True)
-        self.gemm(da_out, dc_rows, self.b, trans_b=True)         # ... so its reduction hides behind dA
+        # ... so its reduction hides behind dA.  The GEMM kernels are persistent and fill every SM, which
+        # would leave the collective's thread blocks waiting for the GEMM to end; while a reduction is in
+        # flight the dA GEMM therefore leaves `comm_sms` SMs free.
+        if work is not None and self.comm_sms and self.gemm is cuda_gemm:
+            sms = torch.cuda.get_device_properties(da_out.device).multi_processor_count
+            self.gemm(da_out, dc_rows, self.b, trans_b=True, max_sms=max(2, sms - self.comm_sms))
+        else:
+            self.gemm(da_out, dc_rows, self.b, trans_b=True)
         if work is not None:
             work.wait()
             if self._side is not None:
