@@ -381,24 +381,24 @@ struct OperandPlan {
     long long batch_stride = 0, reduce_stride = 0;
 };
 
-bool stride_ok(long long s) { return s > 0 && (s * 2) % 16 == 0 && (s * 2) < (1LL << 40); }
+bool stride_ok(long long s, int es) { return s > 0 && (s * es) % 16 == 0 && (s * es) < (1LL << 40); }
 
 /* mn/k: extents; mn_s/k_s: element strides of the output-side index and of the reduction index */
 OperandPlan plan_operand(const void* base, int mn, int k, long long mn_s, long long k_s,
-                         int batch, long long batch_s, int reduce, long long reduce_s) {
+                         int batch, long long batch_s, int reduce, long long reduce_s, int es = 2) {
     OperandPlan o;
     if (reinterpret_cast<uintptr_t>(base) & 15u) return o;
-    if (k_s == 1 && (mn == 1 || stride_ok(mn_s))) { o.mn_major = false; o.outer_stride = mn_s; }
-    else if (mn_s == 1 && (k == 1 || stride_ok(k_s))) { o.mn_major = true; o.outer_stride = k_s; }
+    if (k_s == 1 && (mn == 1 || stride_ok(mn_s, es))) { o.mn_major = false; o.outer_stride = mn_s; }
+    else if (mn_s == 1 && (k == 1 || stride_ok(k_s, es))) { o.mn_major = true; o.outer_stride = k_s; }
     else return o;
     if (batch > 1) {
         if (batch_s == 0) o.batch_mul = 0;
-        else if (stride_ok(batch_s)) o.batch_stride = batch_s;
+        else if (stride_ok(batch_s, es)) o.batch_stride = batch_s;
         else return o;
     }
     if (reduce > 1) {
         if (reduce_s == 0) o.reduce_mul = 0;
-        else if (stride_ok(reduce_s)) o.reduce_stride = reduce_s;
+        else if (stride_ok(reduce_s, es)) o.reduce_stride = reduce_s;
         else return o;
     }
     o.ok = true;
@@ -406,7 +406,7 @@ OperandPlan plan_operand(const void* base, int mn, int k, long long mn_s, long l
 }
 
 int encode_map(CUtensorMap* map, const void* base, const OperandPlan& o, int mn, int k, int batch, int reduce,
-               int box_mn_rows, CUtensorMapDataType dt) {
+               int box_mn_rows, CUtensorMapDataType dt, int es = 2) {
     /* dims, innermost first: (contiguous index, other matrix index, summed problem, batch) */
     cuuint64_t dims[4]; cuuint64_t strides[3]; cuuint32_t box[4]; cuuint32_t estr[4] = {1, 1, 1, 1};
     const cuuint64_t inner = o.mn_major ? mn : k;
@@ -415,26 +415,28 @@ int encode_map(CUtensorMap* map, const void* base, const OperandPlan& o, int mn,
     dims[2] = (reduce > 1 && o.reduce_mul) ? reduce : 1;
     dims[3] = (batch > 1 && o.batch_mul) ? batch : 1;
     auto pad16 = [](unsigned long long b) { return (b + 15ull) & ~15ull; };
-    unsigned long long s1 = (outer > 1 && o.outer_stride > 0) ? (unsigned long long)o.outer_stride * 2 : pad16(inner * 2);
+    unsigned long long s1 = (outer > 1 && o.outer_stride > 0) ? (unsigned long long)o.outer_stride * es : pad16(inner * es);
     if (s1 % 16) s1 = pad16(s1);
-    unsigned long long s2 = dims[2] > 1 ? (unsigned long long)o.reduce_stride * 2 : pad16(s1 * outer);
-    unsigned long long s3 = dims[3] > 1 ? (unsigned long long)o.batch_stride * 2 : pad16(s2 * dims[2]);
+    unsigned long long s2 = dims[2] > 1 ? (unsigned long long)o.reduce_stride * es : pad16(s1 * outer);
+    unsigned long long s3 = dims[3] > 1 ? (unsigned long long)o.batch_stride * es : pad16(s2 * dims[2]);
     const unsigned long long lim = (1ull << 40) - 16;
     if (s2 > lim) s2 = lim;
     if (s3 > lim) s3 = lim;
     strides[0] = s1; strides[1] = s2; strides[2] = s3;
-    box[0] = 64;                                    /* 64 x 2 bytes = the 128-byte swizzle span */
-    box[1] = o.mn_major ? rpb_umma::BLOCK_K : box_mn_rows;
+    box[0] = 128 / es;                              /* the 128-byte swizzle span */
+    box[1] = o.mn_major ? 128 / es : box_mn_rows;   /* MN-major: one K block of rows */
     box[2] = 1; box[3] = 1;
+    /* 32-bit operands read MN-major by the tensor cores need the 128-byte swizzle with 32-byte atoms (the only
+     * shared-memory layout tcgen05 accepts for transposed tf32); everything else uses the plain 128-byte swizzle */
+    const CUtensorMapSwizzle swz = (es == 4 && o.mn_major) ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B;
     MapKey key;
     memset(&key, 0, sizeof(key));
-    key.base = base; key.dt = (int)dt; key.rank = 4; key.swz = 1;
+    key.base = base; key.dt = (int)dt; key.rank = 4; key.swz = 16 + (int)swz;
     for (int i = 0; i < 4; ++i) { key.d[i] = dims[i]; key.box[i] = box[i]; }
     for (int i = 0; i < 3; ++i) key.s[i] = strides[i];
     if (g_maps.get(key, map)) return 0;
     CUresult r = g_encode(map, dt, 4, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                          swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r == CUDA_SUCCESS) g_maps.put(key, *map);
     if (r != CUDA_SUCCESS) {
         fprintf(stderr, "recpulse_b200: cuTensorMapEncodeTiled failed (%d) dims=[%llu,%llu,%llu,%llu] strides=[%llu,%llu,%llu]\n",
@@ -468,9 +470,15 @@ int encode_store_map(CUtensorMap* map, void* base, CUtensorMapDataType dt, int e
 }
 
 /* shared-memory matrix descriptor without the start address (128-byte swizzle, version 1) */
-uint64_t smem_desc_base(bool mn_major) {
+uint64_t smem_desc_base(bool mn_major, int es = 2) {
+    if (es == 4 && mn_major) {
+        /* transposed tf32: layout type 1 (128-byte swizzle, 32-byte atoms): atoms of 4 K rows x 128 bytes */
+        const uint64_t sbo = 512 >> 4;                                /* next group of 4 K rows */
+        const uint64_t lbo = (uint64_t)(32 * 128) >> 4;               /* next 32-element MN chunk (32 K rows further) */
+        return (lbo << 16) | (sbo << 32) | (1ull << 46) | (1ull << 61);
+    }
     const uint64_t sbo = 1024 >> 4;                                   /* next group of 8 rows */
-    const uint64_t lbo = mn_major ? (uint64_t)(rpb_umma::BLOCK_K * 128) >> 4 : 1;   /* next 64-wide MN chunk */
+    const uint64_t lbo = mn_major ? (uint64_t)((128 / es) * 128) >> 4 : 1;   /* next 128-byte-wide MN chunk */
     return (lbo << 16) | (sbo << 32) | (1ull << 46) | (2ull << 61);
 }
 
@@ -487,13 +495,13 @@ int raster_group(int in_flight, int tile_m, int tile_n, int tiles_n) {
 template <typename T, int BN, bool A_MN, bool B_MN, bool PAIR>
 int launch_umma_inst(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, const rpb_umma::Args& args,
                      int grid, cudaStream_t stream) {
-    using Cfg = rpb_umma::Config<BN>;
+    using Cfg = rpb_umma::Config<BN, rpb_umma::Elem<T>::SPLIT>;
     auto kern = rpb_umma::gemm_kernel<T, BN, A_MN, B_MN, PAIR>;
     static std::atomic<bool> attr_done[MAX_DEVICES];
     RPB_CUDA(smem_attr_once(kern, Cfg::SMEM_BYTES, attr_done));
     if (PAIR) {
         cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3((unsigned)grid); cfg.blockDim = dim3(rpb_umma::NUM_THREADS);
+        cfg.gridDim = dim3((unsigned)grid); cfg.blockDim = dim3(rpb_umma::Elem<T>::THREADS);
         cfg.dynamicSmemBytes = Cfg::SMEM_BYTES; cfg.stream = stream;
         cudaLaunchAttribute attr;
         attr.id = cudaLaunchAttributeClusterDimension;
@@ -501,7 +509,7 @@ int launch_umma_inst(const CUtensorMap& ma, const CUtensorMap& mb, const CUtenso
         cfg.attrs = &attr; cfg.numAttrs = 1;
         RPB_CUDA(cudaLaunchKernelEx(&cfg, kern, ma, mb, mc, args));
     } else {
-        kern<<<grid, rpb_umma::NUM_THREADS, Cfg::SMEM_BYTES, stream>>>(ma, mb, mc, args);
+        kern<<<grid, rpb_umma::Elem<T>::THREADS, Cfg::SMEM_BYTES, stream>>>(ma, mb, mc, args);
     }
     g_launches++;
     RPB_CUDA(cudaGetLastError());
@@ -535,8 +543,11 @@ bool want_pair(int m, int n, long long k_total, int batch, int sm_count) {
 template <typename T>
 int launch_umma(const RpbProblem& p, void* C, const void* A, const void* B, DeviceState* d, cudaStream_t stream) {
     if (d->cc_major != 10) return 1;
-    OperandPlan pa = plan_operand(A, p.m, p.k, p.a_row, p.a_col, p.batch, p.a_batch, p.reduce, p.a_reduce);
-    OperandPlan pb = plan_operand(B, p.n, p.k, p.b_col, p.b_row, p.batch, p.b_batch, p.reduce, p.b_reduce);
+    constexpr int ES = (int)sizeof(T);
+    constexpr int BK = rpb_umma::Elem<T>::BLOCK_K;
+    constexpr bool F32 = rpb_umma::Elem<T>::SPLIT;
+    OperandPlan pa = plan_operand(A, p.m, p.k, p.a_row, p.a_col, p.batch, p.a_batch, p.reduce, p.a_reduce, ES);
+    OperandPlan pb = plan_operand(B, p.n, p.k, p.b_col, p.b_row, p.batch, p.b_batch, p.reduce, p.b_reduce, ES);
     if (!pa.ok || !pb.ok) return 1;
 
     const bool pair = want_pair(p.m, p.n, (long long)p.k * p.reduce, p.batch, d->sm_count);
@@ -547,7 +558,7 @@ int launch_umma(const RpbProblem& p, void* C, const void* A, const void* B, Devi
     rpb_umma::Args a;
     memset(&a, 0, sizeof(a));
     a.m = p.m; a.n = p.n; a.k = p.k; a.batch = p.batch; a.reduce = p.reduce;
-    a.k_blocks = (p.k + rpb_umma::BLOCK_K - 1) / rpb_umma::BLOCK_K;
+    a.k_blocks = (p.k + BK - 1) / BK;
     a.k_iters = a.k_blocks * p.reduce;
     a.tiles_m = (p.m + tile_m - 1) / tile_m;
     a.tiles_n = (p.n + tile_n - 1) / tile_n;
@@ -576,20 +587,23 @@ int launch_umma(const RpbProblem& p, void* C, const void* A, const void* B, Devi
         a.partial = reinterpret_cast<float*>(ws);
     }
     const bool bf16 = p.dtype == DTYPE_BFLOAT16;
-    const uint32_t fmt = bf16 ? 1u : 0u;
+    const uint32_t fmt = F32 ? 2u : (bf16 ? 1u : 0u);             /* operand format: F16 = 0, BF16 = 1, TF32 = 2 */
     a.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((pa.mn_major ? 1u : 0u) << 15) | ((pb.mn_major ? 1u : 0u) << 16) |
               ((uint32_t)(tile_n >> 3) << 17) | ((uint32_t)(tile_m >> 4) << 24);
-    a.a_desc_base = smem_desc_base(pa.mn_major);
-    a.b_desc_base = smem_desc_base(pb.mn_major);
-    /* advance per K=16 step: K-major 32 bytes inside the swizzle row; MN-major two 8-row groups */
-    a.a_kstep = pa.mn_major ? (2 * 1024) >> 4 : 32 >> 4;
-    a.b_kstep = pb.mn_major ? (2 * 1024) >> 4 : 32 >> 4;
+    a.a_desc_base = smem_desc_base(pa.mn_major, ES);
+    a.b_desc_base = smem_desc_base(pb.mn_major, ES);
+    /* advance per instruction (32 bytes of K): K-major 32 bytes inside the swizzle row; MN-major the K rows it
+     * covers (16 halves or 8 floats), 128 bytes each */
+    const uint32_t mn_step = (uint32_t)(rpb_umma::Elem<T>::UMMA_K * 128) >> 4;
+    a.a_kstep = pa.mn_major ? mn_step : 32 >> 4;
+    a.b_kstep = pb.mn_major ? mn_step : 32 >> 4;
     a.status = d->status;
 
     CUtensorMap ma, mb;
-    const CUtensorMapDataType dt = bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-    if (encode_map(&ma, A, pa, p.m, p.k, p.batch, p.reduce, rpb_umma::BLOCK_M, dt)) return -1;
-    if (encode_map(&mb, B, pb, p.n, p.k, p.batch, p.reduce, BN, dt)) return -1;
+    const CUtensorMapDataType dt = F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                       : (bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16);
+    if (encode_map(&ma, A, pa, p.m, p.k, p.batch, p.reduce, rpb_umma::BLOCK_M, dt, ES)) return -1;
+    if (encode_map(&mb, B, pb, p.n, p.k, p.batch, p.reduce, BN, dt, ES)) return -1;
 
     /* output through shared memory + TMA store when the destination is TMA-addressable; the register
      * epilogue handles "C += AB" and odd alignments */
@@ -600,9 +614,9 @@ int launch_umma(const RpbProblem& p, void* C, const void* A, const void* B, Devi
             encode_store_map(&mc, a.partial, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, p.n, p.m, (long long)a.splits * p.batch,
                              p.n, (long long)p.m * p.n, 32) == 0)
             a.tma_store = 1;
-    } else if (!p.accumulate && (reinterpret_cast<uintptr_t>(C) & 15u) == 0 && p.c_row % 8 == 0 &&
-               (p.batch == 1 || p.c_batch % 8 == 0)) {
-        if (encode_store_map(&mc, C, dt, 2, p.n, p.m, p.batch, p.c_row, p.c_batch, 64) == 0) a.tma_store = 1;
+    } else if (!p.accumulate && (reinterpret_cast<uintptr_t>(C) & 15u) == 0 && p.c_row % (16 / ES) == 0 &&
+               (p.batch == 1 || p.c_batch % (16 / ES) == 0)) {
+        if (encode_store_map(&mc, C, dt, ES, p.n, p.m, p.batch, p.c_row, p.c_batch, 128 / ES) == 0) a.tma_store = 1;
     }
 
     int sms = d->sm_count;
@@ -676,6 +690,15 @@ int run_gemm(const RpbProblem& in, void* C, const void* A, const void* B, int de
     switch (p.dtype) {
         case DTYPE_FLOAT32: {
             if (forced != RPB_KERNEL_SIMT) {
+                /* large outputs: 3xTF32 on tcgen05 (hi/lo split in shared memory); otherwise, and for layouts TMA
+                 * cannot address, the mma.sync 3xTF32 kernel with its smaller tiles */
+                static int env = -1;
+                if (env < 0) { const char* e = getenv("RPB_FP32_UMMA"); env = e ? (atoi(e) ? 2 : 1) : 0; }
+                const long long big_tiles = (long long)((p.m + 127) / 128) * ((p.n + 127) / 128) * p.batch;
+                if (env != 1 && (env == 2 || forced == RPB_KERNEL_UMMA || big_tiles >= d->sm_count / 2)) {
+                    int rc = launch_umma<float>(p, C, A, B, d, stream);
+                    if (rc <= 0) return rc;
+                }
                 int rc = launch_tf32(p, C, A, B, d, stream);
                 if (rc <= 0) return rc;
             }
@@ -944,7 +967,7 @@ int noalloc_launch(void* C, const void* A, const void* B, int m, int k, int n, i
     rpb_umma::Args a;
     memset(&a, 0, sizeof(a));
     a.m = m; a.n = n; a.k = k; a.batch = 1; a.reduce = 1;
-    a.k_blocks = (k + rpb_umma::BLOCK_K - 1) / rpb_umma::BLOCK_K;
+    a.k_blocks = (k + rpb_umma::Elem<T>::BLOCK_K - 1) / rpb_umma::Elem<T>::BLOCK_K;
     a.k_iters = a.k_blocks;
     a.tiles_m = (m + rpb_umma::BLOCK_M - 1) / rpb_umma::BLOCK_M;
     a.tiles_n = (n + BN - 1) / BN;

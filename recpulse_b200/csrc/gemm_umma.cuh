@@ -32,17 +32,29 @@
 namespace rpb_umma {
 
 constexpr int BLOCK_M = 128;
-constexpr int BLOCK_K = 64;             /* 64 x 2 bytes = one 128-byte swizzle row */
-constexpr int UMMA_K = 16;
 constexpr int EPI_WARPS = 8;           /* two per tensor-memory lane quarter: even / odd column chunks */
-constexpr int NUM_THREADS = (2 + EPI_WARPS) * 32;
+constexpr int SPLIT_WARPS = 4;         /* float32 only: warps that take operand tiles apart into hi + lo */
+
+/* Per element type.  One K block is always 128 bytes wide (one swizzle row): 64 halves or 32 floats.
+ * float32 runs as 3xTF32: the tile that TMA delivered is split in shared memory into hi (the value with
+ * its low 13 mantissa bits cleared, exact in TF32) and lo = x - hi, and each K step issues
+ * lo*hi + hi*lo + hi*hi on kind::tf32 (fp32 accumulate).  The dropped lo*lo is below 2^-22 of the product. */
+template <typename T> struct Elem {
+    static constexpr int BYTES = sizeof(T);
+    static constexpr bool SPLIT = BYTES == 4;
+    static constexpr int BLOCK_K = 128 / BYTES;          /* elements per K block                       */
+    static constexpr int UMMA_K = 32 / BYTES;            /* elements per instruction along K (32 bytes) */
+    static constexpr int CHUNK = 128 / BYTES;            /* MN-major operands: elements per 128-byte chunk */
+    static constexpr int THREADS = (2 + EPI_WARPS + (SPLIT ? SPLIT_WARPS : 0)) * 32;
+};
 constexpr long long WAIT_LIMIT_CYCLES = 4000000000ll;   /* about 2 s of SM clock per wait */
 constexpr int SMEM_LIMIT = 227 * 1024;
 
-template <int BN> struct Config {
-    static constexpr int A_BYTES = BLOCK_M * BLOCK_K * 2;
-    static constexpr int B_BYTES = BN * BLOCK_K * 2;
-    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+template <int BN, bool SPLIT = false> struct Config {
+    static constexpr int A_BYTES = BLOCK_M * 128;
+    static constexpr int B_BYTES = BN * 128;
+    static constexpr int LOAD_BYTES = A_BYTES + B_BYTES;                 /* what TMA delivers per stage */
+    static constexpr int STAGE_BYTES = SPLIT ? 2 * LOAD_BYTES : LOAD_BYTES;   /* [A | B | A_lo | B_lo]   */
     /* epilogue staging for TMA stores: one buffer of 32 rows x 128 bytes per epilogue warp */
     static constexpr int STORE_BUF_BYTES = 32 * 128;
     static constexpr int STORE_BYTES = EPI_WARPS * STORE_BUF_BYTES;
@@ -54,7 +66,7 @@ template <int BN> struct Config {
 struct Args {
     int m, n, k;
     int batch, reduce;
-    int k_blocks;          /* ceil(k / BLOCK_K) */
+    int k_blocks;          /* ceil(k / elements per K block) */
     int k_iters;           /* reduce * k_blocks */
     int splits;            /* CTAs sharing one output tile along K (1 = none) */
     int iters_per_split;
@@ -159,6 +171,23 @@ __device__ __forceinline__ void cluster_sync() {
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 template <bool PAIR>
+__device__ __forceinline__ void umma_tf32(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                          uint32_t idesc, uint32_t accumulate) {
+    if (PAIR) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "setp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+    } else {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "setp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+    }
+}
+template <bool PAIR>
 __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
                                          uint32_t idesc, uint32_t accumulate) {
     if (PAIR) {
@@ -217,7 +246,9 @@ __device__ __forceinline__ void tmem_load_wait() { asm volatile("tcgen05.wait::l
 template <typename T> __device__ __forceinline__ float to_f32(T v);
 template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
 template <> __device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
 template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
 template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
 template <> __device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half_rn(v); }
 template <typename T> __device__ __forceinline__ uint32_t pack2(float lo, float hi);
@@ -234,13 +265,14 @@ template <> __device__ __forceinline__ uint32_t pack2<__half>(float lo, float hi
 template <typename T>
 __device__ __forceinline__ void add_bias_32(uint32_t (&v)[32], const T* bias, int col, int n) {
     const T* bp = bias + col;
+    constexpr int PER = 16 / (int)sizeof(T);             /* elements per 16-byte load */
     if (col + 32 <= n && (reinterpret_cast<uintptr_t>(bp) & 15u) == 0) {
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
+        for (int q = 0; q < 32 / PER; ++q) {
             const uint4 raw = __ldg(reinterpret_cast<const uint4*>(bp) + q);
             const T* b8 = reinterpret_cast<const T*>(&raw);
 #pragma unroll
-            for (int e = 0; e < 8; ++e) v[8 * q + e] = __float_as_uint(__uint_as_float(v[8 * q + e]) + to_f32<T>(b8[e]));
+            for (int e = 0; e < PER; ++e) v[PER * q + e] = __float_as_uint(__uint_as_float(v[PER * q + e]) + to_f32<T>(b8[e]));
         }
     } else {
 #pragma unroll
@@ -259,11 +291,14 @@ __device__ __forceinline__ void add_bias_32(uint32_t (&v)[32], const T* bias, in
  *               accumulator.  Each operand byte is fetched from L2 by one SM only (no multicast), so
  *               L2 traffic per FLOP drops by a third against PAIR = false at the same MMA shape per SM. */
 template <typename T, int BN, bool A_MN, bool B_MN, bool PAIR>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+__global__ void __launch_bounds__(Elem<T>::THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
             const __grid_constant__ CUtensorMap map_c, const Args args)
 {
-    using Cfg = Config<BN>;
+    using E = Elem<T>;
+    constexpr bool SPLIT = E::SPLIT;
+    constexpr int BLOCK_K = E::BLOCK_K, UMMA_K = E::UMMA_K, CHUNK = E::CHUNK;
+    using Cfg = Config<BN, SPLIT>;
     constexpr int ACC_N = PAIR ? 2 * BN : BN;              /* accumulator columns = instruction N */
     constexpr int TILE_M = PAIR ? 2 * BLOCK_M : BLOCK_M;
     constexpr uint32_t TMEM_COLS = 2 * ACC_N;
@@ -274,13 +309,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
     const uint32_t store_base = smem_base + Cfg::STAGES * Cfg::STAGE_BYTES;       /* 1024-aligned */
     const uint32_t bar_base = store_base + Cfg::STORE_BYTES;
-    /* barrier words: full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], then tmem ptr, abort flag */
+    /* barrier words: full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], ready[STAGES], then tmem ptr, abort flag */
     auto full_bar = [&](int s) { return bar_base + 8u * s; };
     auto empty_bar = [&](int s) { return bar_base + 8u * (Cfg::STAGES + s); };
     auto tfull_bar = [&](int i) { return bar_base + 8u * (2 * Cfg::STAGES + i); };
     auto tempty_bar = [&](int i) { return bar_base + 8u * (2 * Cfg::STAGES + 2 + i); };
+    auto ready_bar = [&](int s) { return bar_base + 8u * (2 * Cfg::STAGES + 4 + s); };   /* float32: tile split into hi / lo */
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + Cfg::STAGES * Cfg::STAGE_BYTES + Cfg::STORE_BYTES +
-                                                      8 * (2 * Cfg::STAGES + 4));
+                                                      8 * (3 * Cfg::STAGES + 4));
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5;
@@ -290,7 +326,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     const bool leader = cta_rank == 0;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < Cfg::STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+        for (int s = 0; s < Cfg::STAGES; ++s) {
+            mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1);
+            if (SPLIT) mbar_init(ready_bar(s), (PAIR ? 2 : 1) * SPLIT_WARPS);
+        }
         for (int i = 0; i < 2; ++i) { mbar_init(tfull_bar(i), 1); mbar_init(tempty_bar(i), (PAIR ? 2 : 1) * EPI_WARPS); }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -354,27 +393,29 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                     const uint32_t sb = sa + Cfg::A_BYTES;
                     /* both CTAs of a pair report their bytes to the leader's barrier */
                     uint32_t fb = full_bar(stage);
-                    if (PAIR) {
-                        if (leader) mbar_expect_tx(fb, 2 * Cfg::STAGE_BYTES);
+                    if (PAIR && !SPLIT) {
+                        if (leader) mbar_expect_tx(fb, 2 * Cfg::LOAD_BYTES);
                         fb = cluster_addr(fb, 0);
                     } else {
-                        mbar_expect_tx(fb, Cfg::STAGE_BYTES);
+                        /* float32 pairs: each CTA first splits its own tiles, so its loads report locally */
+                        mbar_expect_tx(fb, Cfg::LOAD_BYTES);
                     }
+                    constexpr bool REMOTE_BAR = PAIR && !SPLIT;
                     if (!A_MN) {
-                        tma_load_4d<PAIR>(sa, &map_a, fb, k0, row0, r * args.a_reduce_mul, bz * args.a_batch_mul);
+                        tma_load_4d<REMOTE_BAR>(sa, &map_a, fb, k0, row0, r * args.a_reduce_mul, bz * args.a_batch_mul);
                     } else {
 #pragma unroll
-                        for (int c = 0; c < BLOCK_M / 64; ++c)
-                            tma_load_4d<PAIR>(sa + c * (BLOCK_K * 128), &map_a, fb, row0 + c * 64, k0,
-                                              r * args.a_reduce_mul, bz * args.a_batch_mul);
+                        for (int c = 0; c < BLOCK_M / CHUNK; ++c)
+                            tma_load_4d<REMOTE_BAR>(sa + c * (BLOCK_K * 128), &map_a, fb, row0 + c * CHUNK, k0,
+                                                    r * args.a_reduce_mul, bz * args.a_batch_mul);
                     }
                     if (!B_MN) {
-                        tma_load_4d<PAIR>(sb, &map_b, fb, k0, col0, r * args.b_reduce_mul, bz * args.b_batch_mul);
+                        tma_load_4d<REMOTE_BAR>(sb, &map_b, fb, k0, col0, r * args.b_reduce_mul, bz * args.b_batch_mul);
                     } else {
 #pragma unroll
-                        for (int c = 0; c < BN / 64; ++c)
-                            tma_load_4d<PAIR>(sb + c * (BLOCK_K * 128), &map_b, fb, col0 + c * 64, k0,
-                                              r * args.b_reduce_mul, bz * args.b_batch_mul);
+                        for (int c = 0; c < BN / CHUNK; ++c)
+                            tma_load_4d<REMOTE_BAR>(sb + c * (BLOCK_K * 128), &map_b, fb, col0 + c * CHUNK, k0,
+                                                    r * args.b_reduce_mul, bz * args.b_batch_mul);
                     }
                     if (++stage == Cfg::STAGES) { stage = 0; phase ^= 1u; }
                 }
@@ -395,7 +436,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + ab * ACC_N;
                 for (int it = it0; it < it1; ++it) {
-                    if (!mbar_wait(full_bar(stage), phase, abort_flag, args.status, 3)) { alive = false; break; }
+                    /* float32: the stage is usable once the split warps (of both CTAs of a pair) are done with it */
+                    if (!mbar_wait(SPLIT ? ready_bar(stage) : full_bar(stage), phase, abort_flag, args.status, 3)) { alive = false; break; }
                     tc_fence_after();
                     const uint32_t sa = smem_base + stage * Cfg::STAGE_BYTES;
                     const uint32_t sb = sa + Cfg::A_BYTES;
@@ -403,13 +445,56 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                     const uint64_t db = args.b_desc_base | (uint64_t)((sb >> 4) & 0x3FFFu);
 #pragma unroll
                     for (int kk = 0; kk < BLOCK_K / UMMA_K; ++kk) {
-                        umma_f16<PAIR>(d_tmem, da + (uint64_t)(kk * args.a_kstep), db + (uint64_t)(kk * args.b_kstep),
-                                       args.idesc, (it > it0 || kk > 0) ? 1u : 0u);
+                        const uint64_t ak = da + (uint64_t)(kk * args.a_kstep), bk = db + (uint64_t)(kk * args.b_kstep);
+                        const uint32_t first = (it > it0 || kk > 0) ? 1u : 0u;
+                        if (SPLIT) {
+                            constexpr uint64_t LO = (uint64_t)(Cfg::LOAD_BYTES >> 4);      /* lo tiles sit LOAD_BYTES further */
+                            umma_tf32<PAIR>(d_tmem, ak + LO, bk, args.idesc, first);       /* small terms first */
+                            umma_tf32<PAIR>(d_tmem, ak, bk + LO, args.idesc, 1u);
+                            umma_tf32<PAIR>(d_tmem, ak, bk, args.idesc, 1u);
+                        } else {
+                            umma_f16<PAIR>(d_tmem, ak, bk, args.idesc, first);
+                        }
                     }
                     umma_commit<PAIR>(empty_bar(stage));      /* frees the stage (in both CTAs of a pair) */
                     if (++stage == Cfg::STAGES) { stage = 0; phase ^= 1u; }
                 }
                 if (alive) umma_commit<PAIR>(tfull_bar(ab));  /* accumulator complete */
+            }
+        }
+    } else if (SPLIT && warp >= 2 + EPI_WARPS) {
+        /* float32 only: take the stage's A and B tiles apart into hi (in place) and lo (a second copy of
+         * the tile, LOAD_BYTES further).  Element-wise on the swizzled bytes, so the layout is untouched. */
+        const int st = (int)threadIdx.x - (2 + EPI_WARPS) * 32;
+        int stage = 0; uint32_t phase = 0;
+        bool alive = true;
+        for (long long w = work_begin; alive && w < args.total_work; w += work_step) {
+            int mt, nt, split, bz; decode(w, mt, nt, split, bz);
+            const int it0 = split * args.iters_per_split;
+            const int it1 = min(it0 + args.iters_per_split, args.k_iters);
+            for (int it = it0; it < it1; ++it) {
+                if (!mbar_wait(full_bar(stage), phase, abort_flag, args.status, 5)) { alive = false; break; }
+                const uint32_t base = smem_base + stage * Cfg::STAGE_BYTES;
+#pragma unroll 4
+                for (int i = st; i < Cfg::LOAD_BYTES / 16; i += SPLIT_WARPS * 32) {
+                    const uint32_t addr = base + (uint32_t)i * 16u;
+                    uint32_t x0, x1, x2, x3;
+                    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(x0), "=r"(x1), "=r"(x2), "=r"(x3) : "r"(addr) : "memory");
+                    const uint32_t h0 = x0 & 0xFFFFE000u, h1 = x1 & 0xFFFFE000u, h2 = x2 & 0xFFFFE000u, h3 = x3 & 0xFFFFE000u;
+                    st_shared_v4(addr, h0, h1, h2, h3);
+                    st_shared_v4(addr + Cfg::LOAD_BYTES,
+                                 __float_as_uint(__uint_as_float(x0) - __uint_as_float(h0)),
+                                 __float_as_uint(__uint_as_float(x1) - __uint_as_float(h1)),
+                                 __float_as_uint(__uint_as_float(x2) - __uint_as_float(h2)),
+                                 __float_as_uint(__uint_as_float(x3) - __uint_as_float(h3)));
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   /* generic writes -> tensor-core reads */
+                __syncwarp();
+                if (lane == 0) {
+                    if (PAIR) mbar_arrive_cluster(cluster_addr(ready_bar(stage), 0));
+                    else mbar_arrive(ready_bar(stage));
+                }
+                if (++stage == Cfg::STAGES) { stage = 0; phase ^= 1u; }
             }
         }
     } else {
@@ -439,7 +524,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                 const uint32_t my_row = (uint32_t)lane * 128u;
                 const uint32_t sw = (uint32_t)lane & 7u;
                 const bool partial_out = args.splits > 1;
-                const int cols_per_box = partial_out ? 32 : 64;             /* 128 bytes of fp32 or of T */
+                const bool wide = partial_out || SPLIT;                     /* rows of fp32: 32 columns per 128 bytes */
+                const int cols_per_box = wide ? 32 : 64;                    /* 128 bytes of fp32 or of 16-bit T */
                 const int zc = partial_out ? split * args.batch + bz : bz;
 #pragma unroll 1
                 for (int c0 = half * cols_per_box; c0 < ACC_N; c0 += 2 * cols_per_box) {
@@ -448,20 +534,20 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                     __syncwarp();
                     /* the accumulator reads of this chunk overlap the TMA engine draining the previous one */
                     tmem_load_32_nowait(tmem_base + ab * ACC_N + c0 + lane_field, v);
-                    if (!partial_out) tmem_load_32_nowait(tmem_base + ab * ACC_N + c0 + 32 + lane_field, v2);
+                    if (!wide) tmem_load_32_nowait(tmem_base + ab * ACC_N + c0 + 32 + lane_field, v2);
                     tmem_load_wait();
                     if (col >= args.n || row_warp >= args.m) continue;      /* warp-uniform */
                     if (args.bias && !partial_out) {
                         add_bias_32<T>(v, reinterpret_cast<const T*>(args.bias), col, args.n);
-                        add_bias_32<T>(v2, reinterpret_cast<const T*>(args.bias), col + 32, args.n);
+                        if (!wide) add_bias_32<T>(v2, reinterpret_cast<const T*>(args.bias), col + 32, args.n);
                     }
                     if (lane == 0) tma_store_wait_read<0>();                /* the previous store has read `buf` */
                     __syncwarp();
-                    if (partial_out) {
+                    if (wide) {
 #pragma unroll
                         for (uint32_t c = 0; c < 8; ++c)
                             st_shared_v4(buf + my_row + ((c ^ sw) << 4), v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
-                    } else {
+                    } else if constexpr (!SPLIT) {
 #pragma unroll
                         for (uint32_t c = 0; c < 4; ++c) {
                             st_shared_v4(buf + my_row + ((c ^ sw) << 4),
@@ -508,7 +594,26 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                 } else {
                     T* dst = cT + bz * args.c_batch + (long long)row * args.c_row + col;
                     if (args.bias) add_bias_32<T>(v, reinterpret_cast<const T*>(args.bias), col, args.n);
-                    if (col + 32 <= args.n && ((reinterpret_cast<uintptr_t>(dst) & 15u) == 0)) {
+                    if constexpr (SPLIT) {
+                        if (col + 32 <= args.n && ((reinterpret_cast<uintptr_t>(dst) & 15u) == 0)) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 4) {
+                                float4 f = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]), __uint_as_float(v[j + 2]),
+                                                       __uint_as_float(v[j + 3]));
+                                if (args.accumulate) {
+                                    const float4 o = *reinterpret_cast<const float4*>(dst + j);
+                                    f.x += o.x; f.y += o.y; f.z += o.z; f.w += o.w;
+                                }
+                                *reinterpret_cast<float4*>(dst + j) = f;
+                            }
+                        } else {
+                            for (int j = 0; j < 32 && col + j < args.n; ++j) {
+                                float f = __uint_as_float(v[j]);
+                                if (args.accumulate) f += to_f32<T>(dst[j]);
+                                dst[j] = from_f32<T>(f);
+                            }
+                        }
+                    } else if (col + 32 <= args.n && ((reinterpret_cast<uintptr_t>(dst) & 15u) == 0)) {
 #pragma unroll
                         for (int j = 0; j < 32; j += 8) {
                             float f[8];

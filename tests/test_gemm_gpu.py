@@ -14,6 +14,9 @@ from helpers import CODE, check_close, f64, rand_operand
 pytestmark = pytest.mark.gpu
 
 
+UMMA = (_lib.KERNEL_UMMA, _lib.KERNEL_UMMA_SPLITK)
+
+
 @pytest.fixture(scope="module")
 def lib():
     lib = rpb.load()
@@ -132,10 +135,32 @@ def test_fp32_3xtf32_kernel(lib, layout):
         a = rand_operand(rng, (1, 1, m, k), dtype); b = rand_operand(rng, (1, 1, k, n), dtype, scale=1 / np.sqrt(k))
         pa = (-m % 4) if ta else (-k % 4)        # stored leading dimension a multiple of 4 floats
         pb = (-k % 4) if tb else (-n % 4)
-        run_ex(lib, dtype, a, b, ta=ta, tb=tb, pad_a=pa, pad_b=pb, expect=(_lib.KERNEL_TF32X3,))
+        run_ex(lib, dtype, a, b, ta=ta, tb=tb, pad_a=pa, pad_b=pb, expect=(_lib.KERNEL_TF32X3,) + UMMA)
     a = rand_operand(rng, (3, 2, 96, 40), dtype); b = rand_operand(rng, (3, 2, 40, 72), dtype)
     run_ex(lib, dtype, a, b, ta=ta, tb=tb, expect=(_lib.KERNEL_TF32X3,))
     run_ex(lib, dtype, a, b, ta=ta, tb=tb, c_init=rand_operand(rng, (3, 96, 72), dtype), expect=(_lib.KERNEL_TF32X3,))
+
+
+@pytest.mark.parametrize("layout", [(False, False), (True, False), (False, True), (True, True)])
+def test_fp32_tcgen05_3xtf32_kernel(lib, layout):
+    """float32 on tcgen05 (kind::tf32, hi/lo split in shared memory): one-CTA and two-CTA tiles, every
+    operand orientation, ragged extents, K split, batches, summed problems, accumulate."""
+    ta, tb = layout
+    dtype = "float32"
+    lib.rpb_force_kernel(_lib.KERNEL_UMMA)
+    rng = np.random.default_rng(71)
+    try:
+        for (m, k, n) in [(128, 32, 128), (128, 784, 256), (64, 512, 2048), (100, 132, 68), (129, 36, 132), (64, 4096, 64),
+                          (1500, 100, 1300), (512, 1024, 768), (2048, 512, 1024)]:
+            a = rand_operand(rng, (1, 1, m, k), dtype); b = rand_operand(rng, (1, 1, k, n), dtype, scale=1 / np.sqrt(k))
+            pa = (-m % 4) if ta else (-k % 4)
+            pb = (-k % 4) if tb else (-n % 4)
+            run_ex(lib, dtype, a, b, ta=ta, tb=tb, pad_a=pa, pad_b=pb, expect=UMMA)
+        a = rand_operand(rng, (3, 2, 96, 40), dtype); b = rand_operand(rng, (3, 2, 40, 72), dtype)
+        run_ex(lib, dtype, a, b, ta=ta, tb=tb, expect=UMMA)
+        run_ex(lib, dtype, a, b, ta=ta, tb=tb, c_init=rand_operand(rng, (3, 96, 72), dtype), expect=UMMA)
+    finally:
+        lib.rpb_force_kernel(0)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "float64", "float16", "bfloat16"])
@@ -150,9 +175,6 @@ def test_batch_reduce_accumulate_semantics(lib, dtype):
     c0 = rand_operand(rng, (3, m, n), dtype)
     run_ex(lib, dtype, a, b, c_init=c0)
     run_ex(lib, dtype, a, b, ta=True, tb=True, c_init=c0)
-
-
-UMMA = (_lib.KERNEL_UMMA, _lib.KERNEL_UMMA_SPLITK)
 
 
 @pytest.mark.parametrize("dtype", ["bfloat16", "float16"])
