@@ -493,8 +493,8 @@ int raster_group(int in_flight, int tile_m, int tile_n, int tiles_n) {
 }
 
 template <typename T, int BN, bool A_MN, bool B_MN, bool PAIR>
-int launch_umma_inst(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, const rpb_umma::Args& args,
-                     int grid, cudaStream_t stream) {
+int launch_umma_inst(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, const CUtensorMap& mp,
+                     const rpb_umma::Args& args, int grid, cudaStream_t stream) {
     using Cfg = rpb_umma::Config<BN, rpb_umma::Elem<T>::SPLIT>;
     auto kern = rpb_umma::gemm_kernel<T, BN, A_MN, B_MN, PAIR>;
     static std::atomic<bool> attr_done[MAX_DEVICES];
@@ -507,9 +507,9 @@ int launch_umma_inst(const CUtensorMap& ma, const CUtensorMap& mb, const CUtenso
         attr.id = cudaLaunchAttributeClusterDimension;
         attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
         cfg.attrs = &attr; cfg.numAttrs = 1;
-        RPB_CUDA(cudaLaunchKernelEx(&cfg, kern, ma, mb, mc, args));
+        RPB_CUDA(cudaLaunchKernelEx(&cfg, kern, ma, mb, mc, mp, args));
     } else {
-        kern<<<grid, rpb_umma::Elem<T>::THREADS, Cfg::SMEM_BYTES, stream>>>(ma, mb, mc, args);
+        kern<<<grid, rpb_umma::Elem<T>::THREADS, Cfg::SMEM_BYTES, stream>>>(ma, mb, mc, mp, args);
     }
     g_launches++;
     RPB_CUDA(cudaGetLastError());
@@ -518,11 +518,11 @@ int launch_umma_inst(const CUtensorMap& ma, const CUtensorMap& mb, const CUtenso
 
 template <typename T, int BN, bool PAIR = false>
 int launch_umma_bn(bool a_mn, bool b_mn, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc,
-                   const rpb_umma::Args& args, int grid, cudaStream_t stream) {
-    if (!a_mn && !b_mn) return launch_umma_inst<T, BN, false, false, PAIR>(ma, mb, mc, args, grid, stream);
-    if (!a_mn && b_mn) return launch_umma_inst<T, BN, false, true, PAIR>(ma, mb, mc, args, grid, stream);
-    if (a_mn && !b_mn) return launch_umma_inst<T, BN, true, false, PAIR>(ma, mb, mc, args, grid, stream);
-    return launch_umma_inst<T, BN, true, true, PAIR>(ma, mb, mc, args, grid, stream);
+                   const CUtensorMap& mp, const rpb_umma::Args& args, int grid, cudaStream_t stream) {
+    if (!a_mn && !b_mn) return launch_umma_inst<T, BN, false, false, PAIR>(ma, mb, mc, mp, args, grid, stream);
+    if (!a_mn && b_mn) return launch_umma_inst<T, BN, false, true, PAIR>(ma, mb, mc, mp, args, grid, stream);
+    if (a_mn && !b_mn) return launch_umma_inst<T, BN, true, false, PAIR>(ma, mb, mc, mp, args, grid, stream);
+    return launch_umma_inst<T, BN, true, true, PAIR>(ma, mb, mc, mp, args, grid, stream);
 }
 
 /* Two-CTA tiles (256 x 256 per cluster) pay off once every cluster has a tile to work on and the
@@ -621,16 +621,57 @@ int launch_umma(const RpbProblem& p, void* C, const void* A, const void* B, Devi
 
     int sms = d->sm_count;
     if (p.max_sms > 0 && p.max_sms < sms) sms = p.max_sms < 2 ? 2 : p.max_sms;
+
+    /* Tail split: if the last wave of tiles would keep fewer than half of the CTAs (or CTA pairs) busy, cut
+     * its tiles along K so that the wave is short instead of sparse (4096^3: 256 tiles on 74 pairs = 3 waves +
+     * 34 tiles; with two K slices each the run takes 3.5 tile times instead of 4). */
+    CUtensorMap mp = ma;
+    a.tail_begin = a.total_work; a.tail_splits = 1; a.tail_iters = a.k_iters;
+    {
+        static int env = -1;
+        if (env < 0) { const char* e = getenv("RPB_TAIL_SPLIT"); env = e ? atoi(e) : 1; }
+        const long long units = pair ? sms / 2 : sms;
+        const long long rem = units > 0 ? tiles % units : 0;
+        /* the extra reduction launch costs ~4 us: measured break-even at about 96 K blocks per tile */
+        if (env && a.splits == 1 && p.batch == 1 && a.tma_store == 1 && tiles > units && rem > 0 && rem * 2 <= units &&
+            a.k_iters >= (env > 1 ? 16 : 96)) {
+            long long ts = units / rem;
+            if (ts > 4) ts = 4;
+            if (ts > a.k_iters / 8) ts = a.k_iters / 8;
+            if (ts >= 2) {
+                const int per = (int)((a.k_iters + ts - 1) / ts);
+                ts = (a.k_iters + per - 1) / per;
+                const size_t bytes = sizeof(float) * (size_t)rem * ts * tile_m * tile_n;
+                void* ws = nullptr;
+                if (get_scratch(d, bytes, stream, &ws)) return -1;
+                if (encode_store_map(&mp, ws, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, tile_n, tile_m, rem * ts, tile_n,
+                                     (long long)tile_m * tile_n, 32) == 0) {
+                    a.partial = reinterpret_cast<float*>(ws);
+                    a.tail_begin = tiles - rem; a.tail_splits = (int)ts; a.tail_iters = per;
+                    a.total_work = a.tail_begin + rem * ts;
+                }
+            }
+        }
+    }
     int grid = (int)(a.total_work < sms ? a.total_work : sms);
     int rc;
     if (pair) {
         const long long clusters = a.total_work < sms / 2 ? a.total_work : sms / 2;
-        rc = launch_umma_bn<T, 128, true>(pa.mn_major, pb.mn_major, ma, mb, mc, a, (int)clusters * 2, stream);
+        rc = launch_umma_bn<T, 128, true>(pa.mn_major, pb.mn_major, ma, mb, mc, mp, a, (int)clusters * 2, stream);
     }
-    else if (BN == 64) rc = launch_umma_bn<T, 64>(pa.mn_major, pb.mn_major, ma, mb, mc, a, grid, stream);
-    else if (BN == 128) rc = launch_umma_bn<T, 128>(pa.mn_major, pb.mn_major, ma, mb, mc, a, grid, stream);
-    else rc = launch_umma_bn<T, 256>(pa.mn_major, pb.mn_major, ma, mb, mc, a, grid, stream);
+    else if (BN == 64) rc = launch_umma_bn<T, 64>(pa.mn_major, pb.mn_major, ma, mb, mc, mp, a, grid, stream);
+    else if (BN == 128) rc = launch_umma_bn<T, 128>(pa.mn_major, pb.mn_major, ma, mb, mc, mp, a, grid, stream);
+    else rc = launch_umma_bn<T, 256>(pa.mn_major, pb.mn_major, ma, mb, mc, mp, a, grid, stream);
     if (rc) return -1;
+    if (a.tail_splits > 1) {
+        const int rem = (int)(tiles - a.tail_begin);
+        rpb_umma::tail_reduce_kernel<T><<<dim3(rem, tile_m), tile_n / 4, 0, stream>>>(
+            a.partial, reinterpret_cast<T*>(C), reinterpret_cast<const T*>(p.bias), p.m, p.n, p.c_row, a.tiles_m, a.tiles_n,
+            a.group_n, (int)a.tail_begin, a.tail_splits, tile_m, tile_n);
+        g_launches++;
+        RPB_CUDA(cudaGetLastError());
+        if (release_scratch(d, stream)) return -1;
+    }
     if (a.splits > 1) {
         rpb_simt::launch_splitk_reduce<T, float>(a.partial, reinterpret_cast<T*>(C), a.splits, p.batch, p.m, p.n, p.c_row,
                                                  p.c_batch, p.accumulate, p.bias, d->sm_count, stream);
@@ -1011,11 +1052,13 @@ int noalloc_launch(void* C, const void* A, const void* B, int m, int k, int n, i
      * is overwritten by this call's GEMM first, so only the status word has to start at zero. */
     RPB_CUDA(cudaMemsetAsync(d->status, 0, sizeof(int), stream));
     const CUtensorMap mc = ma;          /* register epilogue (tma_store = 0): the third map is not read */
+    const CUtensorMap mp = ma;
+    a.tail_begin = a.total_work; a.tail_splits = 1; a.tail_iters = a.k_iters;
     const int grid = (int)(a.total_work < d->sm_count ? a.total_work : d->sm_count);
     int rc;
-    if (BN == 64) rc = launch_umma_bn<T, 64>(pa.mn_major, pb.mn_major, ma, mb, mc, a, grid, stream);
-    else if (BN == 128) rc = launch_umma_bn<T, 128>(pa.mn_major, pb.mn_major, ma, mb, mc, a, grid, stream);
-    else rc = launch_umma_bn<T, 256>(pa.mn_major, pb.mn_major, ma, mb, mc, a, grid, stream);
+    if (BN == 64) rc = launch_umma_bn<T, 64>(pa.mn_major, pb.mn_major, ma, mb, mc, mp, a, grid, stream);
+    else if (BN == 128) rc = launch_umma_bn<T, 128>(pa.mn_major, pb.mn_major, ma, mb, mc, mp, a, grid, stream);
+    else rc = launch_umma_bn<T, 256>(pa.mn_major, pb.mn_major, ma, mb, mc, mp, a, grid, stream);
     if (rc) return -1;
     if (a.splits > 1) {
         const long long elems = (long long)m * n;

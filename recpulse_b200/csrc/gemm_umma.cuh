@@ -72,7 +72,12 @@ struct Args {
     int iters_per_split;
     int tiles_m, tiles_n;
     int group_n;           /* n-tiles per rasterisation group */
-    long long total_work;  /* tiles_m * tiles_n * batch * splits */
+    long long total_work;  /* tiles_m * tiles_n * batch * splits (+ the extra K slices of tail tiles) */
+    /* Tail split: when the last wave of tiles would leave most SMs idle, the tiles of that wave (work items
+     * >= tail_begin) are cut along K into tail_splits slices of tail_iters K blocks each; the slices go to
+     * fp32 tiles in scratch ([tail tile][slice][TILE_M x ACC_N], map_p) and tail_reduce_kernel adds them. */
+    long long tail_begin;  /* == number of output tiles when there is no tail split */
+    int tail_splits, tail_iters;
     int a_batch_mul, a_reduce_mul, b_batch_mul, b_reduce_mul;   /* 0 when that operand is broadcast */
     void* c;               /* output (T), or nullptr when splits > 1 */
     long long c_row, c_batch;
@@ -281,6 +286,16 @@ __device__ __forceinline__ void add_bias_32(uint32_t (&v)[32], const T* bias, in
     }
 }
 
+/* Tile index -> (m-tile, n-tile): tiles are walked in column groups of `group_n` n-tiles, n fastest. */
+__device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int group_n, int& mt, int& nt) {
+    const int per_group = group_n * tiles_m;
+    const int g = t / per_group;
+    const int r = t - g * per_group;
+    const int gn = min(group_n, tiles_n - g * group_n);
+    mt = r / gn;
+    nt = g * group_n + (r - mt * gn);
+}
+
 /* ------------------------------------------------------------------ kernel */
 
 /* PAIR = false: one CTA per output tile of 128 x BN  (tcgen05 cta_group::1).
@@ -293,7 +308,7 @@ __device__ __forceinline__ void add_bias_32(uint32_t (&v)[32], const T* bias, in
 template <typename T, int BN, bool A_MN, bool B_MN, bool PAIR>
 __global__ void __launch_bounds__(Elem<T>::THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-            const __grid_constant__ CUtensorMap map_c, const Args args)
+            const __grid_constant__ CUtensorMap map_c, const __grid_constant__ CUtensorMap map_p, const Args args)
 {
     using E = Elem<T>;
     constexpr bool SPLIT = E::SPLIT;
@@ -336,6 +351,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
         if (args.tma_store) asm volatile("prefetch.tensormap [%0];" ::"l"(&map_c) : "memory");
+        if (args.tail_splits > 1) asm volatile("prefetch.tensormap [%0];" ::"l"(&map_p) : "memory");
     }
     if (warp == 1) {
         if (PAIR) {
@@ -363,16 +379,23 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
      * the tiles in flight then cover a near-square block of C and share their A row panels and B
      * column panels in L2 instead of streaming all of A once per wave. */
     auto decode = [&](long long w, int& mt, int& nt, int& split, int& bz) {
+        if (w >= args.tail_begin) {                 /* K slice of a tail tile (only with splits == batch == 1) */
+            const long long j = w - args.tail_begin;
+            split = (int)(j % args.tail_splits);
+            bz = 0;
+            tile_coords((int)(args.tail_begin + j / args.tail_splits), args.tiles_m, args.tiles_n, args.group_n, mt, nt);
+            return;
+        }
         const int tiles_mn = args.tiles_m * args.tiles_n;
         const int t = (int)(w % tiles_mn); w /= tiles_mn;
         split = (int)(w % args.splits);
         bz = (int)(w / args.splits);
-        const int per_group = args.group_n * args.tiles_m;
-        const int g = t / per_group;
-        const int r = t - g * per_group;
-        const int gn = min(args.group_n, args.tiles_n - g * args.group_n);
-        mt = r / gn;
-        nt = g * args.group_n + (r - mt * gn);
+        tile_coords(t, args.tiles_m, args.tiles_n, args.group_n, mt, nt);
+    };
+    auto k_range = [&](long long w, int split, int& it0, int& it1) {
+        const int per = w >= args.tail_begin ? args.tail_iters : args.iters_per_split;
+        it0 = split * per;
+        it1 = min(it0 + per, args.k_iters);
     };
 
     if (warp == 0) {
@@ -381,8 +404,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             bool alive = true;
             for (long long w = work_begin; alive && w < args.total_work; w += work_step) {
                 int mt, nt, split, bz; decode(w, mt, nt, split, bz);
-                const int it0 = split * args.iters_per_split;
-                const int it1 = min(it0 + args.iters_per_split, args.k_iters);
+                int it0, it1; k_range(w, split, it0, it1);
                 const int row0 = mt * TILE_M + (int)cta_rank * BLOCK_M;     /* this CTA's rows of A */
                 const int col0 = nt * ACC_N + (int)cta_rank * BN;           /* this CTA's columns of B */
                 for (int it = it0; it < it1; ++it) {
@@ -428,8 +450,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             bool alive = true;
             for (long long w = work_begin; alive && w < args.total_work; w += work_step, ++local_tile) {
                 int mt, nt, split, bz; decode(w, mt, nt, split, bz);
-                const int it0 = split * args.iters_per_split;
-                const int it1 = min(it0 + args.iters_per_split, args.k_iters);
+                int it0, it1; k_range(w, split, it0, it1);
                 const uint32_t ab = local_tile & 1u;
                 const uint32_t acc_phase = (local_tile >> 1) & 1u;
                 if (!mbar_wait(tempty_bar(ab), acc_phase ^ 1u, abort_flag, args.status, 2)) { alive = false; break; }
@@ -470,8 +491,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         bool alive = true;
         for (long long w = work_begin; alive && w < args.total_work; w += work_step) {
             int mt, nt, split, bz; decode(w, mt, nt, split, bz);
-            const int it0 = split * args.iters_per_split;
-            const int it1 = min(it0 + args.iters_per_split, args.k_iters);
+            int it0, it1; k_range(w, split, it0, it1);
             for (int it = it0; it < it1; ++it) {
                 if (!mbar_wait(full_bar(stage), phase, abort_flag, args.status, 5)) { alive = false; break; }
                 const uint32_t base = smem_base + stage * Cfg::STAGE_BYTES;
@@ -523,7 +543,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                 const uint32_t buf = store_base + (uint32_t)(warp - 2) * Cfg::STORE_BUF_BYTES;
                 const uint32_t my_row = (uint32_t)lane * 128u;
                 const uint32_t sw = (uint32_t)lane & 7u;
-                const bool partial_out = args.splits > 1;
+                const bool tail_item = w >= args.tail_begin;
+                const bool partial_out = args.splits > 1 || tail_item;
                 const bool wide = partial_out || SPLIT;                     /* rows of fp32: 32 columns per 128 bytes */
                 const int cols_per_box = wide ? 32 : 64;                    /* 128 bytes of fp32 or of 16-bit T */
                 const int zc = partial_out ? split * args.batch + bz : bz;
@@ -564,7 +585,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                     }
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   /* generic writes -> async proxy */
                     __syncwarp();
-                    if (lane == 0) tma_store_3d(&map_c, buf, col, row_warp, zc);
+                    if (lane == 0) {
+                        if (tail_item)   /* compact scratch: [tail slice][row inside the tile][column inside the tile] */
+                            tma_store_3d(&map_p, buf, c0, (int)cta_rank * BLOCK_M + quarter * 32, (int)(w - args.tail_begin));
+                        else
+                            tma_store_3d(&map_c, buf, col, row_warp, zc);
+                    }
                 }
                 tc_fence_before();
                 __syncwarp();                 /* every lane's accumulator reads are done: one arrival per warp */
@@ -663,6 +689,36 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
         else
             asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+/* Adds the K slices of the tail tiles in slice order and writes them into C (with the bias, rounding once).
+ * grid = (tail tiles, rows of a tile), block = tile columns / 4. */
+template <typename T>
+__global__ void tail_reduce_kernel(const float* __restrict__ scratch, T* c, const T* bias, int m, int n, long long c_row,
+                                   int tiles_m, int tiles_n, int group_n, int first_tail_tile, int slices,
+                                   int tile_m, int tile_n)
+{
+    int mt, nt;
+    tile_coords(first_tail_tile + (int)blockIdx.x, tiles_m, tiles_n, group_n, mt, nt);
+    const int lr = blockIdx.y, lc = threadIdx.x * 4;
+    const int row = mt * tile_m + lr, col = nt * tile_n + lc;
+    if (row >= m || col >= n) return;
+    const size_t tile_elems = (size_t)tile_m * tile_n;
+    const float* src = scratch + (size_t)blockIdx.x * slices * tile_elems + (size_t)lr * tile_n + lc;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int sl = 0; sl < slices; ++sl) {
+        const float4 x = *reinterpret_cast<const float4*>(src + sl * tile_elems);
+        acc.x += x.x; acc.y += x.y; acc.z += x.z; acc.w += x.w;
+    }
+    const float v[4] = {acc.x, acc.y, acc.z, acc.w};
+    T* dst = c + (long long)row * c_row + col;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        if (col + e >= n) break;
+        float x = v[e];
+        if (bias) x += to_f32<T>(bias[col + e]);
+        dst[e] = from_f32<T>(x);
     }
 }
 

@@ -41,7 +41,7 @@ def store(logical, transposed, pad):
     return buf, rs, cs, rows * ld
 
 
-def run_ex(lib, dtype, a, b, ta=False, tb=False, pad_a=0, pad_b=0, c_init=None, expect=None):
+def run_ex(lib, dtype, a, b, ta=False, tb=False, pad_a=0, pad_b=0, c_init=None, expect=None, oracle=True, bias=None):
     """a: [batch|1, reduce|1, m, k] bits, b: [batch|1, reduce|1, k, n] bits (size-1 dims broadcast)."""
     batch = max(a.shape[0], b.shape[0]); reduce = max(a.shape[1], b.shape[1])
     m, k = a.shape[2:]; n = b.shape[3]
@@ -56,6 +56,8 @@ def run_ex(lib, dtype, a, b, ta=False, tb=False, pad_a=0, pad_b=0, c_init=None, 
     g.b_batch = b_mat * b.shape[1] if b.shape[0] > 1 else 0
     g.c_row, g.c_batch = n, m * n
     g.accumulate = int(c_init is not None)
+    tbias = dev(bias, dtype) if bias is not None else None
+    g.bias = tbias.data_ptr if tbias is not None else None
     ta_, tb_ = dev(abuf, dtype), dev(bbuf, dtype)
     c0 = c_init if c_init is not None else np.zeros((batch, m, n), O.storage(CODE[dtype]))
     tc = dev(c0, dtype)
@@ -69,12 +71,14 @@ def run_ex(lib, dtype, a, b, ta=False, tb=False, pad_a=0, pad_b=0, c_init=None, 
     a64 = np.broadcast_to(f64(a, dtype), (batch, reduce, m, k))
     b64 = np.broadcast_to(f64(b, dtype), (batch, reduce, k, n))
     ref64 = np.einsum("brmk,brkn->bmn", a64, b64)
+    if bias is not None:
+        ref64 = ref64 + f64(bias, dtype)[None, None, :]
     if c_init is not None:
         ref64 = ref64 + f64(c_init, dtype)
     ref = O.narrow(ref64.astype(np.float32), CODE[dtype]) if dtype in ("float16", "bfloat16") else ref64.astype(
         O.storage(CODE[dtype]))
     check_close(got, ref, dtype, k * reduce, what=f"{dtype} m{m} k{k} n{n} b{batch} r{reduce} ta{ta} tb{tb}")
-    if reduce == 1 and c_init is None:
+    if reduce == 1 and c_init is None and bias is None and oracle:
         # same-dtype reference of the path: the oracle's restatement of rp_matmul
         for bi in range(batch):
             o = O.rp_matmul(np.ascontiguousarray(a[min(bi, a.shape[0] - 1), 0]),
@@ -212,6 +216,23 @@ def test_umma_splitk_batch_reduce_accumulate(lib, dtype):
     # the broadcast-batched fp16 workload, reduced: A[16,512,64] x B[1,64,512]
     a = rand_operand(rng, (16, 1, 512, 64), dtype); b = rand_operand(rng, (1, 1, 64, 512), dtype, scale=1 / 8)
     run_ex(lib, dtype, a, b, expect=UMMA)
+
+
+@pytest.mark.parametrize("dtype", ["bfloat16", "float16", "float32"])
+def test_umma_tail_split_and_bias(lib, dtype):
+    """Tile counts just above one wave: the tiles of the sparse last wave are cut along K and summed by
+    tail_reduce_kernel (with and without a bias); checked against a float64 product (the oracle's naive
+    loop would take minutes at this size)."""
+    rng = np.random.default_rng(73)
+    for (m, k, n) in [(1280, 6144, 4096), (2304, 6400, 2104)]:     # >= 96 K blocks per tile: the tail split is on
+        a = rand_operand(rng, (1, 1, m, k), dtype); b = rand_operand(rng, (1, 1, k, n), dtype, scale=1 / np.sqrt(k))
+        if dtype == "float32":
+            lib.rpb_force_kernel(_lib.KERNEL_UMMA)
+        try:
+            run_ex(lib, dtype, a, b, expect=UMMA, oracle=False)
+            run_ex(lib, dtype, a, b, tb=True, expect=UMMA, oracle=False, bias=rand_operand(rng, (n,), dtype))
+        finally:
+            lib.rpb_force_kernel(0)
 
 
 @pytest.mark.parametrize("dtype", ["bfloat16", "float16"])
