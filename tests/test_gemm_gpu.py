@@ -70,7 +70,7 @@ def run_ex(lib, dtype, a, b, ta=False, tb=False, pad_a=0, pad_b=0, c_init=None, 
     # reference: per batch, sum over the summed problems, unrounded, then one rounding
     a64 = np.broadcast_to(f64(a, dtype), (batch, reduce, m, k))
     b64 = np.broadcast_to(f64(b, dtype), (batch, reduce, k, n))
-    ref64 = np.einsum("brmk,brkn->bmn", a64, b64)
+    ref64 = np.matmul(a64, b64).sum(axis=1)                     # BLAS per (batch, summed problem), then the sum
     if bias is not None:
         ref64 = ref64 + f64(bias, dtype)[None, None, :]
     if c_init is not None:
