@@ -206,7 +206,7 @@ int launch_simt_cfg(const RpbProblem& p, void* C, const void* A, const void* B, 
         if (get_scratch(d, bytes, stream, &a.partial)) return -1;
     }
     constexpr int NT = (BM / TM) * (BN / TN);
-    rpb_simt::gemm_kernel<T, Acc, BM, BN, BK, TM, TN><<<(unsigned)blocks, NT, 0, stream>>>(a);
+    RPB_CUDA(rpb_launch(rpb_simt::gemm_kernel<T, Acc, BM, BN, BK, TM, TN>, dim3((unsigned)blocks), dim3(NT), 0, stream, 1, a));
     g_launches++;
     if (a.splits > 1) {
         rpb_simt::launch_splitk_reduce<T, Acc>(reinterpret_cast<const Acc*>(a.partial), reinterpret_cast<T*>(C), a.splits,
@@ -226,7 +226,7 @@ int launch_dmma_inst(const rpb_simt::Args& a, long long blocks, cudaStream_t str
     auto kern = rpb_dmma::gemm_kernel<A_MN, B_MN>;
     static std::atomic<bool> attr_done[MAX_DEVICES];
     RPB_CUDA(smem_attr_once(kern, rpb_dmma::SMEM_BYTES, attr_done));
-    kern<<<(unsigned)blocks, rpb_dmma::THREADS, rpb_dmma::SMEM_BYTES, stream>>>(a);
+    RPB_CUDA(rpb_launch(kern, dim3((unsigned)blocks), dim3(rpb_dmma::THREADS), rpb_dmma::SMEM_BYTES, stream, 1, a));
     g_launches++;
     return 0;
 }
@@ -295,7 +295,7 @@ int launch_tf32_inst(const rpb_simt::Args& a, long long blocks, cudaStream_t str
     constexpr int smem = rpb_tf32::Cfg<BM, BN>::SMEM_BYTES;
     static std::atomic<bool> attr_done[MAX_DEVICES];
     RPB_CUDA(smem_attr_once(kern, smem, attr_done));
-    kern<<<(unsigned)blocks, WM * WN * 32, smem, stream>>>(a);
+    RPB_CUDA(rpb_launch(kern, dim3((unsigned)blocks), dim3(WM * WN * 32), smem, stream, 1, a));
     g_launches++;
     return 0;
 }
@@ -499,18 +499,8 @@ int launch_umma_inst(const CUtensorMap& ma, const CUtensorMap& mb, const CUtenso
     auto kern = rpb_umma::gemm_kernel<T, BN, A_MN, B_MN, PAIR>;
     static std::atomic<bool> attr_done[MAX_DEVICES];
     RPB_CUDA(smem_attr_once(kern, Cfg::SMEM_BYTES, attr_done));
-    if (PAIR) {
-        cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3((unsigned)grid); cfg.blockDim = dim3(rpb_umma::Elem<T>::THREADS);
-        cfg.dynamicSmemBytes = Cfg::SMEM_BYTES; cfg.stream = stream;
-        cudaLaunchAttribute attr;
-        attr.id = cudaLaunchAttributeClusterDimension;
-        attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
-        cfg.attrs = &attr; cfg.numAttrs = 1;
-        RPB_CUDA(cudaLaunchKernelEx(&cfg, kern, ma, mb, mc, mp, args));
-    } else {
-        kern<<<grid, rpb_umma::Elem<T>::THREADS, Cfg::SMEM_BYTES, stream>>>(ma, mb, mc, mp, args);
-    }
+    RPB_CUDA(rpb_launch(kern, dim3((unsigned)grid), dim3(rpb_umma::Elem<T>::THREADS), Cfg::SMEM_BYTES, stream, PAIR ? 2 : 1,
+                        ma, mb, mc, mp, args));
     g_launches++;
     RPB_CUDA(cudaGetLastError());
     return 0;
@@ -665,9 +655,9 @@ int launch_umma(const RpbProblem& p, void* C, const void* A, const void* B, Devi
     if (rc) return -1;
     if (a.tail_splits > 1) {
         const int rem = (int)(tiles - a.tail_begin);
-        rpb_umma::tail_reduce_kernel<T><<<dim3(rem, tile_m), tile_n / 4, 0, stream>>>(
-            a.partial, reinterpret_cast<T*>(C), reinterpret_cast<const T*>(p.bias), p.m, p.n, p.c_row, a.tiles_m, a.tiles_n,
-            a.group_n, (int)a.tail_begin, a.tail_splits, tile_m, tile_n);
+        RPB_CUDA(rpb_launch(rpb_umma::tail_reduce_kernel<T>, dim3(rem, tile_m), dim3(tile_n / 4), 0, stream, 1,
+                            (const float*)a.partial, reinterpret_cast<T*>(C), reinterpret_cast<const T*>(p.bias), p.m, p.n,
+                            (long long)p.c_row, a.tiles_m, a.tiles_n, a.group_n, (int)a.tail_begin, a.tail_splits, tile_m, tile_n));
         g_launches++;
         RPB_CUDA(cudaGetLastError());
         if (release_scratch(d, stream)) return -1;
@@ -771,10 +761,11 @@ int run_colsum(void* out, const void* in, long long rows, int cols, long long ld
     slabs = (rows + rows_per_block - 1) / rows_per_block;
     void* scratch = nullptr;
     if (get_scratch(d, sizeof(Acc) * (size_t)slabs * cols, stream, &scratch)) return -1;
-    rpb_cols::partial_kernel<T, Acc><<<dim3(col_blocks, (unsigned)slabs), rpb_cols::COLS * rpb_cols::LANES, 0, stream>>>(
-        reinterpret_cast<const T*>(in), reinterpret_cast<Acc*>(scratch), rows, cols, ld, rows_per_block);
-    rpb_cols::final_kernel<T, Acc><<<(cols + 127) / 128, 128, 0, stream>>>(
-        reinterpret_cast<const Acc*>(scratch), reinterpret_cast<T*>(out), (int)slabs, cols, accumulate);
+    RPB_CUDA(rpb_launch(rpb_cols::partial_kernel<T, Acc>, dim3(col_blocks, (unsigned)slabs), dim3(rpb_cols::COLS * rpb_cols::LANES),
+                        0, stream, 1, reinterpret_cast<const T*>(in), reinterpret_cast<Acc*>(scratch), rows, cols, ld,
+                        rows_per_block));
+    RPB_CUDA(rpb_launch(rpb_cols::final_kernel<T, Acc>, dim3((cols + 127) / 128), dim3(128), 0, stream, 1,
+                        reinterpret_cast<const Acc*>(scratch), reinterpret_cast<T*>(out), (int)slabs, cols, accumulate));
     g_launches += 2;
     if (release_scratch(d, stream)) return -1;
     RPB_CUDA(cudaGetLastError());
@@ -1063,8 +1054,8 @@ int noalloc_launch(void* C, const void* A, const void* B, int m, int k, int n, i
     if (a.splits > 1) {
         const long long elems = (long long)m * n;
         int rb = (int)((elems + 255) / 256); if (rb > d->sm_count * 8) rb = d->sm_count * 8;
-        rpb_simt::splitk_reduce_kernel<T, float><<<rb, 256, 0, stream>>>(a.partial, reinterpret_cast<T*>(C), a.splits, 1,
-                                                                        m, n, n, 0, 0, nullptr);
+        RPB_CUDA(rpb_launch(rpb_simt::splitk_reduce_kernel<T, float>, dim3(rb), dim3(256), 0, stream, 1, (const float*)a.partial,
+                            reinterpret_cast<T*>(C), a.splits, 1, m, n, (long long)n, 0ll, 0, (const T*)nullptr));
         g_launches++;
         RPB_CUDA(cudaGetLastError());
     }

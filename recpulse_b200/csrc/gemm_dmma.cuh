@@ -82,6 +82,8 @@ __global__ void __launch_bounds__(THREADS, 1)
 gemm_kernel(const rpb_simt::Args p)
 {
     extern __shared__ __align__(16) double smem[];
+    rpb_pdl_trigger();
+    rpb_pdl_wait();
     long long w = blockIdx.x;
     const int mt = (int)(w % p.tiles_m); w /= p.tiles_m;
     const int nt = (int)(w % p.tiles_n); w /= p.tiles_n;

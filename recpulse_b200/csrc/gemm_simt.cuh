@@ -19,6 +19,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "rpb_common.h"
+
 namespace rpb_simt {
 
 template <typename Acc, typename T> __device__ __forceinline__ Acc widen(T v) { return static_cast<Acc>(v); }
@@ -46,6 +48,8 @@ __global__ void __launch_bounds__((BM / TM) * (BN / TN))
 gemm_kernel(const Args p)
 {
     constexpr int NT = (BM / TM) * (BN / TN);
+    rpb_pdl_trigger();
+    rpb_pdl_wait();
     __shared__ Acc As[BK][BM + 4];
     __shared__ Acc Bs[BK][BN + 4];
 
@@ -150,6 +154,8 @@ template <typename T, typename Acc>
 __global__ void splitk_reduce_kernel(const Acc* __restrict__ partial, T* c, int splits, int batch,
                                      int m, int n, long long c_row, long long c_batch, int accumulate, const T* bias)
 {
+    rpb_pdl_trigger();
+    rpb_pdl_wait();
     const long long per_split = (long long)batch * m * n;
     const long long stride = (long long)gridDim.x * blockDim.x;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < per_split; i += stride) {
@@ -176,6 +182,8 @@ splitk_reduce_vec_kernel(const Acc* __restrict__ partial, T* c, int splits, int 
                          long long c_row, long long c_batch, int accumulate, const T* bias)
 {
     constexpr int GROUPS = 8, VECS = 32;
+    rpb_pdl_trigger();
+    rpb_pdl_wait();
     __shared__ Acc red[GROUPS][VECS][4];
     const long long per_split = (long long)batch * m * n;
     const long long nvec = per_split / 4;
@@ -231,11 +239,13 @@ inline void launch_splitk_reduce(const Acc* partial, T* c, int splits, int batch
     if (n % 4 == 0 && splits >= 4) {
         long long blocks = (elems / 4 + 31) / 32;
         if (blocks > sm_count * 8) blocks = sm_count * 8;
-        splitk_reduce_vec_kernel<T, Acc><<<(unsigned)blocks, 256, 0, stream>>>(partial, c, splits, batch, m, n, c_row, c_batch, accumulate, bias);
+        rpb_launch(splitk_reduce_vec_kernel<T, Acc>, dim3((unsigned)blocks), dim3(256), 0, stream, 1, partial, c, splits, batch, m, n, c_row,
+                   c_batch, accumulate, bias);
     } else {
         long long blocks = (elems + 255) / 256;
         if (blocks > sm_count * 8) blocks = sm_count * 8;
-        splitk_reduce_kernel<T, Acc><<<(unsigned)blocks, 256, 0, stream>>>(partial, c, splits, batch, m, n, c_row, c_batch, accumulate, bias);
+        rpb_launch(splitk_reduce_kernel<T, Acc>, dim3((unsigned)blocks), dim3(256), 0, stream, 1, partial, c, splits, batch, m, n, c_row,
+                   c_batch, accumulate, bias);
     }
 }
 

@@ -83,6 +83,8 @@ gemm_kernel(const rpb_simt::Args p)
     constexpr int MI = BM / WM / 16, NI = BN / WN / 8;
     using C = Cfg<BM, BN>;
     extern __shared__ __align__(16) float smem_f[];
+    rpb_pdl_trigger();
+    rpb_pdl_wait();
     long long w = blockIdx.x;
     const int mt = (int)(w % p.tiles_m); w /= p.tiles_m;
     const int nt = (int)(w % p.tiles_n); w /= p.tiles_n;

@@ -29,6 +29,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "rpb_common.h"
+
 namespace rpb_umma {
 
 constexpr int BLOCK_M = 128;
@@ -369,6 +371,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     if (PAIR) { __syncwarp(); cluster_sync(); }   /* the peer's barriers are initialised before anyone signals them */
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    rpb_pdl_trigger();          /* the next kernel in the stream may begin its own set-up */
+    rpb_pdl_wait();             /* everything below touches memory the previous kernel may still be writing */
 
     /* one work item per CTA (PAIR = false) or per cluster (PAIR = true) */
     const long long work_begin = PAIR ? blockIdx.x / 2 : blockIdx.x;
@@ -701,6 +705,8 @@ __global__ void tail_reduce_kernel(const float* __restrict__ scratch, T* c, cons
 {
     int mt, nt;
     tile_coords(first_tail_tile + (int)blockIdx.x, tiles_m, tiles_n, group_n, mt, nt);
+    rpb_pdl_trigger();
+    rpb_pdl_wait();
     const int lr = blockIdx.y, lc = threadIdx.x * 4;
     const int row = mt * tile_m + lr, col = nt * tile_n + lc;
     if (row >= m || col >= n) return;

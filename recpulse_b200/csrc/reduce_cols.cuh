@@ -22,6 +22,8 @@ partial_kernel(const T* __restrict__ in, Acc* __restrict__ partial, long long ro
                long long rows_per_block)
 {
     __shared__ Acc red[LANES][COLS];
+    rpb_pdl_trigger();
+    rpb_pdl_wait();
     const int cx = threadIdx.x % COLS, ly = threadIdx.x / COLS;
     const int col = blockIdx.x * COLS + cx;
     const long long r0 = (long long)blockIdx.y * rows_per_block;
@@ -43,6 +45,8 @@ partial_kernel(const T* __restrict__ in, Acc* __restrict__ partial, long long ro
 template <typename T, typename Acc>
 __global__ void final_kernel(const Acc* __restrict__ partial, T* out, int slabs, int cols, int accumulate)
 {
+    rpb_pdl_trigger();
+    rpb_pdl_wait();
     const int col = blockIdx.x * blockDim.x + threadIdx.x;
     if (col >= cols) return;
     Acc s = Acc(0);
