@@ -726,7 +726,9 @@ int run_gemm(const RpbProblem& in, void* C, const void* A, const void* B, int de
                 static int env = -1;
                 if (env < 0) { const char* e = getenv("RPB_FP32_UMMA"); env = e ? (atoi(e) ? 2 : 1) : 0; }
                 const long long big_tiles = (long long)((p.m + 127) / 128) * ((p.n + 127) / 128) * p.batch;
-                if (env != 1 && (env == 2 || forced == RPB_KERNEL_UMMA || big_tiles >= d->sm_count / 2)) {
+                /* many output tiles, or few but with enough K to split over the SMs (a skinny dW = X^T.dY) */
+                const bool heavy = p.m >= 128 && p.n >= 128 && (double)p.m * p.n * ((double)p.k * p.reduce) >= 1e9;
+                if (env != 1 && (env == 2 || forced == RPB_KERNEL_UMMA || big_tiles >= d->sm_count / 2 || heavy)) {
                     int rc = launch_umma<float>(p, C, A, B, d, stream);
                     if (rc <= 0) return rc;
                 }
