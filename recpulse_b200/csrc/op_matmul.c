@@ -47,14 +47,39 @@ static Tensor* alloc_struct(DType dtype, int ndim, const int* shape, int device_
     return t;
 }
 
+/* Output and gradient buffers come from the device's stream-ordered memory pool, with the pool told to keep
+ * freed memory instead of returning it to the driver: after the first training step an allocation costs a
+ * microsecond or two instead of a cudaMalloc.  Whoever releases the tensor (this library or RecPulse's
+ * free_tensor_device, core/tensor_device.cu:269-293) may use plain cudaFree on such memory.  Falls back to
+ * cudaMalloc when the pool is unavailable.  RPB_POOL=0 forces cudaMalloc. */
+static int device_alloc(void** out, size_t bytes, int device_id) {
+    static int pool_state[64];          /* 0 = not set up, 1 = in use, -1 = unavailable */
+    if (device_id >= 0 && device_id < 64 && pool_state[device_id] == 0) {
+        const char* e = getenv("RPB_POOL");
+        cudaMemPool_t pool;
+        unsigned long long keep = ~0ull;
+        if ((e && atoi(e) == 0) || cudaDeviceGetDefaultMemPool(&pool, device_id) != cudaSuccess ||
+            cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep) != cudaSuccess) {
+            cudaGetLastError();
+            pool_state[device_id] = -1;
+        } else {
+            pool_state[device_id] = 1;
+        }
+    }
+    if (device_id >= 0 && device_id < 64 && pool_state[device_id] == 1) {
+        if (cudaMallocAsync(out, bytes, NULL) == cudaSuccess) return 0;
+        cudaGetLastError();
+    }
+    return cudaMalloc(out, bytes) == cudaSuccess ? 0 : -1;
+}
+
 /* Uninitialised contiguous device tensor.  RecPulse's zeros_device_tensor
  * (core/tensor_device.cu:12-63) also memsets; the GEMM overwrites every element, so no memset here. */
 Tensor* rpb_tensor_empty(DType dtype, int ndim, const int* shape, int device_id) {
     if (device_id < 0) { fprintf(stderr, "recpulse_b200: device tensors only\n"); return NULL; }
     Tensor* t = alloc_struct(dtype, ndim, shape, device_id);
     if (!t) return NULL;
-    if (cudaSetDevice(device_id) != cudaSuccess ||
-        cudaMalloc(&t->data, t->size * rpb_dtype_size(dtype)) != cudaSuccess) {
+    if (cudaSetDevice(device_id) != cudaSuccess || device_alloc(&t->data, t->size * rpb_dtype_size(dtype), device_id) != 0) {
         fprintf(stderr, "recpulse_b200: cudaMalloc of %zu bytes failed: %s\n", t->size * rpb_dtype_size(dtype),
                 cudaGetErrorString(cudaGetLastError()));
         free_dims(t); free(t);
