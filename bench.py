@@ -154,10 +154,11 @@ def run_reference_arm(args, rank):
     print(json.dumps(line), flush=True)
 
 
-def reference_gpu_as_shipped(dtype_name, m, k, n, steps):
+def reference_gpu_as_shipped(dtype_name, m, k, n, steps, fill=None):
     """The unmodified reference (oracle/_ref) on the GPU, as shipped: op_matmul + backward_matmul_fn through
     its own C entry points (cuBLAS handle created and destroyed per call, transposes materialised,
-    cudaMalloc + memset per output).  Operand values are zeros; returns ms per fwd+bwd step, or None."""
+    cudaMalloc + memset per output).  `fill` = device pointers (A, B, dC) whose contents are copied into the
+    reference's tensors, so it multiplies the same values as the other arms.  Returns ms per step, or None."""
     so = os.path.join(ROOT, "oracle", "_ref", "recpulse_cuda.so")
     if not os.path.exists(so):
         return None
@@ -188,6 +189,11 @@ def reference_gpu_as_shipped(dtype_name, m, k, n, steps):
     a, b, g = make((m, k), True), make((k, n), True), make((m, n), False)
     if not a or not b or not g:
         return None
+    if fill:
+        ref.cudaMemcpy.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_int]
+        es = {"float32": 4, "float64": 8, "float16": 2, "bfloat16": 2}[dtype_name]
+        for t, src, cnt in ((a, fill[0], m * k), (b, fill[1], k * n), (g, fill[2], m * n)):
+            ref.cudaMemcpy(t.contents.data, src, cnt * es, 3)          # device to device
 
     def step():
         out = ref.op_matmul(a, b)
@@ -403,16 +409,17 @@ def main():
             tot += c0.elapsed_time(c1)
         cublas = {"tflops": flops_step / (tot / args.steps * 1e-3) / 1e12, "ms_per_step": tot / args.steps,
                   "what": "torch.matmul x3 (cuBLAS, warm handle, outputs preallocated)"}
-        ref_ms = reference_gpu_as_shipped(dtype_name, rows, k, n, min(args.steps, 5))
+        ref_ms = reference_gpu_as_shipped(dtype_name, rows, k, n, min(args.steps, 5), fill=(A.data_ptr(), Bm.data_ptr(), dC.data_ptr()))
         if ref_ms:
             cublas["reference_as_shipped_ms_per_step"] = ref_ms
             cublas["reference_as_shipped_tflops"] = flops_step / (ref_ms * 1e-3) / 1e12
         # the same step through this library's autograd node (allocation + synchronisation included)
         import recpulse_b200 as rpb
         dn = dtype_name
-        hA = rpb.Tensor.from_numpy(np.zeros((rows, k), np.uint16 if es == 2 else (np.float32 if es == 4 else np.float64)), dtype=dn, requires_grad=True)
-        hB = rpb.Tensor.from_numpy(np.zeros((k, n), np.uint16 if es == 2 else (np.float32 if es == 4 else np.float64)), dtype=dn, requires_grad=True)
-        hG = rpb.Tensor.from_numpy(np.zeros((rows, n), np.uint16 if es == 2 else (np.float32 if es == 4 else np.float64)), dtype=dn)
+        def to_lib(t, grad):                                         # same operand values as the kernel-only arm
+            host = t.contiguous().view(torch.int16 if es == 2 else t.dtype).cpu().numpy()
+            return rpb.Tensor.from_numpy(host.view(np.uint16) if es == 2 else host, dtype=dn, requires_grad=grad)
+        hA, hB, hG = to_lib(A, True), to_lib(Bm, True), to_lib(dC, False)
         def node_step():
             y = hA.op_matmul(hB); y.backward(hG)
             for t in (hA, hB):
