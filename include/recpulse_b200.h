@@ -117,6 +117,13 @@ void backward_matmul_fn(GradFn* self, Tensor* grad_output);
 Tensor* op_linear(Tensor* x, Tensor* w, Tensor* bias);
 void backward_linear_fn(GradFn* self, Tensor* grad_output);
 
+/* y = x . w + h . u (+ bias) as ONE node: the gate pre-activations of an LSTM / GRU cell, which RecPulse
+ * builds from two op_matmul nodes and an op_add (recpulse/module.py:289, 334-335).  The second product is
+ * accumulated into the output inside the GEMM epilogue.  Shapes as for op_linear, both products must have
+ * the same result shape; bias may be NULL.  Backward gives all four matmul gradients and the bias gradient. */
+Tensor* op_linear2(Tensor* x, Tensor* w, Tensor* h, Tensor* u, Tensor* bias);
+void backward_linear2_fn(GradFn* self, Tensor* grad_output);
+
 /* out[j] (+)= sum over i < rows of in[i * row_stride + j], j < cols; fp32 (fp64 for float64) sums in a
  * fixed order, one rounding.  Runs on `stream` without synchronising. */
 int rp_colsum_ex(void* out, const void* in, long long rows, int cols, long long row_stride, DType dtype,

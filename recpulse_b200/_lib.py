@@ -56,6 +56,8 @@ SYMBOLS = {
     "backward_matmul_fn": (None, [C.POINTER(GradFn), TP]),
     "op_linear": (TP, [TP, TP, TP]),
     "backward_linear_fn": (None, [C.POINTER(GradFn), TP]),
+    "op_linear2": (TP, [TP, TP, TP, TP, TP]),
+    "backward_linear2_fn": (None, [C.POINTER(GradFn), TP]),
     "rp_colsum_ex": (C.c_int, [C.c_void_p, C.c_void_p, C.c_longlong, C.c_int, C.c_longlong, C.c_int, C.c_int, C.c_int,
                                C.c_void_p]),
     "rpb_gemm_packed": (None, [C.POINTER(RpbGemm), C.c_int, C.c_int, C.c_int]),

@@ -19,6 +19,7 @@
 #define RPB_MAX_BATCH_DIMS 8
 
 void* rpb_reference_symbol(const char* name);   /* gemm_dispatch.cu */
+static void bias_grad_into(Tensor* bias, Tensor* grad_output);
 
 /* ------------------------------------------------------------------ tensor helpers */
 
@@ -285,6 +286,56 @@ static bool bias_ok(const Tensor* bias, const Tensor* a, int n) {
     return true;
 }
 
+/* out (+)= a . b (+ bias) for operands that already passed the shape checks; out is packed with the
+ * broadcast batch shape of a and b */
+static int product_into(Tensor* out, const Tensor* a, const Tensor* b, const Tensor* bias, int accumulate,
+                        int nd, const int* oshape) {
+    const int m = a->shape[a->ndim - 2], k = a->shape[a->ndim - 1], n = b->shape[b->ndim - 1];
+    RpbGemm g;
+    rpb_gemm_packed(&g, m, k, n);
+    g.a_row = a->strides[a->ndim - 2]; g.a_col = a->strides[a->ndim - 1];
+    g.b_row = b->strides[b->ndim - 2]; g.b_col = b->strides[b->ndim - 1];
+    g.a_batch = g.b_batch = g.c_batch = 0;
+    g.bias = bias ? bias->data : NULL;
+    g.accumulate = accumulate;
+    BatchDim bd[RPB_MAX_BATCH_DIMS];
+    int nbd = 0;
+    for (int i = 0; i < nd; i++) {
+        if (oshape[i] == 1) continue;
+        bd[nbd].extent = oshape[i];
+        bd[nbd].a = batch_stride(a, nd, i); bd[nbd].b = batch_stride(b, nd, i); bd[nbd].c = out->strides[i];
+        nbd++;
+    }
+    return run_batched(out->data, a->data, b->data, g, bd, nbd, NULL, 0, a->dtype, a->device_id);
+}
+
+static bool operands_ok(const Tensor* a, const Tensor* b) {      /* ops/ops.c:6817-6820, with ndim >= 2 */
+    if (!a || !b) return false;
+    if (a->ndim < 2 || b->ndim < 2) return false;
+    if (a->shape[a->ndim - 1] != b->shape[b->ndim - 2]) return false;
+    return a->dtype == b->dtype && a->device_id == b->device_id;
+}
+
+/* Meta + GradFn for a fresh output, with RecPulse's grad_fn_attach bookkeeping (ops/ops.c:11-19) */
+static int attach_node(Tensor* out, BackwardFunction backward, Tensor** in, int n_in) {
+    out->metadata = (Meta*)calloc(1, sizeof(Meta));
+    GradFn* fn = (GradFn*)calloc(1, sizeof(GradFn));
+    Tensor** inputs = (Tensor**)malloc(n_in * sizeof(Tensor*));
+    if (!out->metadata || !fn || !inputs) { free(fn); free(inputs); return -1; }
+    out->metadata->requires_grad = true;
+    out->metadata->is_leaf = false;
+    fn->backward = backward;
+    fn->num_inputs = n_in;
+    fn->inputs = inputs;
+    fn->saved_data = NULL;
+    fn->owner = out;
+    for (int i = 0; i < n_in; i++) { inputs[i] = in[i]; if (in[i] != out) in[i]->refcount++; }
+    out->metadata->grad_fn = fn;
+    return 0;
+}
+
+static bool wants_grad(const Tensor* t) { return t && t->metadata && t->metadata->requires_grad; }
+
 /* shared by op_matmul (bias == NULL) and op_linear */
 static Tensor* matmul_node(Tensor* a, Tensor* b, Tensor* bias) {
     if (!a || !b) return NULL;
@@ -301,7 +352,7 @@ static Tensor* matmul_node(Tensor* a, Tensor* b, Tensor* bias) {
     }
     if (bias && !bias_ok(bias, a, b->shape[b->ndim - 1])) return NULL;
 
-    const int m = a->shape[a->ndim - 2], k = a->shape[a->ndim - 1], n = b->shape[b->ndim - 1];
+    const int m = a->shape[a->ndim - 2], n = b->shape[b->ndim - 1];
     int nd = 0, oshape[RPB_MAX_BATCH_DIMS + 2];
     if (broadcast_batch(a, b, &nd, oshape)) return NULL;
     oshape[nd] = m; oshape[nd + 1] = n;
@@ -309,45 +360,17 @@ static Tensor* matmul_node(Tensor* a, Tensor* b, Tensor* bias) {
     Tensor* out = rpb_tensor_empty(a->dtype, nd + 2, oshape, a->device_id);
     if (!out) return NULL;
 
-    RpbGemm g;
-    rpb_gemm_packed(&g, m, k, n);
-    g.a_row = a->strides[a->ndim - 2]; g.a_col = a->strides[a->ndim - 1];
-    g.b_row = b->strides[b->ndim - 2]; g.b_col = b->strides[b->ndim - 1];
-    g.a_batch = g.b_batch = g.c_batch = 0;
-    g.bias = bias ? bias->data : NULL;
-    BatchDim bd[RPB_MAX_BATCH_DIMS];
-    int nbd = 0;
-    for (int i = 0; i < nd; i++) {
-        if (oshape[i] == 1) continue;
-        bd[nbd].extent = oshape[i];
-        bd[nbd].a = batch_stride(a, nd, i); bd[nbd].b = batch_stride(b, nd, i); bd[nbd].c = out->strides[i];
-        nbd++;
-    }
-    int rc = run_batched(out->data, a->data, b->data, g, bd, nbd, NULL, 0, a->dtype, a->device_id);
+    int rc = product_into(out, a, b, bias, 0, nd, oshape);
     /* callers assume the result is complete on return (every RecPulse device op synchronises) */
     if (rc == 0 && cudaStreamSynchronize(NULL) != cudaSuccess) rc = -1;
     if (rc != 0) { rpb_tensor_release(out); return NULL; }
 
-    const bool needs_grad = (a->metadata && a->metadata->requires_grad) || (b->metadata && b->metadata->requires_grad) ||
-                            (bias && bias->metadata && bias->metadata->requires_grad);
-    if (needs_grad) {
-        const int n_in = bias ? 3 : 2;
-        out->metadata = (Meta*)calloc(1, sizeof(Meta));
-        GradFn* fn = (GradFn*)calloc(1, sizeof(GradFn));
-        Tensor** inputs = (Tensor**)malloc(n_in * sizeof(Tensor*));
-        if (!out->metadata || !fn || !inputs) { free(fn); free(inputs); rpb_tensor_release(out); return NULL; }
-        out->metadata->requires_grad = true;
-        out->metadata->is_leaf = false;
-        fn->backward = bias ? backward_linear_fn : backward_matmul_fn;
-        fn->num_inputs = n_in;
-        fn->inputs = inputs;
-        inputs[0] = a; inputs[1] = b;
-        if (bias) inputs[2] = bias;
-        fn->saved_data = NULL;
-        /* grad_fn_attach, ops/ops.c:11-19 */
-        fn->owner = out;
-        for (int i = 0; i < n_in; i++) if (inputs[i] != out) inputs[i]->refcount++;
-        out->metadata->grad_fn = fn;
+    if (wants_grad(a) || wants_grad(b) || wants_grad(bias)) {
+        Tensor* in[3] = {a, b, bias};
+        if (attach_node(out, bias ? backward_linear_fn : backward_matmul_fn, in, bias ? 3 : 2)) {
+            rpb_tensor_release(out);
+            return NULL;
+        }
     }
     return out;
 }
@@ -456,9 +479,14 @@ void backward_linear_fn(GradFn* self, Tensor* grad_output) {
     Tensor* bias = self->inputs[2];
     if (!x || !w || !bias || x->device_id < 0) return;
     if (matmul_grads(x, w, grad_output)) return;
-    if (!(bias->metadata && bias->metadata->requires_grad)) return;
+    bias_grad_into(bias, grad_output);
+}
+
+/* bias gradient shared by the Linear nodes */
+static void bias_grad_into(Tensor* bias, Tensor* grad_output) {
+    if (!wants_grad(bias)) return;
     if (!is_contiguous(grad_output)) {
-        fprintf(stderr, "recpulse_b200: backward_linear_fn: upstream gradient must be packed for the bias gradient\n");
+        fprintf(stderr, "recpulse_b200: upstream gradient must be packed for the bias gradient\n");
         return;
     }
     const int n = grad_output->shape[grad_output->ndim - 1];
@@ -475,6 +503,44 @@ void backward_linear_fn(GradFn* self, Tensor* grad_output) {
     if (rc == 0 && cudaStreamSynchronize(NULL) != cudaSuccess) rc = -1;
     if (rc != 0) { if (fresh) rpb_tensor_release(grad); return; }
     if (fresh) bias->metadata->grad = grad;
+}
+
+Tensor* op_linear2(Tensor* x, Tensor* w, Tensor* h, Tensor* u, Tensor* bias) {
+    if (!operands_ok(x, w) || !operands_ok(h, u)) return NULL;
+    if (x->dtype != h->dtype || x->device_id != h->device_id) return NULL;
+    if (x->device_id < 0) {
+        fprintf(stderr, "recpulse_b200: op_linear2 on host tensors: this library has no CPU path\n");
+        return NULL;
+    }
+    const int n = w->shape[w->ndim - 1];
+    if (u->shape[u->ndim - 1] != n) return NULL;
+    if (bias && !bias_ok(bias, x, n)) return NULL;
+    int nd = 0, oshape[RPB_MAX_BATCH_DIMS + 2], nd2 = 0, oshape2[RPB_MAX_BATCH_DIMS + 2];
+    if (broadcast_batch(x, w, &nd, oshape) || broadcast_batch(h, u, &nd2, oshape2)) return NULL;
+    oshape[nd] = x->shape[x->ndim - 2]; oshape[nd + 1] = n;
+    oshape2[nd2] = h->shape[h->ndim - 2]; oshape2[nd2 + 1] = n;
+    if (nd != nd2 || memcmp(oshape, oshape2, sizeof(int) * (nd + 2)) != 0) return NULL;   /* both products, same shape */
+
+    Tensor* out = rpb_tensor_empty(x->dtype, nd + 2, oshape, x->device_id);
+    if (!out) return NULL;
+    int rc = product_into(out, x, w, bias, 0, nd, oshape);
+    if (rc == 0) rc = product_into(out, h, u, NULL, 1, nd, oshape);          /* second product lands in the epilogue's "+= C" */
+    if (rc == 0 && cudaStreamSynchronize(NULL) != cudaSuccess) rc = -1;
+    if (rc != 0) { rpb_tensor_release(out); return NULL; }
+    if (wants_grad(x) || wants_grad(w) || wants_grad(h) || wants_grad(u) || wants_grad(bias)) {
+        Tensor* in[5] = {x, w, h, u, bias};
+        if (attach_node(out, backward_linear2_fn, in, bias ? 5 : 4)) { rpb_tensor_release(out); return NULL; }
+    }
+    return out;
+}
+
+void backward_linear2_fn(GradFn* self, Tensor* grad_output) {
+    if (!self || !grad_output || (self->num_inputs != 4 && self->num_inputs != 5) || !self->inputs) return;
+    Tensor** in = self->inputs;
+    if (!in[0] || !in[1] || !in[2] || !in[3] || in[0]->device_id < 0) return;
+    if (matmul_grads(in[0], in[1], grad_output)) return;
+    if (matmul_grads(in[2], in[3], grad_output)) return;
+    if (self->num_inputs == 5 && in[4]) bias_grad_into(in[4], grad_output);
 }
 
 int rpb_backward_node(Tensor* out, Tensor* grad_output) {

@@ -152,6 +152,13 @@ class Tensor:
             raise RuntimeError("op_linear operation failed")
         return Tensor(p, keepalive=(self, weight, bias))
 
+    def op_linear2(self, weight: "Tensor", h: "Tensor", u: "Tensor", bias: "Tensor | None" = None) -> "Tensor":
+        """y = self . weight + h . u + bias as one node (LSTM / GRU gate pre-activations)."""
+        p = _lib.load().op_linear2(self._p, weight._p, h._p, u._p, bias._p if bias is not None else None)
+        if not p:
+            raise RuntimeError("op_linear2 operation failed")
+        return Tensor(p, keepalive=(self, weight, h, u, bias))
+
     def backward(self, grad_output: "Tensor") -> None:
         """Run this node's backward with an explicit upstream gradient and free the node."""
         if _lib.load().rpb_backward_node(self._p, grad_output._p) != 0:

@@ -203,3 +203,32 @@ def test_colsum_entry_point(lib):
             assert lib.rp_colsum_ex(C.c_void_p(tout.data_ptr), C.c_void_p(tin.data_ptr), rows, cols, cols + pad, CODE[dtype],
                                     0, 0, None) == 0
             check_close(tout.to_numpy(), O.bias_grad(np.ascontiguousarray(x[:, :cols]), CODE[dtype]), dtype, rows, "colsum")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "float64", "float16", "bfloat16"])
+def test_gate_node_two_products_one_output(lib, dtype):
+    """op_linear2: x.W_ih + h.W_hh + b as one node (LSTMCell / GRUCell gate pre-activations,
+    recpulse/module.py:289, 334-335), against the reference composition matmul, matmul, add, add."""
+    from helpers import f64
+    rng = np.random.default_rng(79)
+    for (bsz, e, hdim, n) in [(64, 64, 256, 1024), (5, 24, 40, 72), (128, 512, 512, 2048)]:
+        x = rand_operand(rng, (bsz, e), dtype); w = rand_operand(rng, (e, n), dtype, scale=1 / np.sqrt(e))
+        h = rand_operand(rng, (bsz, hdim), dtype); u = rand_operand(rng, (hdim, n), dtype, scale=1 / np.sqrt(hdim))
+        b = rand_operand(rng, (n,), dtype); g = rand_operand(rng, (bsz, n), dtype)
+        X, W, H, U, B = (T(v, dtype, True) for v in (x, w, h, u, b))
+        y = X.op_linear2(W, H, U, B)
+        assert y.shape == (bsz, n)
+        ref = f64(x, dtype) @ f64(w, dtype) + f64(h, dtype) @ f64(u, dtype) + f64(b, dtype)
+        got = f64(y.to_numpy(), dtype)
+        tol = {"float32": 2e-6, "float64": 1e-13, "float16": 1e-3, "bfloat16": 6e-3}[dtype]
+        assert np.linalg.norm(got - ref) / np.linalg.norm(ref) < tol
+        # the reference's own composition (each op rounds to the storage dtype) is no closer to the exact result
+        comp = O.linear_forward(x, w, np.zeros_like(b), CODE[dtype])
+        y.backward(T(g, dtype))
+        dx, dw = O.matmul_backward(x, w, g, CODE[dtype]); dh, du = O.matmul_backward(h, u, g, CODE[dtype])
+        check_close(X.grad.to_numpy(), dx, dtype, n, "dx"); check_close(W.grad.to_numpy(), dw, dtype, bsz, "dw")
+        check_close(H.grad.to_numpy(), dh, dtype, n, "dh"); check_close(U.grad.to_numpy(), du, dtype, bsz, "du")
+        check_close(B.grad.to_numpy(), O.bias_grad(g, CODE[dtype]), dtype, bsz, "dbias")
+        del comp
+    with pytest.raises(RuntimeError):
+        T(x, dtype).op_linear2(T(w, dtype), T(h, dtype), T(rand_operand(rng, (hdim, n + 8), dtype), dtype))
