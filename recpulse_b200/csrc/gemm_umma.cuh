@@ -1,15 +1,15 @@
 /*
- * tcgen05 GEMM for float16 / bfloat16 (fp32 accumulation in tensor memory).
+ * tcgen05 GEMM for float16 / bfloat16 and, as 3xTF32, float32 (fp32 accumulation in tensor memory).
  *
- * One persistent CTA per SM, 10 warps:
- *   warp 0      TMA producer: 128B-swizzled tiles of A and B into a shared-memory ring
- *   warp 1      owns tensor memory; one lane issues tcgen05.mma (M=128, N=BN, K=16)
- *   warps 2..9  epilogue: tcgen05.ld of the fp32 accumulator, rounding, staging in shared memory
- *               and TMA stores (or register stores with optional "+= C"); fp32 partial tiles
- *               when K is split across CTAs.  Two warps share each tensor-memory lane quarter
- *               and take alternate column chunks.
- * Two accumulators (2 x BN tensor-memory columns) let the epilogue of tile i overlap
- * the main loop of tile i+1.
+ * One persistent CTA per SM (or one cluster of two CTAs per pair of SMs, cta_group::2):
+ *   warp 0        TMA producer: 128B-swizzled tiles of A and B into a shared-memory ring
+ *   warp 1        owns tensor memory; one lane issues tcgen05.mma (M = 128 or 256, K = 32 bytes per instruction)
+ *   warps 2..9    epilogue: tcgen05.ld of the fp32 accumulator, bias, rounding, staging in shared memory
+ *                 and TMA stores (or register stores with optional "+= C"); fp32 partial tiles
+ *                 when K is split across CTAs.  Two warps share each tensor-memory lane quarter
+ *                 and take alternate column chunks.
+ *   warps 10..13  float32 only: split each delivered tile into hi and lo TF32 parts in shared memory
+ * Two accumulators in tensor memory let the epilogue of tile i overlap the main loop of tile i+1.
  *
  * Operands are read where they lie: each one may be K-major (reduction index
  * contiguous) or MN-major (output index contiguous); the TMA descriptor is built from
