@@ -120,6 +120,14 @@ int device_state(int device_id, DeviceState** out) {
             RPB_CUDA(cudaMalloc(&d.status, sizeof(int)));
             RPB_CUDA(cudaMemset(d.status, 0, sizeof(int)));
             RPB_CUDA(cudaEventCreateWithFlags(&d.scratch_free, cudaEventDisableTiming));
+            {   /* temporaries for packed operands come from the stream-ordered pool: let it keep freed blocks */
+                const char* e = getenv("RPB_POOL");
+                cudaMemPool_t pool;
+                unsigned long long keep = ~0ull;
+                if (!(e && atoi(e) == 0) && cudaDeviceGetDefaultMemPool(&pool, device_id) == cudaSuccess)
+                    cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep);
+                cudaGetLastError();
+            }
             if (!g_encode) {
                 void* fn = nullptr;
                 cudaDriverEntryPointQueryResult qres;
@@ -673,6 +681,123 @@ int launch_umma(const RpbProblem& p, void* C, const void* A, const void* B, Devi
     return 0;
 }
 
+/* ------------------------------------------------------------------ packing of layouts TMA cannot address */
+
+/* dst[(z, o, i)] = src[z_b * batch_s + z_r * reduce_s + o * outer_s + i * inner_s] for o < outer, i < inner
+ * (zero for inner <= i < inner_pad): the operand as packed rows of inner_pad elements. */
+template <typename T>
+__global__ void pack_operand_kernel(T* __restrict__ dst, const T* __restrict__ src, int outer, int inner, int inner_pad,
+                                    long long outer_s, long long inner_s, int nbatch, long long batch_s, int nreduce,
+                                    long long reduce_s)
+{
+    rpb_pdl_trigger();
+    rpb_pdl_wait();
+    const long long total = (long long)nbatch * nreduce * outer * inner_pad;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += stride) {
+        const int i = (int)(e % inner_pad);
+        long long t = e / inner_pad;
+        const int o = (int)(t % outer); t /= outer;
+        const int r = (int)(t % nreduce);
+        const int b = (int)(t / nreduce);
+        T v = T(0.f);
+        if (i < inner) v = src[b * batch_s + r * reduce_s + o * outer_s + i * inner_s];
+        dst[e] = v;
+    }
+}
+
+/* dst[b][r][c] = src[b][r][c] for c < cols: takes the padding out of an output computed with an aligned
+ * leading dimension */
+template <typename T>
+__global__ void unpack_rows_kernel(T* __restrict__ dst, const T* __restrict__ src, long long rows, int cols,
+                                   long long dst_row_s, long long src_row_s, int nbatch, long long dst_batch_s,
+                                   long long src_batch_s)
+{
+    rpb_pdl_trigger();
+    rpb_pdl_wait();
+    const long long total = (long long)nbatch * rows * cols;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += stride) {
+        const int c = (int)(e % cols);
+        long long t = e / cols;
+        const long long r = t % rows;
+        const int b = (int)(t / rows);
+        dst[b * dst_batch_s + r * dst_row_s + c] = src[b * src_batch_s + r * src_row_s + c];
+    }
+}
+
+template <typename T> int launch_umma(const RpbProblem& p, void* C, const void* A, const void* B, DeviceState* d, cudaStream_t stream);
+
+/* A large 16-bit (or fp32) problem whose operands are not TMA-addressable (odd leading dimension, unaligned
+ * base, both strides != 1): copy the offending operands once, from the stream-ordered pool, into packed rows
+ * padded to 16 bytes -- keeping the operand's orientation when one of its strides is 1, so that the copy reads
+ * and writes contiguously -- and run the tcgen05 kernel on the copies.  RecPulse copies every non-contiguous
+ * operand (ops/ops.c:21-25); here it only happens for layouts the TMA engine rejects.  1 = not applicable. */
+template <typename T>
+int launch_umma_packed(const RpbProblem& p, void* C, const void* A, const void* B, DeviceState* d, cudaStream_t stream) {
+    if (d->cc_major != 10) return 1;
+    constexpr int ES = (int)sizeof(T);
+    constexpr int AL = 16 / ES;
+    const double flops = 2.0 * p.m * p.n * (double)p.k * p.batch * p.reduce;
+    if (flops < 5e8 || p.m < 64 || p.n < 64) return 1;
+    OperandPlan pa = plan_operand(A, p.m, p.k, p.a_row, p.a_col, p.batch, p.a_batch, p.reduce, p.a_reduce, ES);
+    OperandPlan pb = plan_operand(B, p.n, p.k, p.b_col, p.b_row, p.batch, p.b_batch, p.reduce, p.b_reduce, ES);
+    const bool c_odd = !p.accumulate && ((reinterpret_cast<uintptr_t>(C) & 15u) != 0 || p.c_row % AL != 0 ||
+                                          (p.batch > 1 && p.c_batch % AL != 0));
+    if (pa.ok && pb.ok && !c_odd) return 1;             /* nothing to pack: the caller already tried the direct path */
+    RpbProblem q = p;
+    void* tmp[3] = {nullptr, nullptr, nullptr};
+    const void* A2 = A; const void* B2 = B;
+    /* packs one operand; on return *mn_stride / *k_stride are its new element strides */
+    auto pack = [&](int which, const void* src, int mn, long long mn_s, long long k_s, long long batch_s, long long reduce_s,
+                    const void** out, long long* new_mn_s, long long* new_k_s, long long* new_reduce_s,
+                    long long* new_batch_s) -> int {
+        const bool keep_mn_major = mn_s == 1 && k_s != 1;
+        const int outer = keep_mn_major ? p.k : mn, inner = keep_mn_major ? mn : p.k;
+        const long long outer_s = keep_mn_major ? k_s : mn_s, inner_s = keep_mn_major ? mn_s : k_s;
+        const int inner_pad = (inner + AL - 1) / AL * AL;
+        const int nb = (p.batch > 1 && batch_s != 0) ? p.batch : 1;
+        const int nr = (p.reduce > 1 && reduce_s != 0) ? p.reduce : 1;
+        const size_t mat = (size_t)outer * inner_pad;
+        const size_t elems = (size_t)nb * nr * mat;
+        RPB_CUDA(cudaMallocAsync(&tmp[which], elems * ES, stream));
+        long long blocks = (long long)((elems + 255) / 256);
+        if (blocks > d->sm_count * 16) blocks = d->sm_count * 16;
+        RPB_CUDA(rpb_launch(pack_operand_kernel<T>, dim3((unsigned)blocks), dim3(256), 0, stream, 1, reinterpret_cast<T*>(tmp[which]),
+                            reinterpret_cast<const T*>(src), outer, inner, inner_pad, outer_s, inner_s, nb, batch_s, nr, reduce_s));
+        g_launches++;
+        *out = tmp[which];
+        *new_mn_s = keep_mn_major ? 1 : inner_pad;
+        *new_k_s = keep_mn_major ? inner_pad : 1;
+        *new_reduce_s = nr > 1 ? (long long)mat : 0;
+        *new_batch_s = nb > 1 ? (long long)mat * nr : 0;
+        return 0;
+    };
+    int rc = 0;
+    if (!pa.ok) rc = pack(0, A, p.m, p.a_row, p.a_col, p.a_batch, p.a_reduce, &A2, &q.a_row, &q.a_col, &q.a_reduce, &q.a_batch);
+    if (!rc && !pb.ok) rc = pack(1, B, p.n, p.b_col, p.b_row, p.b_batch, p.b_reduce, &B2, &q.b_col, &q.b_row, &q.b_reduce, &q.b_batch);
+    /* an output with an odd leading dimension would fall to per-element stores: write it padded, then unpad */
+    void* C2 = C;
+    const int n_pad = (p.n + AL - 1) / AL * AL;
+    if (!rc && c_odd) {
+        RPB_CUDA(cudaMallocAsync(&tmp[2], (size_t)p.batch * p.m * n_pad * ES, stream));
+        C2 = tmp[2];
+        q.c_row = n_pad; q.c_batch = (long long)p.m * n_pad;
+    }
+    if (!rc) rc = launch_umma<T>(q, C2, A2, B2, d, stream);
+    if (!rc && c_odd) {
+        const long long elems = (long long)p.batch * p.m * p.n;
+        long long blocks = (elems + 255) / 256;
+        if (blocks > d->sm_count * 16) blocks = d->sm_count * 16;
+        RPB_CUDA(rpb_launch(unpack_rows_kernel<T>, dim3((unsigned)blocks), dim3(256), 0, stream, 1, reinterpret_cast<T*>(C),
+                            reinterpret_cast<const T*>(C2), (long long)p.m, p.n, p.c_row, (long long)n_pad, p.batch, p.c_batch,
+                            (long long)p.m * n_pad));
+        g_launches++;
+    }
+    for (int i = 0; i < 3; ++i) if (tmp[i]) cudaFreeAsync(tmp[i], stream);
+    return rc;
+}
+
 /* ------------------------------------------------------------------ dispatch */
 
 int validate(const RpbProblem& p, const void* C, const void* A, const void* B) {
@@ -710,8 +835,12 @@ int run_gemm(const RpbProblem& in, void* C, const void* A, const void* B, int de
     const int forced = forced_family();
     const bool half_type = p.dtype == DTYPE_FLOAT16 || p.dtype == DTYPE_BFLOAT16;
     if (half_type && forced != RPB_KERNEL_SIMT) {
-        int rc = p.dtype == DTYPE_BFLOAT16 ? launch_umma<__nv_bfloat16>(p, C, A, B, d, stream)
-                                           : launch_umma<__half>(p, C, A, B, d, stream);
+        /* large problems with an operand or output the TMA engine cannot address are packed / padded first */
+        int rc = p.dtype == DTYPE_BFLOAT16 ? launch_umma_packed<__nv_bfloat16>(p, C, A, B, d, stream)
+                                           : launch_umma_packed<__half>(p, C, A, B, d, stream);
+        if (rc <= 0) return rc;
+        rc = p.dtype == DTYPE_BFLOAT16 ? launch_umma<__nv_bfloat16>(p, C, A, B, d, stream)
+                                       : launch_umma<__half>(p, C, A, B, d, stream);
         if (rc <= 0) return rc;
         if (forced == RPB_KERNEL_UMMA) {
             fprintf(stderr, "recpulse_b200: tcgen05 path forced but the operand layout is not TMA-addressable\n");
@@ -729,7 +858,9 @@ int run_gemm(const RpbProblem& in, void* C, const void* A, const void* B, int de
                 /* many output tiles, or few but with enough K to split over the SMs (a skinny dW = X^T.dY) */
                 const bool heavy = p.m >= 128 && p.n >= 128 && (double)p.m * p.n * ((double)p.k * p.reduce) >= 1e9;
                 if (env != 1 && (env == 2 || forced == RPB_KERNEL_UMMA || big_tiles >= d->sm_count / 2 || heavy)) {
-                    int rc = launch_umma<float>(p, C, A, B, d, stream);
+                    int rc = launch_umma_packed<float>(p, C, A, B, d, stream);  /* odd strides: pack / pad once */
+                    if (rc <= 0) return rc;
+                    rc = launch_umma<float>(p, C, A, B, d, stream);
                     if (rc <= 0) return rc;
                 }
                 int rc = launch_tf32(p, C, A, B, d, stream);

@@ -242,6 +242,21 @@ def test_unaligned_half_operands_take_the_general_path(lib, dtype):
     run_ex(lib, dtype, a, b, expect=(_lib.KERNEL_SIMT,))
 
 
+@pytest.mark.parametrize("dtype", ["bfloat16", "float16"])
+def test_large_unaligned_half_operands_are_packed_for_the_tensor_cores(lib, dtype):
+    """Odd leading dimensions (a vocabulary of 50257, a padded view) cannot be described to the TMA engine;
+    above ~0.5 GFLOP the offending operands are packed once and the tcgen05 kernel still runs."""
+    rng = np.random.default_rng(83)
+    for (m, k, n, ta, tb, pa, pb) in [(520, 1001, 1003, False, False, 0, 0), (1000, 999, 520, True, True, 3, 5),
+                                      (640, 1024, 1030, False, False, 0, 0)]:
+        a = rand_operand(rng, (1, 1, m, k), dtype); b = rand_operand(rng, (1, 1, k, n), dtype, scale=1 / np.sqrt(k))
+        run_ex(lib, dtype, a, b, ta=ta, tb=tb, pad_a=pa, pad_b=pb, expect=UMMA, oracle=False)
+    # batched, summed problems, broadcast B, accumulate: the packed copies keep the batch structure
+    a = rand_operand(rng, (3, 2, 300, 333), dtype); b = rand_operand(rng, (1, 2, 333, 520), dtype, scale=0.05)
+    run_ex(lib, dtype, a, b, expect=UMMA, oracle=False)
+    run_ex(lib, dtype, a, b, tb=True, c_init=rand_operand(rng, (3, 300, 520), dtype), expect=UMMA, oracle=False)
+
+
 @pytest.mark.parametrize("dtype", ["float32", "float64", "float16", "bfloat16"])
 def test_rp_matmul_and_matmul_kernel_device(lib, dtype):
     rng = np.random.default_rng(31)
