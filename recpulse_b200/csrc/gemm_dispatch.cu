@@ -523,18 +523,52 @@ int launch_umma_bn(bool a_mn, bool b_mn, const CUtensorMap& ma, const CUtensorMa
     return launch_umma_inst<T, BN, true, true, PAIR>(ma, mb, mc, mp, args, grid, stream);
 }
 
-/* Two-CTA tiles (256 x 256 per cluster) pay off once every cluster has a tile to work on and the
- * main loop is long enough to hide the pair's cross-CTA hand-offs (measured: at K = 64 the one-CTA
- * kernel is 1.3-1.5x faster, at K >= 512 the pair wins). */
-bool want_pair(int m, int n, long long k_total, int batch, int sm_count) {
-    static int env = -1;
-    if (env < 0) { const char* e = getenv("RPB_UMMA_PAIR"); env = e ? (atoi(e) ? 1 : 0) + 1 : 0; }
-    if (env == 1) return false;
-    if (n < 256 || m < 256) return false;
-    if (env == 2) return true;
-    if (k_total < 512) return false;
-    const long long tiles = (long long)((m + 255) / 256) * ((n + 255) / 256) * batch;
-    return tiles >= sm_count / 2;
+/* Tile shape and K slices, chosen by a small cost model in microseconds fitted to measurements on B200
+ * (cold operands).  A CTA's main loop advances one K block (128 bytes of K) per step; the step time depends on
+ * the tile width much less than the arithmetic does, because narrow tiles are bound by the shared-memory fill
+ * rate rather than the tensor pipe.  A CTA pair multiplies a 256 x 2BN tile with half the B traffic per SM,
+ * so it wins whenever it keeps about as many SMs busy.  Slicing K costs a second launch plus a round trip of
+ * fp32 partial sums. */
+struct TilePlan { int bn, splits, pair; };
+TilePlan plan_tiles(int m, int n, int batch, int k_iters, int sms, bool f32) {
+    static int pair_env = -1;
+    if (pair_env < 0) { const char* e = getenv("RPB_UMMA_PAIR"); pair_env = e ? (atoi(e) ? 2 : 1) : 0; }
+    if (const char* e = getenv("RPB_UMMA_PLAN")) {                  /* "BN,splits,pair": pins the plan (experiments) */
+        int b = 0, sp = 0, pr = 0;
+        if (sscanf(e, "%d,%d,%d", &b, &sp, &pr) >= 2 && (b == 64 || b == 128 || (b == 256 && !pr)) && sp >= 1) {
+            if (sp > k_iters) sp = k_iters;
+            return TilePlan{b, sp > 128 ? 128 : sp, pr ? 1 : 0};
+        }
+    }
+    static const int cand_splits[] = {1, 2, 3, 4, 6, 8, 12, 16, 24, 32, 48, 64, 96, 128};
+    /* microseconds per K block: one-CTA tiles 128 x {64, 128, 256}, pair tiles 256 x {128, 256} */
+    static const double step16[5] = {0.31, 0.35, 0.44, 0.33, 0.40};
+    static const double step32[5] = {0.67, 0.85, 1.55, 1.10, 1.28};
+    const double* step = f32 ? step32 : step16;
+    TilePlan best = {n <= 64 ? 64 : (n <= 128 ? 128 : 256), 1, 0};
+    double best_t = 1e30;
+    for (int c = 0; c < 5; ++c) {
+        const int pair = c >= 3;
+        const int bn = pair ? (c == 3 ? 64 : 128) : 64 << c;
+        const int tile_m = pair ? 256 : 128, tile_n = pair ? 2 * bn : bn;
+        if (pair && (pair_env == 1 || m < 256 || n < tile_n)) continue;
+        if (!pair && pair_env == 2 && m >= 256 && n >= 256) continue;
+        if (tile_n > 64 && n <= tile_n / 2) continue;               /* never a tile twice as wide as C */
+        const long long tiles = (long long)((m + tile_m - 1) / tile_m) * ((n + tile_n - 1) / tile_n) * batch;
+        const int units = pair ? sms / 2 : sms;
+        for (int sp : cand_splits) {
+            if (sp > 1 && (k_iters / sp < 4 || tiles * sp > units)) break;
+            const int ips = (k_iters + sp - 1) / sp;
+            const long long waves = (tiles * sp + units - 1) / units;
+            double t = (double)waves * (ips * step[c] + (pair ? 0.8 : 0.5));
+            if (sp > 1) t += 3.5 + (double)sp * m * n * batch * 8.0 / 3.0e6;
+            if (t < best_t) { best_t = t; best.bn = bn; best.splits = sp; best.pair = pair; }
+        }
+    }
+    if (getenv("RPB_UMMA_PLAN_LOG"))
+        fprintf(stderr, "rpb plan %dx%dx(%d blocks) batch %d: %s 128x%d, %d slices, model %.1f us\n", m, n, k_iters, batch,
+                best.pair ? "pair" : "one-CTA", best.bn, best.splits, best_t);
+    return best;
 }
 
 /* returns 1 when the problem cannot take the tcgen05 path (caller falls back to SIMT) */
@@ -548,9 +582,13 @@ int launch_umma(const RpbProblem& p, void* C, const void* A, const void* B, Devi
     OperandPlan pb = plan_operand(B, p.n, p.k, p.b_col, p.b_row, p.batch, p.b_batch, p.reduce, p.b_reduce, ES);
     if (!pa.ok || !pb.ok) return 1;
 
-    const bool pair = want_pair(p.m, p.n, (long long)p.k * p.reduce, p.batch, d->sm_count);
+    const int k_iters_total = ((p.k + BK - 1) / BK) * p.reduce;
+    int sms = d->sm_count;
+    if (p.max_sms > 0 && p.max_sms < sms) sms = p.max_sms < 2 ? 2 : p.max_sms;
     /* BN = rows of B per CTA; a pair multiplies 256 x (2 BN) tiles */
-    const int BN = pair ? 128 : (p.n <= 64 ? 64 : (p.n <= 128 ? 128 : 256));
+    const TilePlan tp = plan_tiles(p.m, p.n, p.batch, k_iters_total, sms, F32);
+    const bool pair = tp.pair != 0;
+    const int BN = tp.bn;
     const int tile_m = pair ? 2 * rpb_umma::BLOCK_M : rpb_umma::BLOCK_M;
     const int tile_n = pair ? 2 * BN : BN;
     rpb_umma::Args a;
@@ -561,14 +599,7 @@ int launch_umma(const RpbProblem& p, void* C, const void* A, const void* B, Devi
     a.tiles_m = (p.m + tile_m - 1) / tile_m;
     a.tiles_n = (p.n + tile_n - 1) / tile_n;
     long long tiles = (long long)a.tiles_m * a.tiles_n * p.batch;
-    int splits = 1;
-    if (!pair && tiles * 2 <= d->sm_count && a.k_iters >= 8) {
-        long long want = d->sm_count / tiles;
-        long long cap = a.k_iters / 4;
-        splits = (int)(want < cap ? want : cap);
-        if (splits > 128) splits = 128;
-        if (splits < 1) splits = 1;
-    }
+    const int splits = tp.splits;
     a.iters_per_split = (a.k_iters + splits - 1) / splits;
     a.splits = (a.k_iters + a.iters_per_split - 1) / a.iters_per_split;
     a.total_work = tiles * a.splits;
@@ -617,9 +648,6 @@ int launch_umma(const RpbProblem& p, void* C, const void* A, const void* B, Devi
         if (encode_store_map(&mc, C, dt, ES, p.n, p.m, p.batch, p.c_row, p.c_batch, 128 / ES) == 0) a.tma_store = 1;
     }
 
-    int sms = d->sm_count;
-    if (p.max_sms > 0 && p.max_sms < sms) sms = p.max_sms < 2 ? 2 : p.max_sms;
-
     /* Tail split: if the last wave of tiles would keep fewer than half of the CTAs (or CTA pairs) busy, cut
      * its tiles along K so that the wave is short instead of sparse (4096^3: 256 tiles on 74 pairs = 3 waves +
      * 34 tiles; with two K slices each the run takes 3.5 tile times instead of 4). */
@@ -655,7 +683,8 @@ int launch_umma(const RpbProblem& p, void* C, const void* A, const void* B, Devi
     int rc;
     if (pair) {
         const long long clusters = a.total_work < sms / 2 ? a.total_work : sms / 2;
-        rc = launch_umma_bn<T, 128, true>(pa.mn_major, pb.mn_major, ma, mb, mc, mp, a, (int)clusters * 2, stream);
+        if (BN == 64) rc = launch_umma_bn<T, 64, true>(pa.mn_major, pb.mn_major, ma, mb, mc, mp, a, (int)clusters * 2, stream);
+        else rc = launch_umma_bn<T, 128, true>(pa.mn_major, pb.mn_major, ma, mb, mc, mp, a, (int)clusters * 2, stream);
     }
     else if (BN == 64) rc = launch_umma_bn<T, 64>(pa.mn_major, pb.mn_major, ma, mb, mc, mp, a, grid, stream);
     else if (BN == 128) rc = launch_umma_bn<T, 128>(pa.mn_major, pb.mn_major, ma, mb, mc, mp, a, grid, stream);

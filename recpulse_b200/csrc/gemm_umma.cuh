@@ -133,6 +133,22 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     atomicCAS(status, 0, code);
     return false;
 }
+/* One lane of a converged warp.  The producer and MMA warps run their loops with all 32 lanes and elect the
+ * issuing lane per iteration: loop counters, shared-memory addresses and descriptors then stay warp-uniform,
+ * which lets the compiler keep them in uniform registers, where TMA and tcgen05.mma take their operands.  (With
+ * the whole loop under "lane == 0" every issue paid for moving its operands there: ~100 clocks per
+ * tcgen05.mma, measured, which capped every tile shape at ~420 clocks per K block.) */
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+    return pred != 0;
+}
+/* all lanes of a converged warp wait; the verdict is uniform */
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                               int* status, int code) {
+    const bool ok = mbar_wait(bar, parity, abort_flag, status, code);
+    return __all_sync(0xffffffffu, ok);
+}
 /* PAIR: the copy may signal an mbarrier in the other CTA of the pair (cta_group::2); never multicast */
 template <bool PAIR>
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
@@ -403,7 +419,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     };
 
     if (warp == 0) {
-        if (lane == 0) {
+        {
             int stage = 0; uint32_t phase = 0;
             bool alive = true;
             for (long long w = work_begin; alive && w < args.total_work; w += work_step) {
@@ -414,11 +430,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                 for (int it = it0; it < it1; ++it) {
                     const int r = it / args.k_blocks;
                     const int k0 = (it - r * args.k_blocks) * BLOCK_K;
-                    if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, args.status, 1)) { alive = false; break; }
+                    if (!mbar_wait_warp(empty_bar(stage), phase ^ 1u, abort_flag, args.status, 1)) { alive = false; break; }
                     const uint32_t sa = smem_base + stage * Cfg::STAGE_BYTES;
                     const uint32_t sb = sa + Cfg::A_BYTES;
                     /* both CTAs of a pair report their bytes to the leader's barrier */
                     uint32_t fb = full_bar(stage);
+                    if (elect_one()) {
                     if (PAIR && !SPLIT) {
                         if (leader) mbar_expect_tx(fb, 2 * Cfg::LOAD_BYTES);
                         fb = cluster_addr(fb, 0);
@@ -443,12 +460,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                             tma_load_4d<REMOTE_BAR>(sb + c * (BLOCK_K * 128), &map_b, fb, col0 + c * CHUNK, k0,
                                                     r * args.b_reduce_mul, bz * args.b_batch_mul);
                     }
+                    }
+                    __syncwarp();
                     if (++stage == Cfg::STAGES) { stage = 0; phase ^= 1u; }
                 }
             }
         }
     } else if (warp == 1) {
-        if (lane == 0 && leader) {
+        if (leader) {
             int stage = 0; uint32_t phase = 0;
             uint32_t local_tile = 0;
             bool alive = true;
@@ -457,17 +476,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                 int it0, it1; k_range(w, split, it0, it1);
                 const uint32_t ab = local_tile & 1u;
                 const uint32_t acc_phase = (local_tile >> 1) & 1u;
-                if (!mbar_wait(tempty_bar(ab), acc_phase ^ 1u, abort_flag, args.status, 2)) { alive = false; break; }
+                if (!mbar_wait_warp(tempty_bar(ab), acc_phase ^ 1u, abort_flag, args.status, 2)) { alive = false; break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + ab * ACC_N;
                 for (int it = it0; it < it1; ++it) {
                     /* float32: the stage is usable once the split warps (of both CTAs of a pair) are done with it */
-                    if (!mbar_wait(SPLIT ? ready_bar(stage) : full_bar(stage), phase, abort_flag, args.status, 3)) { alive = false; break; }
+                    if (!mbar_wait_warp(SPLIT ? ready_bar(stage) : full_bar(stage), phase, abort_flag, args.status, 3)) { alive = false; break; }
                     tc_fence_after();
                     const uint32_t sa = smem_base + stage * Cfg::STAGE_BYTES;
                     const uint32_t sb = sa + Cfg::A_BYTES;
                     const uint64_t da = args.a_desc_base | (uint64_t)((sa >> 4) & 0x3FFFu);
                     const uint64_t db = args.b_desc_base | (uint64_t)((sb >> 4) & 0x3FFFu);
+                    if (elect_one()) {
 #pragma unroll
                     for (int kk = 0; kk < BLOCK_K / UMMA_K; ++kk) {
                         const uint64_t ak = da + (uint64_t)(kk * args.a_kstep), bk = db + (uint64_t)(kk * args.b_kstep);
@@ -482,9 +502,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                         }
                     }
                     umma_commit<PAIR>(empty_bar(stage));      /* frees the stage (in both CTAs of a pair) */
+                    }
+                    __syncwarp();
                     if (++stage == Cfg::STAGES) { stage = 0; phase ^= 1u; }
                 }
-                if (alive) umma_commit<PAIR>(tfull_bar(ab));  /* accumulator complete */
+                if (alive && elect_one()) umma_commit<PAIR>(tfull_bar(ab));  /* accumulator complete */
+                __syncwarp();
             }
         }
     } else if (SPLIT && warp >= 2 + EPI_WARPS) {
