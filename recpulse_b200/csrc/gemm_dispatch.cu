@@ -524,9 +524,11 @@ int launch_umma_bn(bool a_mn, bool b_mn, const CUtensorMap& ma, const CUtensorMa
 }
 
 /* Tile shape and K slices, chosen by a small cost model in microseconds fitted to measurements on B200
- * (cold operands).  A CTA's main loop advances one K block (128 bytes of K) per step; the step time depends on
- * the tile width much less than the arithmetic does, because narrow tiles are bound by the shared-memory fill
- * rate rather than the tensor pipe.  A CTA pair multiplies a 256 x 2BN tile with half the B traffic per SM,
+ * (cold operands).  A CTA's main loop advances one K block (128 bytes of K) per step.  The step time shrinks
+ * far less than the arithmetic when the tile gets narrower: one tcgen05.mma took at least ~100-120 clocks to
+ * issue and retire whatever its N (measured with the loads switched off: N = 256 runs at the tensor pipe's
+ * rate, N = 128 at half of it, N = 64 at a quarter), so narrow tiles only pay when the wide ones leave most SMs
+ * without work.  A CTA pair multiplies a 256 x 2BN tile with half the B traffic per SM and draws less power,
  * so it wins whenever it keeps about as many SMs busy.  Slicing K costs a second launch plus a round trip of
  * fp32 partial sums. */
 struct TilePlan { int bn, splits, pair; };
@@ -542,8 +544,8 @@ TilePlan plan_tiles(int m, int n, int batch, int k_iters, int sms, bool f32) {
     }
     static const int cand_splits[] = {1, 2, 3, 4, 6, 8, 12, 16, 24, 32, 48, 64, 96, 128};
     /* microseconds per K block: one-CTA tiles 128 x {64, 128, 256}, pair tiles 256 x {128, 256} */
-    static const double step16[5] = {0.31, 0.35, 0.44, 0.33, 0.40};
-    static const double step32[5] = {0.67, 0.85, 1.55, 1.10, 1.28};
+    static const double step16[5] = {0.26, 0.28, 0.41, 0.25, 0.38};
+    static const double step32[5] = {0.70, 0.86, 1.50, 1.12, 1.33};
     const double* step = f32 ? step32 : step16;
     TilePlan best = {n <= 64 ? 64 : (n <= 128 ? 128 : 256), 1, 0};
     double best_t = 1e30;

@@ -193,38 +193,40 @@ __device__ __forceinline__ void cluster_sync() {
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+/* Descriptors travel as two 32-bit words: the low word (start address and leading-dimension offset) changes
+ * per stage and per instruction, the high word never does, so the loop only does 32-bit adds. */
 template <bool PAIR>
-__device__ __forceinline__ void umma_tf32(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+__device__ __forceinline__ void umma_tf32(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi,
                                           uint32_t idesc, uint32_t accumulate) {
     if (PAIR) {
         asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "setp.ne.b32 p, %4, 0;\n\t"
-            "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
-            ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+            "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+            "setp.ne.b32 p, %6, 0;\n\tmov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\t"
+            "tcgen05.mma.cta_group::2.kind::tf32 [%0], da, db, %5, p;\n\t}"
+            ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate) : "memory");
     } else {
         asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "setp.ne.b32 p, %4, 0;\n\t"
-            "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
-            ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+            "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+            "setp.ne.b32 p, %6, 0;\n\tmov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\t"
+            "tcgen05.mma.cta_group::1.kind::tf32 [%0], da, db, %5, p;\n\t}"
+            ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate) : "memory");
     }
 }
 template <bool PAIR>
-__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi,
                                          uint32_t idesc, uint32_t accumulate) {
     if (PAIR) {
         asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "setp.ne.b32 p, %4, 0;\n\t"
-            "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-            ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+            "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+            "setp.ne.b32 p, %6, 0;\n\tmov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\t"
+            "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %5, p;\n\t}"
+            ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate) : "memory");
     } else {
         asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "setp.ne.b32 p, %4, 0;\n\t"
-            "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-            ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+            "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+            "setp.ne.b32 p, %6, 0;\n\tmov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}"
+            ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate) : "memory");
     }
 }
 /* The mbarrier receives one arrival once every tcgen05.mma issued so far by this thread has
@@ -420,49 +422,54 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
 
     if (warp == 0) {
         {
-            int stage = 0; uint32_t phase = 0;
+            /* The loop below is one warp's serial code and bounds the K-block rate of narrow tiles, so it carries
+             * running values (stage addresses, K coordinates) instead of recomputing them per block. */
+            constexpr bool REMOTE_BAR = PAIR && !SPLIT;
+            int stage = 0; uint32_t parity = 1u;                      /* empty barriers: first pass falls through */
+            uint32_t sa = smem_base, eb = empty_bar(0), fb = full_bar(0);
             bool alive = true;
             for (long long w = work_begin; alive && w < args.total_work; w += work_step) {
                 int mt, nt, split, bz; decode(w, mt, nt, split, bz);
                 int it0, it1; k_range(w, split, it0, it1);
                 const int row0 = mt * TILE_M + (int)cta_rank * BLOCK_M;     /* this CTA's rows of A */
                 const int col0 = nt * ACC_N + (int)cta_rank * BN;           /* this CTA's columns of B */
-                for (int it = it0; it < it1; ++it) {
-                    const int r = it / args.k_blocks;
-                    const int k0 = (it - r * args.k_blocks) * BLOCK_K;
-                    if (!mbar_wait_warp(empty_bar(stage), phase ^ 1u, abort_flag, args.status, 1)) { alive = false; break; }
-                    const uint32_t sa = smem_base + stage * Cfg::STAGE_BYTES;
-                    const uint32_t sb = sa + Cfg::A_BYTES;
-                    /* both CTAs of a pair report their bytes to the leader's barrier */
-                    uint32_t fb = full_bar(stage);
+                const int r0 = it0 / args.k_blocks;
+                int kb = it0 - r0 * args.k_blocks, k0 = kb * BLOCK_K;
+                int a_r = r0 * args.a_reduce_mul, b_r = r0 * args.b_reduce_mul;
+                const int a_b = bz * args.a_batch_mul, b_b = bz * args.b_batch_mul;
+                for (int left = it1 - it0; left > 0; --left) {
+                    if (!mbar_wait_warp(eb, parity, abort_flag, args.status, 1)) { alive = false; break; }
                     if (elect_one()) {
-                    if (PAIR && !SPLIT) {
-                        if (leader) mbar_expect_tx(fb, 2 * Cfg::LOAD_BYTES);
-                        fb = cluster_addr(fb, 0);
-                    } else {
-                        /* float32 pairs: each CTA first splits its own tiles, so its loads report locally */
-                        mbar_expect_tx(fb, Cfg::LOAD_BYTES);
-                    }
-                    constexpr bool REMOTE_BAR = PAIR && !SPLIT;
-                    if (!A_MN) {
-                        tma_load_4d<REMOTE_BAR>(sa, &map_a, fb, k0, row0, r * args.a_reduce_mul, bz * args.a_batch_mul);
-                    } else {
+                        const uint32_t sb = sa + Cfg::A_BYTES;
+                        uint32_t tb = fb;
+                        if (REMOTE_BAR) {
+                            /* both CTAs of a pair report their bytes to the leader's barrier */
+                            if (leader) mbar_expect_tx(fb, 2 * Cfg::LOAD_BYTES);
+                            tb = cluster_addr(fb, 0);
+                        } else {
+                            /* float32 pairs: each CTA first splits its own tiles, so its loads report locally */
+                            mbar_expect_tx(fb, Cfg::LOAD_BYTES);
+                        }
+                        if (!A_MN) {
+                            tma_load_4d<REMOTE_BAR>(sa, &map_a, tb, k0, row0, a_r, a_b);
+                        } else {
 #pragma unroll
-                        for (int c = 0; c < BLOCK_M / CHUNK; ++c)
-                            tma_load_4d<REMOTE_BAR>(sa + c * (BLOCK_K * 128), &map_a, fb, row0 + c * CHUNK, k0,
-                                                    r * args.a_reduce_mul, bz * args.a_batch_mul);
-                    }
-                    if (!B_MN) {
-                        tma_load_4d<REMOTE_BAR>(sb, &map_b, fb, k0, col0, r * args.b_reduce_mul, bz * args.b_batch_mul);
-                    } else {
+                            for (int c = 0; c < BLOCK_M / CHUNK; ++c)
+                                tma_load_4d<REMOTE_BAR>(sa + c * (BLOCK_K * 128), &map_a, tb, row0 + c * CHUNK, k0, a_r, a_b);
+                        }
+                        if (!B_MN) {
+                            tma_load_4d<REMOTE_BAR>(sb, &map_b, tb, k0, col0, b_r, b_b);
+                        } else {
 #pragma unroll
-                        for (int c = 0; c < BN / CHUNK; ++c)
-                            tma_load_4d<REMOTE_BAR>(sb + c * (BLOCK_K * 128), &map_b, fb, col0 + c * CHUNK, k0,
-                                                    r * args.b_reduce_mul, bz * args.b_batch_mul);
-                    }
+                            for (int c = 0; c < BN / CHUNK; ++c)
+                                tma_load_4d<REMOTE_BAR>(sb + c * (BLOCK_K * 128), &map_b, tb, col0 + c * CHUNK, k0, b_r, b_b);
+                        }
                     }
                     __syncwarp();
-                    if (++stage == Cfg::STAGES) { stage = 0; phase ^= 1u; }
+                    k0 += BLOCK_K;
+                    if (++kb == args.k_blocks) { kb = 0; k0 = 0; a_r += args.a_reduce_mul; b_r += args.b_reduce_mul; }
+                    sa += Cfg::STAGE_BYTES; eb += 8u; fb += 8u;
+                    if (++stage == Cfg::STAGES) { stage = 0; parity ^= 1u; sa = smem_base; eb = empty_bar(0); fb = full_bar(0); }
                 }
             }
         }
@@ -470,6 +477,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         if (leader) {
             int stage = 0; uint32_t phase = 0;
             uint32_t local_tile = 0;
+            /* descriptor words: the start address (16-byte units, 14 bits) sits in the low word, whose other bits and
+             * the high word are fixed per operand; shared memory ends below 2^18 bytes, so adding stage and K offsets
+             * to the low word never carries out of the address field */
+            const uint32_t a_hi = (uint32_t)(args.a_desc_base >> 32), b_hi = (uint32_t)(args.b_desc_base >> 32);
+            const uint32_t a_lo0 = (uint32_t)args.a_desc_base + (smem_base >> 4);
+            const uint32_t b_lo0 = (uint32_t)args.b_desc_base + ((smem_base + Cfg::A_BYTES) >> 4);
+            uint32_t a_lo = a_lo0, b_lo = b_lo0;
+            uint32_t wb = SPLIT ? ready_bar(0) : full_bar(0), eb = empty_bar(0);
+            const uint32_t a_kstep = args.a_kstep, b_kstep = args.b_kstep, idesc = args.idesc;
             bool alive = true;
             for (long long w = work_begin; alive && w < args.total_work; w += work_step, ++local_tile) {
                 int mt, nt, split, bz; decode(w, mt, nt, split, bz);
@@ -479,32 +495,34 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                 if (!mbar_wait_warp(tempty_bar(ab), acc_phase ^ 1u, abort_flag, args.status, 2)) { alive = false; break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + ab * ACC_N;
-                for (int it = it0; it < it1; ++it) {
+                uint32_t acc = 0u;                                  /* the first instruction of a tile overwrites */
+                for (int left = it1 - it0; left > 0; --left) {
                     /* float32: the stage is usable once the split warps (of both CTAs of a pair) are done with it */
-                    if (!mbar_wait_warp(SPLIT ? ready_bar(stage) : full_bar(stage), phase, abort_flag, args.status, 3)) { alive = false; break; }
+                    if (!mbar_wait_warp(wb, phase, abort_flag, args.status, 3)) { alive = false; break; }
                     tc_fence_after();
-                    const uint32_t sa = smem_base + stage * Cfg::STAGE_BYTES;
-                    const uint32_t sb = sa + Cfg::A_BYTES;
-                    const uint64_t da = args.a_desc_base | (uint64_t)((sa >> 4) & 0x3FFFu);
-                    const uint64_t db = args.b_desc_base | (uint64_t)((sb >> 4) & 0x3FFFu);
                     if (elect_one()) {
 #pragma unroll
-                    for (int kk = 0; kk < BLOCK_K / UMMA_K; ++kk) {
-                        const uint64_t ak = da + (uint64_t)(kk * args.a_kstep), bk = db + (uint64_t)(kk * args.b_kstep);
-                        const uint32_t first = (it > it0 || kk > 0) ? 1u : 0u;
-                        if (SPLIT) {
-                            constexpr uint64_t LO = (uint64_t)(Cfg::LOAD_BYTES >> 4);      /* lo tiles sit LOAD_BYTES further */
-                            umma_tf32<PAIR>(d_tmem, ak + LO, bk, args.idesc, first);       /* small terms first */
-                            umma_tf32<PAIR>(d_tmem, ak, bk + LO, args.idesc, 1u);
-                            umma_tf32<PAIR>(d_tmem, ak, bk, args.idesc, 1u);
-                        } else {
-                            umma_f16<PAIR>(d_tmem, ak, bk, args.idesc, first);
+                        for (int kk = 0; kk < BLOCK_K / UMMA_K; ++kk) {
+                            const uint32_t ak = a_lo + kk * a_kstep, bk = b_lo + kk * b_kstep;
+                            if (SPLIT) {
+                                constexpr uint32_t LO = (uint32_t)(Cfg::LOAD_BYTES >> 4);  /* lo tiles sit LOAD_BYTES further */
+                                umma_tf32<PAIR>(d_tmem, ak + LO, a_hi, bk, b_hi, idesc, acc);   /* small terms first */
+                                umma_tf32<PAIR>(d_tmem, ak, a_hi, bk + LO, b_hi, idesc, 1u);
+                                umma_tf32<PAIR>(d_tmem, ak, a_hi, bk, b_hi, idesc, 1u);
+                            } else {
+                                umma_f16<PAIR>(d_tmem, ak, a_hi, bk, b_hi, idesc, acc);
+                            }
+                            acc = 1u;
                         }
-                    }
-                    umma_commit<PAIR>(empty_bar(stage));      /* frees the stage (in both CTAs of a pair) */
+                        umma_commit<PAIR>(eb);                      /* frees the stage (in both CTAs of a pair) */
                     }
                     __syncwarp();
-                    if (++stage == Cfg::STAGES) { stage = 0; phase ^= 1u; }
+                    acc = 1u;
+                    a_lo += Cfg::STAGE_BYTES >> 4; b_lo += Cfg::STAGE_BYTES >> 4; wb += 8u; eb += 8u;
+                    if (++stage == Cfg::STAGES) {
+                        stage = 0; phase ^= 1u; a_lo = a_lo0; b_lo = b_lo0;
+                        wb = SPLIT ? ready_bar(0) : full_bar(0); eb = empty_bar(0);
+                    }
                 }
                 if (alive && elect_one()) umma_commit<PAIR>(tfull_bar(ab));  /* accumulator complete */
                 __syncwarp();
