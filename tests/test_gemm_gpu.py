@@ -235,6 +235,31 @@ def test_umma_tail_split_and_bias(lib, dtype):
             lib.rpb_force_kernel(0)
 
 
+PLANS = ["64,1,0", "128,1,0", "256,1,0", "64,1,1", "128,1,1",          # every tile shape, unsplit
+         "64,3,0", "128,2,0", "256,4,0", "64,2,1", "128,4,1"]          # and with K slices
+
+
+@pytest.mark.parametrize("dtype", ["bfloat16", "float16", "float32"])
+@pytest.mark.parametrize("plan", PLANS)
+def test_every_tile_plan_gives_the_same_product(lib, dtype, plan, monkeypatch):
+    """The planner picks among one-CTA tiles 128 x {64, 128, 256}, pair tiles 256 x {128, 256} and K slices;
+    RPB_UMMA_PLAN pins each in turn.  Ragged M/N/K, both B orientations, plus bias (unsplit) and C += AB."""
+    monkeypatch.setenv("RPB_UMMA_PLAN", plan)
+    rng = np.random.default_rng(hash((dtype, plan)) % 2**32)
+    m, k, n = 520, 1160, 776                       # ragged against every tile; 19 / 37 K blocks
+    a = rand_operand(rng, (1, 1, m, k), dtype); b = rand_operand(rng, (1, 1, k, n), dtype, scale=1 / np.sqrt(k))
+    split = int(plan.split(",")[1]) > 1
+    kinds = (_lib.KERNEL_UMMA_SPLITK,) if split else (_lib.KERNEL_UMMA,)
+    lib.rpb_force_kernel(_lib.KERNEL_UMMA)         # float32 of this size would otherwise take the mma.sync kernel
+    try:
+        run_ex(lib, dtype, a, b, expect=kinds, oracle=False)
+        run_ex(lib, dtype, a, b, tb=True, expect=kinds, oracle=False)
+        run_ex(lib, dtype, a, b, ta=True, expect=kinds, oracle=False, bias=rand_operand(rng, (n,), dtype))
+        run_ex(lib, dtype, a, b, c_init=rand_operand(rng, (1, m, n), dtype), expect=UMMA, oracle=False)
+    finally:
+        lib.rpb_force_kernel(0)
+
+
 @pytest.mark.parametrize("dtype", ["bfloat16", "float16"])
 def test_unaligned_half_operands_take_the_general_path(lib, dtype):
     rng = np.random.default_rng(29)
