@@ -265,8 +265,8 @@ int launch_dmma(const RpbProblem& p, void* C, const void* A, const void* B, Devi
     a.k_iters = a.k_blocks * p.reduce;
     const long long tiles = (long long)a.tiles_m * a.tiles_n * p.batch;
     int splits = 1;
-    if (tiles * 2 <= d->sm_count && a.k_iters >= 16) {
-        long long want = d->sm_count / tiles, cap = a.k_iters / 8;
+    if (tiles * 2 <= d->sm_count && a.k_iters >= 8) {
+        long long want = d->sm_count / tiles, cap = a.k_iters / 4;
         splits = (int)(want < cap ? want : cap);
         if (splits > 64) splits = 64;
         if (splits < 1) splits = 1;
@@ -274,15 +274,35 @@ int launch_dmma(const RpbProblem& p, void* C, const void* A, const void* B, Devi
     a.iters_per_split = (a.k_iters + splits - 1) / splits;
     a.splits = (a.k_iters + a.iters_per_split - 1) / a.iters_per_split;
     a.partial = nullptr;
-    const long long blocks = tiles * a.splits;
+    long long blocks = tiles * a.splits;
     if (blocks > 0x7fffffffLL) return 1;
     if (a.splits > 1 && get_scratch(d, sizeof(double) * (size_t)a.splits * p.batch * p.m * p.n, stream, &a.partial)) return -1;
+    /* More tiles than SMs and a sparse last wave: deal (tile, K block) units evenly to one CTA per SM instead
+     * (2048^3: 256 tiles = 1.73 waves of work ran as 2 waves) */
+    {
+        const char* e = getenv("RPB_DMMA_BALANCED");            /* 0: one CTA per tile always (A/B evidence) */
+        const int env = e ? atoi(e) : 1;
+        int sms = d->sm_count;
+        if (p.max_sms > 0 && p.max_sms < sms) sms = p.max_sms;
+        const long long waves = (tiles + sms - 1) / sms;
+        if (env && a.splits == 1 && tiles > sms && a.k_iters >= 8 && tiles * 100 < waves * sms * 93) {
+            void* ws = nullptr;
+            if (get_scratch(d, sizeof(double) * (size_t)(sms - 1) * 2 * rpb_dmma::BM * rpb_dmma::BN, stream, &ws)) return -1;
+            a.sk_ctas = sms; a.sk_units = tiles * a.k_iters; a.sk_scratch = reinterpret_cast<double*>(ws);
+            blocks = sms;
+        }
+    }
     int rc;
     if (!a_mn && !b_mn) rc = launch_dmma_inst<false, false>(a, blocks, stream);
     else if (!a_mn && b_mn) rc = launch_dmma_inst<false, true>(a, blocks, stream);
     else if (a_mn && !b_mn) rc = launch_dmma_inst<true, false>(a, blocks, stream);
     else rc = launch_dmma_inst<true, true>(a, blocks, stream);
     if (rc) return -1;
+    if (a.sk_ctas > 0) {
+        RPB_CUDA(rpb_launch(rpb_dmma::balanced_fixup_kernel, dim3((unsigned)(a.sk_ctas - 1)), dim3(256), 0, stream, 1, a));
+        g_launches++;
+        if (release_scratch(d, stream)) return -1;
+    }
     if (a.splits > 1) {
         rpb_simt::launch_splitk_reduce<double, double>(reinterpret_cast<const double*>(a.partial), reinterpret_cast<double*>(C),
                                                        a.splits, p.batch, p.m, p.n, p.c_row, p.c_batch, p.accumulate,

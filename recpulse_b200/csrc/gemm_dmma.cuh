@@ -1,13 +1,21 @@
 /*
  * float64 GEMM on the double-precision tensor-core path (mma.sync m16n8k8, f64 accumulate).
  *
- * CTA tile 128 x 128, K staged 16 at a time through a 3-stage cp.async ring, 8 warps of 64 x 32.
+ * CTA tile 128 x 128, K staged 32 at a time through a 3-stage cp.async ring (216 KB), 8 warps of 64 x 32.
  * Each operand is kept in shared memory in the orientation it has in global memory, so both
  * row-major and transposed views are copied with 16-byte cp.async along their contiguous index:
- *   K-contiguous  X[mn][k], leading dimension 20 doubles
+ *   K-contiguous  X[mn][k], leading dimension 36 doubles
  *   MN-contiguous X[k][mn], leading dimension 136 doubles
  * Both leading dimensions make the 8 x 4 (or 4 x 8) fragment reads of a warp hit every bank pair
  * exactly twice, the minimum for 32 lanes x 8 bytes.
+ *
+ * Schedules.  Plain: one CTA per output tile (times K slices for skinny outputs, partial sums reduced by a
+ * second kernel).  Balanced (sk_ctas > 0): for outputs of more tiles than SMs whose last wave would be sparse
+ * (2048^3: 256 tiles on 148 SMs = two waves for 1.73 waves of work), the (tile, K block) units are dealt
+ * evenly and contiguously to one CTA per SM.  A CTA finishes the tile cut by its range start, runs its whole
+ * tiles, and starts the tile cut by its range end; every CTA gets at least one tile's worth of units, so a tile
+ * is cut at most once.  The two pieces of a cut tile go to scratch and `balanced_fixup_kernel` adds them in a
+ * fixed order (deterministic; no atomics, no CTA waits for another).
  *
  * Requirements (checked by the dispatcher, which otherwise uses the general-stride kernel): the
  * contiguous index has stride 1, every other stride is even (16-byte multiples) and the base
@@ -23,10 +31,10 @@
 
 namespace rpb_dmma {
 
-constexpr int BM = 128, BN = 128, BK = 16, STAGES = 3, THREADS = 256;
-constexpr int LD_K = 20;        /* K-contiguous tile: [128][20]  */
-constexpr int LD_MN = 136;      /* MN-contiguous tile: [16][136] */
-constexpr int TILE_DOUBLES = 128 * LD_K;             /* 2560 >= 16 * 136 = 2176 */
+constexpr int BM = 128, BN = 128, BK = 32, STAGES = 3, THREADS = 256;
+constexpr int LD_K = BK + 4;    /* K-contiguous tile: [128][36]  */
+constexpr int LD_MN = 136;      /* MN-contiguous tile: [32][136] */
+constexpr int TILE_DOUBLES = 128 * LD_K;             /* 4608 >= 32 * 136 = 4352 */
 constexpr int STAGE_DOUBLES = 2 * TILE_DOUBLES;
 constexpr int SMEM_BYTES = STAGES * STAGE_DOUBLES * 8;
 
@@ -50,11 +58,12 @@ template <bool MN_CONTIG>
 __device__ __forceinline__ void load_tile(double* smem, const double* g, long long stride_other, int mn0, int k0,
                                           int ext_mn, int ext_k, int tid) {
     if (!MN_CONTIG) {
-        /* rows = mn (128), 16 doubles of k per row = 8 vectors: 1024 vectors / 256 threads = 4 each */
+        /* rows = mn (128), BK doubles of k per row = BK/2 vectors */
+        constexpr int VPR = BK / 2;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
+        for (int i = 0; i < 128 * VPR / THREADS; ++i) {
             const int v = tid + i * THREADS;
-            const int r = v >> 3, c = (v & 7) * 2;
+            const int r = v / VPR, c = (v % VPR) * 2;
             const int gm = mn0 + r, gk = k0 + c;
             int bytes = 0;
             if (gm < ext_mn && gk < ext_k) bytes = (ext_k - gk >= 2) ? 16 : 8;
@@ -62,9 +71,9 @@ __device__ __forceinline__ void load_tile(double* smem, const double* g, long lo
             cp_async_16(smem + r * LD_K + c, src, bytes);
         }
     } else {
-        /* rows = k (16), 128 doubles of mn per row = 64 vectors: 1024 vectors / 256 threads = 4 each */
+        /* rows = k (BK), 128 doubles of mn per row = 64 vectors */
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
+        for (int i = 0; i < BK * 64 / THREADS; ++i) {
             const int v = tid + i * THREADS;
             const int r = v >> 6, c = (v & 63) * 2;
             const int gk = k0 + r, gm = mn0 + c;
@@ -84,14 +93,39 @@ gemm_kernel(const rpb_simt::Args p)
     extern __shared__ __align__(16) double smem[];
     rpb_pdl_trigger();
     rpb_pdl_wait();
-    long long w = blockIdx.x;
-    const int mt = (int)(w % p.tiles_m); w /= p.tiles_m;
-    const int nt = (int)(w % p.tiles_n); w /= p.tiles_n;
-    const int split = (int)(w % p.splits);
-    const int bz = (int)(w / p.splits);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int wm = (warp >> 2) * 64, wn = (warp & 3) * 32;       /* warp tile origin inside the CTA tile */
     const int g = lane >> 2, t = lane & 3;
+    /* balanced schedule: this CTA's range of (tile, K block) units */
+    long long cursor = 0, range_end = 0;
+    if (p.sk_ctas > 0) {
+        const long long base = p.sk_units / p.sk_ctas, extra = p.sk_units % p.sk_ctas, b = blockIdx.x;
+        cursor = b * base + (b < extra ? b : extra);
+        range_end = cursor + base + (b < extra ? 1 : 0);
+    }
+  for (;;) {
+    long long w = blockIdx.x;
+    int split = 0, it0, it1;
+    int cut = -1;                              /* balanced: 0 = head piece of a cut tile, 1 = tail piece, -1 = whole */
+    if (p.sk_ctas > 0) {
+        if (cursor >= range_end) break;
+        w = cursor / p.k_iters;
+        it0 = (int)(cursor - w * p.k_iters);
+        const long long room = range_end - cursor;
+        it1 = (p.k_iters - it0 <= room) ? p.k_iters : it0 + (int)room;
+        cursor += it1 - it0;
+        if (it0 > 0) cut = 1; else if (it1 < p.k_iters) cut = 0;
+    }
+    const int mt = (int)(w % p.tiles_m); w /= p.tiles_m;
+    const int nt = (int)(w % p.tiles_n); w /= p.tiles_n;
+    int bz;
+    if (p.sk_ctas > 0) bz = (int)w;
+    else {
+        split = (int)(w % p.splits);
+        bz = (int)(w / p.splits);
+        it0 = split * p.iters_per_split;
+        it1 = min(it0 + p.iters_per_split, p.k_iters);
+    }
     const int row0 = mt * BM, col0 = nt * BN;
 
     const double* A = reinterpret_cast<const double*>(p.a) + bz * p.a_batch;
@@ -107,8 +141,6 @@ gemm_kernel(const rpb_simt::Args p)
 #pragma unroll
             for (int e = 0; e < 4; ++e) acc[i][j][e] = 0.0;
 
-    const int it0 = split * p.iters_per_split;
-    const int it1 = min(it0 + p.iters_per_split, p.k_iters);
     const int n_it = it1 - it0;
 
     auto issue = [&](int it, int stage) {
@@ -161,6 +193,22 @@ gemm_kernel(const rpb_simt::Args p)
     cp_async_wait<0>();
 
     /* accumulator fragment: (row g, cols 2t, 2t+1) and (row g+8, same cols) of each 16 x 8 block */
+    if (cut >= 0) {
+        /* piece of a cut tile: the tail piece belongs to the boundary before this CTA, the head piece to the one
+         * after it; compact [128][128] tile, rows and columns beyond M, N hold zeros times nothing (never read) */
+        double* S = p.sk_scratch + ((long long)(cut == 1 ? blockIdx.x - 1 : blockIdx.x) * 2 + cut) * (BM * BN);
+#pragma unroll
+        for (int mi = 0; mi < 4; ++mi)
+#pragma unroll
+            for (int ni = 0; ni < 4; ++ni)
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const int r = wm + mi * 16 + g + h * 8, c = wn + ni * 8 + 2 * t;
+                    *reinterpret_cast<double2*>(S + r * BN + c) = make_double2(acc[mi][ni][2 * h], acc[mi][ni][2 * h + 1]);
+                }
+        __syncthreads();                       /* shared memory is reused by the next piece */
+        continue;
+    }
     const bool to_partial = p.splits > 1;
     double* P = to_partial ? reinterpret_cast<double*>(p.partial) + ((long long)split * p.batch + bz) * p.m * (long long)p.n
                            : nullptr;
@@ -187,6 +235,38 @@ gemm_kernel(const rpb_simt::Args p)
                     }
                 }
             }
+    if (p.sk_ctas == 0) break;
+    __syncthreads();                           /* shared memory is reused by the next tile */
+  }
+}
+
+/* Adds the two pieces of every tile that the balanced schedule cut between CTA i and CTA i + 1 (block i) and
+ * writes the tile: head + tail (+ bias) (+ C when accumulating), always in that order. */
+__global__ void __launch_bounds__(256)
+balanced_fixup_kernel(const rpb_simt::Args p)
+{
+    rpb_pdl_trigger();
+    rpb_pdl_wait();
+    const long long base = p.sk_units / p.sk_ctas, extra = p.sk_units % p.sk_ctas, b = blockIdx.x + 1;
+    const long long boundary = b * base + (b < extra ? b : extra);      /* first unit of CTA b */
+    long long w = boundary / p.k_iters;
+    if (boundary - w * p.k_iters == 0) return;                          /* CTA b starts on a tile boundary */
+    const int mt = (int)(w % p.tiles_m); w /= p.tiles_m;
+    const int nt = (int)(w % p.tiles_n);
+    const int bz = (int)(w / p.tiles_n);
+    const double* head = p.sk_scratch + (long long)blockIdx.x * 2 * (BM * BN);
+    const double* tail = head + BM * BN;
+    double* C = reinterpret_cast<double*>(p.c) + bz * p.c_batch;
+    const double* bias = reinterpret_cast<const double*>(p.bias);
+    for (int i = threadIdx.x; i < BM * BN; i += blockDim.x) {
+        const int r = mt * BM + i / BN, c = nt * BN + i % BN;
+        if (r >= p.m || c >= p.n) continue;
+        double v = head[i] + tail[i];
+        if (bias) v += bias[c];
+        double* dst = C + (long long)r * p.c_row + c;
+        if (p.accumulate) v += *dst;
+        *dst = v;
+    }
 }
 
 }  // namespace rpb_dmma

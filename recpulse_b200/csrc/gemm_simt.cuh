@@ -41,6 +41,10 @@ struct Args {
     int k_blocks, k_iters, splits, iters_per_split;
     void* partial;          /* [splits][batch][m][n] in the accumulation type, when splits > 1 */
     const void* bias;       /* n values of T added to every output row (applied by the reduction when K is split) */
+    /* float64 tensor-core kernel only: balanced schedule over (tile, K block) units, see gemm_dmma.cuh */
+    int sk_ctas = 0;                /* 0 = one CTA per tile (and K slice) */
+    long long sk_units = 0;         /* tiles * k_iters */
+    double* sk_scratch = nullptr;   /* [sk_ctas - 1][2][128 x 128] partial tiles of the tiles cut between two CTAs */
 };
 
 template <typename T, typename Acc, int BM, int BN, int BK, int TM, int TN>

@@ -127,6 +127,28 @@ def test_fp64_tensor_core_kernel(lib, layout):
     run_ex(lib, dtype, a, b, ta=ta, tb=tb, c_init=rand_operand(rng, (3, 96, 72), dtype), expect=(_lib.KERNEL_DMMA,))
 
 
+@pytest.mark.parametrize("layout", [(False, False), (True, True)])
+def test_fp64_balanced_schedule(lib, layout, monkeypatch):
+    """More tiles than SMs with a sparse last wave: (tile, K block) units are dealt evenly to one CTA per SM and
+    the tiles cut between two CTAs are summed by a fix-up kernel.  Ragged edges, batches, bias, C += AB; the
+    result is reproducible and agrees with the one-CTA-per-tile schedule to rounding."""
+    ta, tb = layout
+    dtype = "float64"
+    rng = np.random.default_rng(101)
+    m, k, n = 1700, 300, 1500                       # 14 x 12 = 168 tiles of 128 x 128, 10 K blocks
+    a = rand_operand(rng, (1, 1, m, k), dtype, dist="uniform"); b = rand_operand(rng, (1, 1, k, n), dtype, dist="uniform")
+    got = run_ex(lib, dtype, a, b, ta=ta, tb=tb, expect=(_lib.KERNEL_DMMA,), oracle=False)
+    again = run_ex(lib, dtype, a, b, ta=ta, tb=tb, expect=(_lib.KERNEL_DMMA,), oracle=False)
+    assert np.array_equal(got, again)
+    run_ex(lib, dtype, a, b, ta=ta, tb=tb, oracle=False, bias=rand_operand(rng, (n,), dtype))
+    run_ex(lib, dtype, a, b, ta=ta, tb=tb, oracle=False, c_init=rand_operand(rng, (1, m, n), dtype))
+    a2 = rand_operand(rng, (2, 2, 1100, 200), dtype); b2 = rand_operand(rng, (2, 2, 200, 1300), dtype)
+    run_ex(lib, dtype, a2, b2, ta=ta, tb=tb, oracle=False)      # 2 x 99 tiles, 2 summed problems of 7 K blocks
+    monkeypatch.setenv("RPB_DMMA_BALANCED", "0")
+    plain = run_ex(lib, dtype, a, b, ta=ta, tb=tb, expect=(_lib.KERNEL_DMMA,), oracle=False)
+    assert np.max(np.abs(plain - got)) <= 1e-12 * np.sqrt(k)
+
+
 @pytest.mark.parametrize("layout", [(False, False), (True, False), (False, True), (True, True)])
 def test_fp32_3xtf32_kernel(lib, layout):
     """float32 on tensor cores (3xTF32): must meet the same fp32 bound as the strict-fp32 reference,
