@@ -299,7 +299,7 @@ int launch_dmma(const RpbProblem& p, void* C, const void* A, const void* B, Devi
     else rc = launch_dmma_inst<true, true>(a, blocks, stream);
     if (rc) return -1;
     if (a.sk_ctas > 0) {
-        RPB_CUDA(rpb_launch(rpb_dmma::balanced_fixup_kernel, dim3((unsigned)(a.sk_ctas - 1)), dim3(256), 0, stream, 1, a));
+        RPB_CUDA(rpb_launch(rpb_dmma::balanced_fixup_kernel, dim3((unsigned)(a.sk_ctas - 1), 16), dim3(256), 0, stream, 1, a));
         g_launches++;
         if (release_scratch(d, stream)) return -1;
     }

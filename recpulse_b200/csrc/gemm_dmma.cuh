@@ -258,7 +258,9 @@ balanced_fixup_kernel(const rpb_simt::Args p)
     const double* tail = head + BM * BN;
     double* C = reinterpret_cast<double*>(p.c) + bz * p.c_batch;
     const double* bias = reinterpret_cast<const double*>(p.bias);
-    for (int i = threadIdx.x; i < BM * BN; i += blockDim.x) {
+    /* gridDim.y blocks share a tile so that the pass is not bound by the latency of 147 blocks' loads */
+    const int per = BM * BN / gridDim.y;
+    for (int i = blockIdx.y * per + threadIdx.x; i < (blockIdx.y + 1) * per; i += blockDim.x) {
         const int r = mt * BM + i / BN, c = nt * BN + i % BN;
         if (r >= p.m || c >= p.n) continue;
         double v = head[i] + tail[i];
