@@ -124,6 +124,21 @@ void backward_linear_fn(GradFn* self, Tensor* grad_output);
 Tensor* op_linear2(Tensor* x, Tensor* w, Tensor* h, Tensor* u, Tensor* bias);
 void backward_linear2_fn(GradFn* self, Tensor* grad_output);
 
+/* The activated gates of an LSTM cell as ONE node: y = act(x . w + h . u (+ bias)) with n = 4 * hidden
+ * columns in the order i, f, g, o; sigmoid on i, f, o and tanh on g.  RecPulse builds this from two op_matmul,
+ * up to three op_add, a chunk and four activation nodes (recpulse/module.py:289-300).  Backward turns dY into
+ * the gradient of the pre-activations through the saved output (g y (1 - y), g (1 - y^2): ops/grad_host.c:365-385,
+ * 622-640) and continues as backward_linear2_fn.  Operands as for op_linear2; n must be a multiple of 4. */
+Tensor* op_lstm_gates(Tensor* x, Tensor* w, Tensor* h, Tensor* u, Tensor* bias);
+void backward_lstm_gates_fn(GradFn* self, Tensor* grad_output);
+
+/* The two element-wise passes of op_lstm_gates on raw device pointers, on `stream`, without synchronising:
+ * in place y[r, c] = c in [n/2, 3n/4) ? tanh(y[r, c]) : 1 / (1 + exp(-y[r, c])), and
+ * dpre[r, c] = dy[r, c] * act'(.) from the activated y.  Strides in elements between rows.  0 / -1. */
+int rp_lstm_gates_ex(void* y, long long rows, int n, long long row_stride, DType dtype, int device_id, void* stream);
+int rp_lstm_gates_grad_ex(void* dpre, const void* dy, const void* y, long long rows, int n, long long dpre_stride,
+                          long long dy_stride, long long y_stride, DType dtype, int device_id, void* stream);
+
 /* out[j] (+)= sum over i < rows of in[i * row_stride + j], j < cols; fp32 (fp64 for float64) sums in a
  * fixed order, one rounding.  Runs on `stream` without synchronising. */
 int rp_colsum_ex(void* out, const void* in, long long rows, int cols, long long row_stride, DType dtype,

@@ -4,6 +4,7 @@
  * the reference's loops round the multiply and the add separately.
  */
 #include "matmul_oracle.h"
+#include <math.h>
 #include <stdlib.h>
 #include <string.h>
 
@@ -328,5 +329,71 @@ int orc_bias_grad(void* dbias, const void* dY, long long rows, int n, int dtype)
         }
     if (dtype == ORC_F32) memcpy(dbias, acc, (size_t)n * 4); else orc_narrow(acc, dbias, (size_t)n, dtype);
     free(acc);
+    return 0;
+}
+
+/* recpulse/module.py:289-300 over functional/functional_host.c:498-545 */
+int orc_lstm_gates_forward(void* Y, const void* X, const void* W, const void* H, const void* U, const void* bias,
+                           int m, int kx, int kh, int n, int dtype) {
+    if (!Y || !X || !W || !H || !U || m <= 0 || kx <= 0 || kh <= 0 || n <= 0 || n % 4 != 0) return -1;
+    const size_t es = dtype == ORC_F64 ? 8 : (dtype == ORC_F32 ? 4 : 2);
+    const size_t cnt = (size_t)m * n;
+    void* t2 = malloc(cnt * es);
+    if (!t2) return -1;
+    int rc = orc_rp_matmul(Y, X, W, m, kx, n, dtype);
+    if (rc == 0) rc = orc_rp_matmul(t2, H, U, m, kh, n, dtype);
+    if (rc) { free(t2); return rc; }
+    const int q = n / 4;
+    for (int i = 0; i < m; i++)
+        for (int j = 0; j < n; j++) {
+            const size_t e = (size_t)i * n + j;
+            const int is_tanh = j >= 2 * q && j < 3 * q;
+            if (dtype == ORC_F64) {
+                double* y = (double*)Y; const double* b = (const double*)bias;
+                volatile double v = y[e] + ((const double*)t2)[e];
+                if (b) { volatile double w2 = v + b[j]; v = w2; }
+                y[e] = is_tanh ? tanh(v) : 1.0 / (1.0 + exp(-v));
+            } else if (dtype == ORC_F32) {
+                float* y = (float*)Y; const float* b = (const float*)bias;
+                volatile float v = y[e] + ((const float*)t2)[e];
+                if (b) { volatile float w2 = v + b[j]; v = w2; }
+                y[e] = is_tanh ? tanhf(v) : 1.0f / (1.0f + expf(-v));
+            } else {
+                uint16_t* y = (uint16_t*)Y;
+                float a, c, s;
+                orc_widen(y + e, &a, 1, dtype); orc_widen((const uint16_t*)t2 + e, &c, 1, dtype);
+                s = a + c; orc_narrow(&s, y + e, 1, dtype);                       /* op_add rounds */
+                if (bias) {
+                    orc_widen(y + e, &a, 1, dtype); orc_widen((const uint16_t*)bias + j, &c, 1, dtype);
+                    s = a + c; orc_narrow(&s, y + e, 1, dtype);
+                }
+                orc_widen(y + e, &a, 1, dtype);
+                s = is_tanh ? tanhf(a) : 1.0f / (1.0f + expf(-a));
+                orc_narrow(&s, y + e, 1, dtype);
+            }
+        }
+    free(t2);
+    return 0;
+}
+
+/* ops/grad_host.c:365-385, 622-640 */
+int orc_lstm_gates_grad(void* dpre, const void* dY, const void* Y, long long rows, int n, int dtype) {
+    if (!dpre || !dY || !Y || rows <= 0 || n <= 0 || n % 4 != 0) return -1;
+    const int q = n / 4;
+    for (long long i = 0; i < rows; i++)
+        for (int j = 0; j < n; j++) {
+            const size_t e = (size_t)i * n + j;
+            const int is_tanh = j >= 2 * q && j < 3 * q;
+            if (dtype == ORC_F64) {
+                const double g = ((const double*)dY)[e], y = ((const double*)Y)[e];
+                ((double*)dpre)[e] = is_tanh ? g * (1 - y * y) : g * y * (1.0 - y);
+            } else {
+                float g, y, r;
+                if (dtype == ORC_F32) { g = ((const float*)dY)[e]; y = ((const float*)Y)[e]; }
+                else { orc_widen((const uint16_t*)dY + e, &g, 1, dtype); orc_widen((const uint16_t*)Y + e, &y, 1, dtype); }
+                r = is_tanh ? g * (1.0f - y * y) : g * y * (1.0f - y);
+                if (dtype == ORC_F32) ((float*)dpre)[e] = r; else orc_narrow(&r, (uint16_t*)dpre + e, 1, dtype);
+            }
+        }
     return 0;
 }

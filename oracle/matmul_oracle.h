@@ -75,6 +75,17 @@ int orc_linear_forward(void* Y, const void* X, const void* W, const void* bias, 
  * (fp64 for float64), one narrowing at the end. */
 int orc_bias_grad(void* dbias, const void* dY, long long rows, int n, int dtype);
 
+/* Activated gates of an LSTM cell as RecPulse composes them (recpulse/module.py:289-300):
+ * gates = op_add(op_matmul(X, W), op_matmul(H, U)), then op_add(bias) when bias != NULL, every node's output
+ * rounded to the storage dtype; columns split in four (i, f, g, o); sigmoid 1 / (1 + expf(-x)) on i, f, o and
+ * tanhf on g (functional/functional_host.c:498-545; f16/bf16 widen, compute in float, narrow).
+ * X: m x kx, W: kx x n, H: m x kh, U: kh x n, n a multiple of 4. */
+int orc_lstm_gates_forward(void* Y, const void* X, const void* W, const void* H, const void* U, const void* bias,
+                           int m, int kx, int kh, int n, int dtype);
+/* Gradient of the pre-activations from the activated output: g * y * (1 - y) for the sigmoid columns,
+ * g * (1 - y * y) for the tanh columns (ops/grad_host.c:365-385, 622-640), in float (double for float64). */
+int orc_lstm_gates_grad(void* dpre, const void* dY, const void* Y, long long rows, int n, int dtype);
+
 #ifdef __cplusplus
 }
 #endif

@@ -175,3 +175,27 @@ def bias_grad(dy, dtype):
     if rc != 0:
         raise RuntimeError("orc_bias_grad failed")
     return out
+
+
+def lstm_gates_forward(x, w, h, u, bias, dtype):
+    """Activated LSTM gates as RecPulse's LSTMCell.forward composes them (recpulse/module.py:289-300)."""
+    x = np.ascontiguousarray(x, _NP[dtype]); w = np.ascontiguousarray(w, _NP[dtype])
+    h = np.ascontiguousarray(h, _NP[dtype]); u = np.ascontiguousarray(u, _NP[dtype])
+    m, kx = x.shape; kh = h.shape[1]; n = w.shape[1]
+    b = None if bias is None else np.ascontiguousarray(bias, _NP[dtype]).reshape(-1)
+    y = np.empty((m, n), _NP[dtype])
+    rc = lib().orc_lstm_gates_forward(_p(y), _p(x), _p(w), _p(h), _p(u), _p(b) if b is not None else None, m, kx, kh, n, dtype)
+    if rc != 0:
+        raise RuntimeError("orc_lstm_gates_forward failed")
+    return y
+
+
+def lstm_gates_grad(dy, y, dtype):
+    """Gradient of the gate pre-activations from the activated output (sigmoid / tanh backward)."""
+    dy = np.ascontiguousarray(dy, _NP[dtype]); y = np.ascontiguousarray(y, _NP[dtype])
+    n = y.shape[-1]; rows = y.size // n
+    out = np.empty(y.shape, _NP[dtype])
+    rc = lib().orc_lstm_gates_grad(_p(out), _p(dy), _p(y), C.c_longlong(rows), n, dtype)
+    if rc != 0:
+        raise RuntimeError("orc_lstm_gates_grad failed")
+    return out

@@ -58,6 +58,11 @@ SYMBOLS = {
     "backward_linear_fn": (None, [C.POINTER(GradFn), TP]),
     "op_linear2": (TP, [TP, TP, TP, TP, TP]),
     "backward_linear2_fn": (None, [C.POINTER(GradFn), TP]),
+    "op_lstm_gates": (TP, [TP, TP, TP, TP, TP]),
+    "backward_lstm_gates_fn": (None, [C.POINTER(GradFn), TP]),
+    "rp_lstm_gates_ex": (C.c_int, [C.c_void_p, C.c_longlong, C.c_int, C.c_longlong, C.c_int, C.c_int, C.c_void_p]),
+    "rp_lstm_gates_grad_ex": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_longlong, C.c_int, C.c_longlong, C.c_longlong,
+                                        C.c_longlong, C.c_int, C.c_int, C.c_void_p]),
     "rp_colsum_ex": (C.c_int, [C.c_void_p, C.c_void_p, C.c_longlong, C.c_int, C.c_longlong, C.c_int, C.c_int, C.c_int,
                                C.c_void_p]),
     "rpb_gemm_packed": (None, [C.POINTER(RpbGemm), C.c_int, C.c_int, C.c_int]),

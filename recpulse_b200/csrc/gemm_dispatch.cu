@@ -17,6 +17,7 @@
 #include "gemm_simt.cuh"
 #include "gemm_tf32x3.cuh"
 #include "reduce_cols.cuh"
+#include "gate_act.cuh"
 #include "gemm_umma.cuh"
 #include "rpb_common.h"
 
@@ -933,6 +934,27 @@ int run_gemm(const RpbProblem& in, void* C, const void* A, const void* B, int de
 }
 
 template <typename T, typename Acc>
+int run_gates(void* y, long long rows, int n, long long ld, DeviceState* d, cudaStream_t s) {
+    long long blocks = (rows * n + 255) / 256;
+    const long long cap = (long long)d->sm_count * 16;
+    if (blocks > cap) blocks = cap;
+    RPB_CUDA(rpb_launch(rpb_gate::forward_kernel<T, Acc>, dim3((unsigned)blocks), dim3(256), 0, s, 1, reinterpret_cast<T*>(y), rows, n, ld));
+    g_launches++;
+    return 0;
+}
+template <typename T, typename Acc>
+int run_gates_grad(void* dpre, const void* dy, const void* y, long long rows, int n, long long ld_dpre, long long ld_dy,
+                   long long ld_y, DeviceState* d, cudaStream_t s) {
+    long long blocks = (rows * n + 255) / 256;
+    const long long cap = (long long)d->sm_count * 16;
+    if (blocks > cap) blocks = cap;
+    RPB_CUDA(rpb_launch(rpb_gate::backward_kernel<T, Acc>, dim3((unsigned)blocks), dim3(256), 0, s, 1, reinterpret_cast<T*>(dpre),
+                        reinterpret_cast<const T*>(dy), reinterpret_cast<const T*>(y), rows, n, ld_dpre, ld_dy, ld_y));
+    g_launches++;
+    return 0;
+}
+
+template <typename T, typename Acc>
 int run_colsum(void* out, const void* in, long long rows, int cols, long long ld, int accumulate, DeviceState* d,
                cudaStream_t stream) {
     const int col_blocks = (cols + rpb_cols::COLS - 1) / rpb_cols::COLS;
@@ -1023,6 +1045,51 @@ int rp_colsum_ex(void* out, const void* in, long long rows, int cols, long long 
             case DTYPE_FLOAT64: rc = run_colsum<double, double>(out, in, rows, cols, row_stride, accumulate, d, s); break;
             case DTYPE_FLOAT16: rc = run_colsum<__half, float>(out, in, rows, cols, row_stride, accumulate, d, s); break;
             case DTYPE_BFLOAT16: rc = run_colsum<__nv_bfloat16, float>(out, in, rows, cols, row_stride, accumulate, d, s); break;
+            default: rc = -1;
+        }
+    }
+    if (prev != device_id) cudaSetDevice(prev);
+    return rc;
+}
+
+int rp_lstm_gates_ex(void* y, long long rows, int n, long long row_stride, DType dtype, int device_id, void* stream) {
+    if (!y || rows <= 0 || n <= 0 || n % 4 != 0 || row_stride < n || device_id < 0) return -1;
+    int prev = -1;
+    RPB_CUDA(cudaGetDevice(&prev));
+    if (prev != device_id) RPB_CUDA(cudaSetDevice(device_id));
+    DeviceState* d = nullptr;
+    int rc = device_state(device_id, &d);
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    if (!rc) {
+        switch ((int)dtype) {
+            case DTYPE_FLOAT32: rc = run_gates<float, float>(y, rows, n, row_stride, d, s); break;
+            case DTYPE_FLOAT64: rc = run_gates<double, double>(y, rows, n, row_stride, d, s); break;
+            case DTYPE_FLOAT16: rc = run_gates<__half, float>(y, rows, n, row_stride, d, s); break;
+            case DTYPE_BFLOAT16: rc = run_gates<__nv_bfloat16, float>(y, rows, n, row_stride, d, s); break;
+            default: rc = -1;
+        }
+    }
+    if (prev != device_id) cudaSetDevice(prev);
+    return rc;
+}
+
+int rp_lstm_gates_grad_ex(void* dpre, const void* dy, const void* y, long long rows, int n, long long dpre_stride,
+                          long long dy_stride, long long y_stride, DType dtype, int device_id, void* stream) {
+    if (!dpre || !dy || !y || rows <= 0 || n <= 0 || n % 4 != 0 || dpre_stride < n || dy_stride < n || y_stride < n ||
+        device_id < 0)
+        return -1;
+    int prev = -1;
+    RPB_CUDA(cudaGetDevice(&prev));
+    if (prev != device_id) RPB_CUDA(cudaSetDevice(device_id));
+    DeviceState* d = nullptr;
+    int rc = device_state(device_id, &d);
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    if (!rc) {
+        switch ((int)dtype) {
+            case DTYPE_FLOAT32: rc = run_gates_grad<float, float>(dpre, dy, y, rows, n, dpre_stride, dy_stride, y_stride, d, s); break;
+            case DTYPE_FLOAT64: rc = run_gates_grad<double, double>(dpre, dy, y, rows, n, dpre_stride, dy_stride, y_stride, d, s); break;
+            case DTYPE_FLOAT16: rc = run_gates_grad<__half, float>(dpre, dy, y, rows, n, dpre_stride, dy_stride, y_stride, d, s); break;
+            case DTYPE_BFLOAT16: rc = run_gates_grad<__nv_bfloat16, float>(dpre, dy, y, rows, n, dpre_stride, dy_stride, y_stride, d, s); break;
             default: rc = -1;
         }
     }

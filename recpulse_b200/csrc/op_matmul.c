@@ -505,15 +505,17 @@ static void bias_grad_into(Tensor* bias, Tensor* grad_output) {
     if (fresh) bias->metadata->grad = grad;
 }
 
-Tensor* op_linear2(Tensor* x, Tensor* w, Tensor* h, Tensor* u, Tensor* bias) {
+/* shared by op_linear2 (gates = 0) and op_lstm_gates (gates = 1: the activation pass runs on the result) */
+static Tensor* linear2_node(Tensor* x, Tensor* w, Tensor* h, Tensor* u, Tensor* bias, int gates) {
     if (!operands_ok(x, w) || !operands_ok(h, u)) return NULL;
     if (x->dtype != h->dtype || x->device_id != h->device_id) return NULL;
     if (x->device_id < 0) {
-        fprintf(stderr, "recpulse_b200: op_linear2 on host tensors: this library has no CPU path\n");
+        fprintf(stderr, "recpulse_b200: op_linear2 / op_lstm_gates on host tensors: this library has no CPU path\n");
         return NULL;
     }
     const int n = w->shape[w->ndim - 1];
     if (u->shape[u->ndim - 1] != n) return NULL;
+    if (gates && n % 4 != 0) return NULL;
     if (bias && !bias_ok(bias, x, n)) return NULL;
     int nd = 0, oshape[RPB_MAX_BATCH_DIMS + 2], nd2 = 0, oshape2[RPB_MAX_BATCH_DIMS + 2];
     if (broadcast_batch(x, w, &nd, oshape) || broadcast_batch(h, u, &nd2, oshape2)) return NULL;
@@ -525,14 +527,23 @@ Tensor* op_linear2(Tensor* x, Tensor* w, Tensor* h, Tensor* u, Tensor* bias) {
     if (!out) return NULL;
     int rc = product_into(out, x, w, bias, 0, nd, oshape);
     if (rc == 0) rc = product_into(out, h, u, NULL, 1, nd, oshape);          /* second product lands in the epilogue's "+= C" */
+    if (rc == 0 && gates)
+        rc = rp_lstm_gates_ex(out->data, (long long)(out->size / (size_t)n), n, n, out->dtype, out->device_id, NULL);
     if (rc == 0 && cudaStreamSynchronize(NULL) != cudaSuccess) rc = -1;
     if (rc != 0) { rpb_tensor_release(out); return NULL; }
     if (wants_grad(x) || wants_grad(w) || wants_grad(h) || wants_grad(u) || wants_grad(bias)) {
         Tensor* in[5] = {x, w, h, u, bias};
-        if (attach_node(out, backward_linear2_fn, in, bias ? 5 : 4)) { rpb_tensor_release(out); return NULL; }
+        if (attach_node(out, gates ? backward_lstm_gates_fn : backward_linear2_fn, in, bias ? 5 : 4)) {
+            rpb_tensor_release(out);
+            return NULL;
+        }
     }
     return out;
 }
+
+Tensor* op_linear2(Tensor* x, Tensor* w, Tensor* h, Tensor* u, Tensor* bias) { return linear2_node(x, w, h, u, bias, 0); }
+
+Tensor* op_lstm_gates(Tensor* x, Tensor* w, Tensor* h, Tensor* u, Tensor* bias) { return linear2_node(x, w, h, u, bias, 1); }
 
 void backward_linear2_fn(GradFn* self, Tensor* grad_output) {
     if (!self || !grad_output || (self->num_inputs != 4 && self->num_inputs != 5) || !self->inputs) return;
@@ -541,6 +552,23 @@ void backward_linear2_fn(GradFn* self, Tensor* grad_output) {
     if (matmul_grads(in[0], in[1], grad_output)) return;
     if (matmul_grads(in[2], in[3], grad_output)) return;
     if (self->num_inputs == 5 && in[4]) bias_grad_into(in[4], grad_output);
+}
+
+void backward_lstm_gates_fn(GradFn* self, Tensor* grad_output) {
+    if (!self || !grad_output || !self->owner || (self->num_inputs != 4 && self->num_inputs != 5) || !self->inputs) return;
+    Tensor* y = self->owner;                    /* the activated gates */
+    if (y->device_id < 0 || grad_output->dtype != y->dtype || grad_output->size != y->size) return;
+    if (!is_contiguous(grad_output) || !is_contiguous(y)) {
+        fprintf(stderr, "recpulse_b200: op_lstm_gates backward needs packed output and upstream gradient\n");
+        return;
+    }
+    const int n = y->shape[y->ndim - 1];
+    Tensor* dpre = rpb_tensor_empty(y->dtype, y->ndim, y->shape, y->device_id);
+    if (!dpre) return;
+    int rc = rp_lstm_gates_grad_ex(dpre->data, grad_output->data, y->data, (long long)(y->size / (size_t)n), n, n, n, n,
+                                   y->dtype, y->device_id, NULL);
+    if (rc == 0) backward_linear2_fn(self, dpre);
+    rpb_tensor_release(dpre);
 }
 
 int rpb_backward_node(Tensor* out, Tensor* grad_output) {

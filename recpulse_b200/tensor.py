@@ -159,6 +159,14 @@ class Tensor:
             raise RuntimeError("op_linear2 operation failed")
         return Tensor(p, keepalive=(self, weight, h, u, bias))
 
+    def op_lstm_gates(self, weight: "Tensor", h: "Tensor", u: "Tensor", bias: "Tensor | None" = None) -> "Tensor":
+        """Activated LSTM gates act(self . weight + h . u + bias), columns i, f, g, o (sigmoid, sigmoid, tanh,
+        sigmoid), as one node; the composition of recpulse/module.py:289-300."""
+        p = _lib.load().op_lstm_gates(self._p, weight._p, h._p, u._p, bias._p if bias is not None else None)
+        if not p:
+            raise RuntimeError("op_lstm_gates operation failed")
+        return Tensor(p, keepalive=(self, weight, h, u, bias))
+
     def backward(self, grad_output: "Tensor") -> None:
         """Run this node's backward with an explicit upstream gradient and free the node."""
         if _lib.load().rpb_backward_node(self._p, grad_output._p) != 0:

@@ -33,3 +33,14 @@ def linear_golden():
         name, dtype, field = key.split("/")
         cases.setdefault((name, dtype), {})[field] = z[key]
     return cases
+
+
+@pytest.fixture(scope="session")
+def lstm_gates_golden():
+    import numpy as np
+    z = np.load(os.path.join(ROOT, "tests", "golden", "lstm_gates_golden.npz"))
+    cases = {}
+    for key in z.files:
+        name, dtype, field = key.split("/")
+        cases.setdefault((name, dtype), {})[field] = z[key]
+    return cases

@@ -1,4 +1,4 @@
-"""Generate tests/golden/matmul_golden.npz from the UNMODIFIED reference.
+"""Generate tests/golden/{matmul,linear,lstm_gates}_golden.npz from the UNMODIFIED reference.
 
 Run in a container where the reference tree is mounted and compiled by
 ``make -C oracle ref`` (produces oracle/_ref/recpulse_cuda.so):
@@ -82,6 +82,33 @@ def run_linear(name, dtype, m, k, n, rng):
     return {f"{name}/{dtype}/{key}": val for key, val in out.items()}
 
 
+def run_lstm_gates(name, dtype, m, kx, kh, hidden, rng):
+    """The gate block of LSTMCell.forward (recpulse/module.py:289-300) with one bias, loss = sum(act * g)."""
+    n = 4 * hidden
+    x64 = rng.uniform(-1, 1, (m, kx)); w64 = rng.uniform(-1, 1, (kx, n)) / np.sqrt(kx)
+    h64 = rng.uniform(-1, 1, (m, kh)); u64 = rng.uniform(-1, 1, (kh, n)) / np.sqrt(kh)
+    b64 = rng.uniform(-1, 1, (n,)); g64 = rng.uniform(-1, 1, (m, n))
+    x = to_rp(x64, dtype); w = to_rp(w64, dtype); h = to_rp(h64, dtype); u = to_rp(u64, dtype); b = to_rp(b64, dtype)
+    for t in (x, w, h, u, b):
+        t.requires_grad_(True)
+    gates = x.op_matmul(w).op_add(h.op_matmul(u)).op_add(b)
+    i_g, f_g, g_g, o_g = gates.chunk(4, 1)
+    acts = [i_g.op_sigmoid(), f_g.op_sigmoid(), g_g.op_tanh(), o_g.op_sigmoid()]
+    gs = [to_rp(g64[:, q * hidden:(q + 1) * hidden], dtype) for q in range(4)]
+    keep = [gates, i_g, f_g, g_g, o_g] + acts + gs
+    loss = None
+    for a, g in zip(acts, gs):
+        term = a.op_mul(g).op_sum_all()
+        keep.append(term)
+        loss = term if loss is None else loss.op_add(term)
+        keep.append(loss)
+    loss.backward()
+    out = {"x": bits(x), "w": bits(w), "h": bits(h), "u": bits(u), "b": bits(b),
+           "g": np.concatenate([bits(g) for g in gs], axis=1), "y": np.concatenate([bits(a) for a in acts], axis=1),
+           "dx": bits(x.grad), "dw": bits(w.grad), "dh": bits(h.grad), "du": bits(u.grad), "db": bits(b.grad)}
+    return {f"{name}/{dtype}/{key}": val for key, val in out.items()}
+
+
 def main():
     rng = np.random.default_rng(20240607)
     store = {}
@@ -103,6 +130,13 @@ def main():
             lin.update(run_linear(f"linear_{m}x{k}x{n}", dtype, m, k, n, rng))
     np.savez_compressed(os.path.join(HERE, "linear_golden.npz"), **lin)
     print("linear cases:", len(lin) // 8)
+    gates = {}
+    rng = np.random.default_rng(20240609)
+    for dtype in DT:
+        for (m, kx, kh, hidden) in [(3, 5, 4, 2), (16, 24, 8, 8), (9, 33, 17, 5)]:
+            gates.update(run_lstm_gates(f"gates_{m}x{kx}x{kh}x{hidden}", dtype, m, kx, kh, hidden, rng))
+    np.savez_compressed(os.path.join(HERE, "lstm_gates_golden.npz"), **gates)
+    print("lstm gate cases:", len(gates) // 12)
 
 
 if __name__ == "__main__":

@@ -27,7 +27,9 @@ def f64(x, dtype):
     return O.to_f64(np.asarray(x), CODE[dtype])
 
 
-def check_close(got, ref, dtype, k, what=""):
+def check_close(got, ref, dtype, k, what="", tight=True):
+    """`tight=False` for results that sit behind several roundings of the 16-bit type in the reference's
+    composition (a chain of nodes), where only the path's stated tolerance applies."""
     g = f64(got, dtype); r = f64(ref, dtype)
     assert g.shape == r.shape, (what, g.shape, r.shape)
     err = np.abs(g - r)
@@ -41,7 +43,7 @@ def check_close(got, ref, dtype, k, what=""):
     else:
         fro = float(np.linalg.norm(g - r) / (np.linalg.norm(r) or 1.0))
         assert fro <= HALF_FROB, f"{what}: {dtype} rel Frobenius {fro:.3e}"
-        assert fro <= HALF_FROB_TIGHT[dtype], f"{what}: {dtype} rel Frobenius {fro:.3e} (tight bound)"
+        assert not tight or fro <= HALF_FROB_TIGHT[dtype], f"{what}: {dtype} rel Frobenius {fro:.3e} (tight bound)"
 
 
 def gemm_ex(lib, a_dev, b_dev, c_dev, g, dtype, device=0, stream=None):

@@ -232,3 +232,82 @@ def test_gate_node_two_products_one_output(lib, dtype):
         del comp
     with pytest.raises(RuntimeError):
         T(x, dtype).op_linear2(T(w, dtype), T(h, dtype), T(rand_operand(rng, (hdim, n + 8), dtype), dtype))
+
+
+@pytest.mark.parametrize("family", [_lib.KERNEL_SIMT, 0])
+@pytest.mark.parametrize("dtype", ["float32", "float64", "float16", "bfloat16"])
+def test_lstm_gates_node_vs_reference_fixtures(lib, lstm_gates_golden, dtype, family):
+    """op_lstm_gates against the reference's own run of LSTMCell's gate block (matmul, matmul, add, add, chunk,
+    sigmoid / tanh) and of its backward down to all five leaves."""
+    lib.rpb_force_kernel(family)
+    try:
+        for (name, dt), case in lstm_gates_golden.items():
+            if dt != dtype:
+                continue
+            m, kx = case["x"].shape; kh = case["h"].shape[1]; n = case["w"].shape[1]
+            x = T(case["x"], dtype, True); w = T(case["w"], dtype, True); h = T(case["h"], dtype, True)
+            u = T(case["u"], dtype, True); b = T(case["b"], dtype, True)
+            y = x.op_lstm_gates(w, h, u, b)
+            check_close(y.to_numpy(), case["y"], dtype, kx + kh, f"{name} y", tight=False)
+            y.backward(T(case["g"], dtype))
+            check_close(x.grad.to_numpy(), case["dx"], dtype, n, f"{name} dx", tight=False)
+            check_close(w.grad.to_numpy(), case["dw"], dtype, m, f"{name} dw", tight=False)
+            check_close(h.grad.to_numpy(), case["dh"], dtype, n, f"{name} dh", tight=False)
+            check_close(u.grad.to_numpy(), case["du"], dtype, m, f"{name} du", tight=False)
+            check_close(b.grad.to_numpy(), case["db"], dtype, m, f"{name} dbias", tight=False)
+    finally:
+        lib.rpb_force_kernel(0)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "float64", "float16", "bfloat16"])
+def test_lstm_gates_node_cell_sizes(lib, dtype):
+    """LSTM cell sizes (batch 64 / 128, hidden 256 / 512) against the oracle's restatement of the composition;
+    no bias as well; a column count that is not a multiple of 4 is refused."""
+    rng = np.random.default_rng(83)
+    for (bsz, e, hdim, bias) in [(64, 64, 256, True), (128, 512, 512, True), (33, 40, 24, False)]:
+        n = 4 * hdim
+        x = rand_operand(rng, (bsz, e), dtype); w = rand_operand(rng, (e, n), dtype, scale=1 / np.sqrt(e))
+        h = rand_operand(rng, (bsz, hdim), dtype); u = rand_operand(rng, (hdim, n), dtype, scale=1 / np.sqrt(hdim))
+        b = rand_operand(rng, (n,), dtype) if bias else None
+        g = rand_operand(rng, (bsz, n), dtype)
+        X = T(x, dtype, True); W = T(w, dtype, True); H = T(h, dtype, True); U = T(u, dtype, True)
+        B = T(b, dtype, True) if bias else None
+        y = X.op_lstm_gates(W, H, U, B)
+        ref_y = O.lstm_gates_forward(x, w, h, u, b, CODE[dtype])
+        check_close(y.to_numpy(), ref_y, dtype, e + hdim, "gates")
+        got_y = y.to_numpy()
+        y.backward(T(g, dtype))
+        dpre = O.lstm_gates_grad(g, got_y, CODE[dtype])          # from the node's own output: isolates the backward
+        dx, dw = O.matmul_backward(x, w, dpre, CODE[dtype])
+        dh, du = O.matmul_backward(h, u, dpre, CODE[dtype])
+        check_close(X.grad.to_numpy(), dx, dtype, n, "dx"); check_close(W.grad.to_numpy(), dw, dtype, bsz, "dw")
+        check_close(H.grad.to_numpy(), dh, dtype, n, "dh"); check_close(U.grad.to_numpy(), du, dtype, bsz, "du")
+        if bias:
+            check_close(B.grad.to_numpy(), O.bias_grad(dpre, CODE[dtype]), dtype, bsz, "dbias")
+    with pytest.raises(RuntimeError):
+        T(x, dtype).op_lstm_gates(T(rand_operand(rng, (x.shape[1], 6), dtype), dtype), T(h, dtype),
+                                  T(rand_operand(rng, (h.shape[1], 6), dtype), dtype))
+
+
+def test_lstm_gate_passes_on_strided_rows(lib):
+    """rp_lstm_gates_ex / rp_lstm_gates_grad_ex on matrices whose rows are further apart than n."""
+    import ctypes as C
+    rng = np.random.default_rng(89)
+    for dtype in ("float32", "bfloat16", "float64"):
+        rows, n, pad = 37, 24, 8
+        pre = rand_operand(rng, (rows, n + pad), dtype); g = rand_operand(rng, (rows, n + pad), dtype)
+        t = T(pre, dtype)
+        assert lib.rp_lstm_gates_ex(C.c_void_p(t.data_ptr), rows, n, n + pad, CODE[dtype], 0, None) == 0
+        out = t.to_numpy()
+        from helpers import f64
+        p64 = f64(pre, dtype)[:, :n]
+        ref = 1 / (1 + np.exp(-p64)); ref[:, n // 2:3 * n // 4] = np.tanh(p64[:, n // 2:3 * n // 4])
+        tol = {"float32": 1e-6, "float64": 1e-14, "bfloat16": 8e-3}[dtype]
+        assert np.max(np.abs(f64(out, dtype)[:, :n] - ref)) < tol
+        assert np.array_equal(out[:, n:], pre[:, n:])              # the padding is not touched
+        tg = T(g, dtype); td = T(np.zeros((rows, n), O.storage(CODE[dtype])), dtype)
+        assert lib.rp_lstm_gates_grad_ex(C.c_void_p(td.data_ptr), C.c_void_p(tg.data_ptr), C.c_void_p(t.data_ptr), rows, n,
+                                         n, n + pad, n + pad, CODE[dtype], 0, None) == 0
+        exp = O.lstm_gates_grad(np.ascontiguousarray(g[:, :n]), np.ascontiguousarray(out[:, :n]), CODE[dtype])
+        check_close(td.to_numpy(), exp, dtype, 1, "gate grad")
+        assert lib.rp_lstm_gates_ex(C.c_void_p(t.data_ptr), rows, 6, 8, CODE[dtype], 0, None) == -1   # n % 4 != 0

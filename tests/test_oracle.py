@@ -148,3 +148,24 @@ def test_linear_composition_bit_exact_vs_reference_fixtures(linear_golden, dtype
         assert np.array_equal(dx, case["dx"]) and np.array_equal(dw, case["dw"]), name
         assert np.array_equal(O.bias_grad(case["g"], code), case["db"]), name
     assert seen == 3
+
+
+@pytest.mark.parametrize("dtype", list(CODE))
+def test_lstm_gates_composition_bit_exact_vs_reference_fixtures(lstm_gates_golden, dtype):
+    """The gate block of LSTMCell.forward (module.py:289-300) and its five gradients, as run by the reference:
+    forward, then dY -> gradient of the pre-activations -> the two matmul backwards and the bias gradient."""
+    seen = 0
+    for (name, dt), case in lstm_gates_golden.items():
+        if dt != dtype:
+            continue
+        seen += 1
+        code = CODE[dtype]
+        y = O.lstm_gates_forward(case["x"], case["w"], case["h"], case["u"], case["b"], code)
+        assert np.array_equal(y, case["y"]), name
+        dpre = O.lstm_gates_grad(case["g"], case["y"], code)
+        dx, dw = O.matmul_backward(case["x"], case["w"], dpre, code)
+        dh, du = O.matmul_backward(case["h"], case["u"], dpre, code)
+        assert np.array_equal(dx, case["dx"]) and np.array_equal(dw, case["dw"]), name
+        assert np.array_equal(dh, case["dh"]) and np.array_equal(du, case["du"]), name
+        assert np.array_equal(O.bias_grad(dpre, code), case["db"]), name
+    assert seen == 3
