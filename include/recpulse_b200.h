@@ -163,7 +163,11 @@ typedef struct {
     int max_sms;                    /* 0 = use every SM; otherwise the persistent tensor-core */
                                     /* kernels occupy at most this many SMs, leaving the rest */
                                     /* to work that runs beside the GEMM (a collective)       */
+    int epilogue;                   /* 0: none; 1 (RPB_EPILOGUE_LSTM_GATES): after bias and "+= C", columns   */
+                                    /* [n/2, 3n/4) go through tanh and the others through 1 / (1 + exp(-x))    */
+                                    /* before the one rounding; n must be a multiple of 4                      */
 } RpbGemm;
+#define RPB_EPILOGUE_LSTM_GATES 1
 
 /* Fills `g` for a packed row-major m x k times k x n product (batch = reduce = 1). */
 void rpb_gemm_packed(RpbGemm* g, int m, int k, int n);

@@ -44,7 +44,7 @@ class RpbGemm(C.Structure):
     _fields_ = [("m", C.c_int), ("n", C.c_int), ("k", C.c_int), ("batch", C.c_int), ("reduce", C.c_int),
                 ("a_row", C.c_longlong), ("a_col", C.c_longlong), ("a_batch", C.c_longlong), ("a_reduce", C.c_longlong),
                 ("b_row", C.c_longlong), ("b_col", C.c_longlong), ("b_batch", C.c_longlong), ("b_reduce", C.c_longlong),
-                ("c_row", C.c_longlong), ("c_batch", C.c_longlong), ("accumulate", C.c_int), ("bias", C.c_void_p), ("max_sms", C.c_int)]
+                ("c_row", C.c_longlong), ("c_batch", C.c_longlong), ("accumulate", C.c_int), ("bias", C.c_void_p), ("max_sms", C.c_int), ("epilogue", C.c_int)]
 
 
 # every symbol include/recpulse_b200.h declares: name -> (restype, argtypes)

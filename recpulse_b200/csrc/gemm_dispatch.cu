@@ -42,6 +42,7 @@ std::mutex g_mutex;
 std::atomic<unsigned long long> g_launches{0};
 std::atomic<int> g_force{-1};
 thread_local int t_last_kernel = RPB_KERNEL_NONE;
+thread_local bool t_act_fused = false;      /* set by the launcher whose epilogue applied RpbProblem.act */
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -215,6 +216,8 @@ int launch_simt_cfg(const RpbProblem& p, void* C, const void* A, const void* B, 
         if (get_scratch(d, bytes, stream, &a.partial)) return -1;
     }
     constexpr int NT = (BM / TM) * (BN / TN);
+    a.act = a.splits == 1 ? p.act : 0;
+    if (a.act) t_act_fused = true;
     RPB_CUDA(rpb_launch(rpb_simt::gemm_kernel<T, Acc, BM, BN, BK, TM, TN>, dim3((unsigned)blocks), dim3(NT), 0, stream, 1, a));
     g_launches++;
     if (a.splits > 1) {
@@ -293,6 +296,8 @@ int launch_dmma(const RpbProblem& p, void* C, const void* A, const void* B, Devi
             blocks = sms;
         }
     }
+    a.act = (a.splits == 1 && a.sk_ctas == 0) ? p.act : 0;
+    if (a.act) t_act_fused = true;
     int rc;
     if (!a_mn && !b_mn) rc = launch_dmma_inst<false, false>(a, blocks, stream);
     else if (!a_mn && b_mn) rc = launch_dmma_inst<false, true>(a, blocks, stream);
@@ -355,6 +360,8 @@ int launch_tf32_cfg(const RpbProblem& p, void* C, const void* A, const void* B, 
     const long long blocks = tiles * a.splits;
     if (blocks > 0x7fffffffLL) return 1;
     if (a.splits > 1 && get_scratch(d, sizeof(float) * (size_t)a.splits * p.batch * p.m * p.n, stream, &a.partial)) return -1;
+    a.act = a.splits == 1 ? p.act : 0;
+    if (a.act) t_act_fused = true;
     int rc;
     if (!a_mn && !b_mn) rc = launch_tf32_inst<BM, BN, WM, WN, false, false>(a, blocks, stream);
     else if (!a_mn && b_mn) rc = launch_tf32_inst<BM, BN, WM, WN, false, true>(a, blocks, stream);
@@ -671,6 +678,9 @@ int launch_umma(const RpbProblem& p, void* C, const void* A, const void* B, Devi
         if (encode_store_map(&mc, C, dt, ES, p.n, p.m, p.batch, p.c_row, p.c_batch, 128 / ES) == 0) a.tma_store = 1;
     }
 
+    /* the gate non-linearity lives in the register epilogue (it follows "C += AB" in its only user) */
+    if (p.act && a.splits == 1) a.tma_store = 0;
+    a.act = a.splits == 1 ? p.act : 0;
     /* Tail split: if the last wave of tiles would keep fewer than half of the CTAs (or CTA pairs) busy, cut
      * its tiles along K so that the wave is short instead of sparse (4096^3: 256 tiles on 74 pairs = 3 waves +
      * 34 tiles; with two K slices each the run takes 3.5 tile times instead of 4). */
@@ -702,6 +712,7 @@ int launch_umma(const RpbProblem& p, void* C, const void* A, const void* B, Devi
             }
         }
     }
+    if (a.act) t_act_fused = true;
     int grid = (int)(a.total_work < sms ? a.total_work : sms);
     int rc;
     if (pair) {
@@ -798,6 +809,7 @@ int launch_umma_packed(const RpbProblem& p, void* C, const void* A, const void* 
                                           (p.batch > 1 && p.c_batch % AL != 0));
     if (pa.ok && pb.ok && !c_odd) return 1;             /* nothing to pack: the caller already tried the direct path */
     RpbProblem q = p;
+    q.act = 0;                                          /* a padded C has other column quarters: the caller's pass applies it */
     void* tmp[3] = {nullptr, nullptr, nullptr};
     const void* A2 = A; const void* B2 = B;
     /* packs one operand; on return *mn_stride / *k_stride are its new element strides */
@@ -867,7 +879,7 @@ int validate(const RpbProblem& p, const void* C, const void* A, const void* B) {
     return 0;
 }
 
-int run_gemm(const RpbProblem& in, void* C, const void* A, const void* B, int device_id, cudaStream_t stream) {
+int run_gemm_planned(const RpbProblem& in, void* C, const void* A, const void* B, int device_id, cudaStream_t stream) {
     if (validate(in, C, A, B)) return -1;
     RpbProblem p = in;
     /* a broadcast B with packed A / C batches is one tall GEMM; summed problems whose K ranges are
@@ -954,6 +966,32 @@ int run_gates_grad(void* dpre, const void* dy, const void* y, long long rows, in
     return 0;
 }
 
+/* The GEMM, then — when an epilogue non-linearity was asked for and the plan that ran could not apply it in its
+ * own epilogue (K slices, balanced fp64 schedule, packed or padded operands) — one element-wise pass over C. */
+int run_gemm(const RpbProblem& p, void* C, const void* A, const void* B, int device_id, cudaStream_t stream) {
+    if (p.act && (p.act != 1 || p.n % 4 != 0)) {
+        fprintf(stderr, "recpulse_b200: epilogue %d needs n to be a multiple of 4 (n=%d)\n", p.act, p.n);
+        return -1;
+    }
+    t_act_fused = false;
+    int rc = run_gemm_planned(p, C, A, B, device_id, stream);
+    if (rc || !p.act || t_act_fused) return rc;
+    DeviceState* d = nullptr;
+    if (device_state(device_id, &d)) return -1;
+    const size_t es = rpb_dtype_size(p.dtype);
+    for (int b = 0; b < p.batch && !rc; ++b) {
+        void* cb = reinterpret_cast<char*>(C) + (size_t)b * p.c_batch * es;
+        switch (p.dtype) {
+            case DTYPE_FLOAT32: rc = run_gates<float, float>(cb, p.m, p.n, p.c_row, d, stream); break;
+            case DTYPE_FLOAT64: rc = run_gates<double, double>(cb, p.m, p.n, p.c_row, d, stream); break;
+            case DTYPE_FLOAT16: rc = run_gates<__half, float>(cb, p.m, p.n, p.c_row, d, stream); break;
+            case DTYPE_BFLOAT16: rc = run_gates<__nv_bfloat16, float>(cb, p.m, p.n, p.c_row, d, stream); break;
+            default: rc = -1;
+        }
+    }
+    return rc;
+}
+
 template <typename T, typename Acc>
 int run_colsum(void* out, const void* in, long long rows, int cols, long long ld, int accumulate, DeviceState* d,
                cudaStream_t stream) {
@@ -1021,7 +1059,7 @@ int rp_matmul_ex(void* C, const void* A, const void* B, const RpbGemm* g, DType 
     p.a_row = g->a_row; p.a_col = g->a_col; p.a_batch = g->a_batch; p.a_reduce = g->a_reduce;
     p.b_row = g->b_row; p.b_col = g->b_col; p.b_batch = g->b_batch; p.b_reduce = g->b_reduce;
     p.c_row = g->c_row; p.c_batch = g->c_batch; p.accumulate = g->accumulate; p.dtype = (int)dtype;
-    p.bias = g->bias; p.max_sms = g->max_sms;
+    p.bias = g->bias; p.max_sms = g->max_sms; p.act = g->epilogue;
     int prev = -1;
     RPB_CUDA(cudaGetDevice(&prev));
     if (prev != device_id) RPB_CUDA(cudaSetDevice(device_id));
@@ -1107,7 +1145,7 @@ int matmul_kernel_device(void* C, const void* A, const void* B, int m, int k, in
     p.m = m; p.n = n; p.k = k; p.batch = 1; p.reduce = 1;
     p.a_row = g.a_row; p.a_col = 1; p.a_batch = 0; p.a_reduce = 0;
     p.b_row = g.b_row; p.b_col = 1; p.b_batch = 0; p.b_reduce = 0;
-    p.c_row = n; p.c_batch = 0; p.accumulate = 0; p.dtype = (int)dtype; p.bias = nullptr; p.max_sms = 0;
+    p.c_row = n; p.c_batch = 0; p.accumulate = 0; p.dtype = (int)dtype; p.bias = nullptr; p.max_sms = 0; p.act = 0;
     if (run_gemm(p, C, A, B, dev, nullptr)) return -1;
     RPB_CUDA(cudaStreamSynchronize(nullptr));
     return 0;

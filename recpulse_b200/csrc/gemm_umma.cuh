@@ -91,6 +91,7 @@ struct Args {
     uint64_t a_desc_base, b_desc_base;   /* shared-memory descriptors without start address */
     uint32_t a_kstep, b_kstep;           /* descriptor advance per UMMA_K, in 16-byte units */
     int* status;
+    int act;               /* 1: LSTM gate non-linearities on the finished sum (register epilogue, no K slices) */
 };
 
 /* ------------------------------------------------------------------ PTX wrappers */
@@ -675,12 +676,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                                     const float4 o = *reinterpret_cast<const float4*>(dst + j);
                                     f.x += o.x; f.y += o.y; f.z += o.z; f.w += o.w;
                                 }
+                                if (args.act) {
+                                    const int q = args.n >> 2;
+                                    f.x = rpb_gate_act(f.x, col + j, q); f.y = rpb_gate_act(f.y, col + j + 1, q);
+                                    f.z = rpb_gate_act(f.z, col + j + 2, q); f.w = rpb_gate_act(f.w, col + j + 3, q);
+                                }
                                 *reinterpret_cast<float4*>(dst + j) = f;
                             }
                         } else {
                             for (int j = 0; j < 32 && col + j < args.n; ++j) {
                                 float f = __uint_as_float(v[j]);
                                 if (args.accumulate) f += to_f32<T>(dst[j]);
+                                if (args.act) f = rpb_gate_act(f, col + j, args.n >> 2);
                                 dst[j] = from_f32<T>(f);
                             }
                         }
@@ -696,6 +703,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
 #pragma unroll
                                 for (int e = 0; e < 8; ++e) f[e] += to_f32<T>(o[e]);
                             }
+                            if (args.act) {
+#pragma unroll
+                                for (int e = 0; e < 8; ++e) f[e] = rpb_gate_act(f[e], col + j + e, args.n >> 2);
+                            }
                             uint4 out = make_uint4(pack2<T>(f[0], f[1]), pack2<T>(f[2], f[3]),
                                                    pack2<T>(f[4], f[5]), pack2<T>(f[6], f[7]));
                             *reinterpret_cast<uint4*>(dst + j) = out;
@@ -704,6 +715,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                         for (int j = 0; j < 32 && col + j < args.n; ++j) {
                             float f = __uint_as_float(v[j]);
                             if (args.accumulate) f += to_f32<T>(dst[j]);
+                            if (args.act) f = rpb_gate_act(f, col + j, args.n >> 2);
                             dst[j] = from_f32<T>(f);
                         }
                     }

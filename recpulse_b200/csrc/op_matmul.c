@@ -288,7 +288,7 @@ static bool bias_ok(const Tensor* bias, const Tensor* a, int n) {
 
 /* out (+)= a . b (+ bias) for operands that already passed the shape checks; out is packed with the
  * broadcast batch shape of a and b */
-static int product_into(Tensor* out, const Tensor* a, const Tensor* b, const Tensor* bias, int accumulate,
+static int product_into(Tensor* out, const Tensor* a, const Tensor* b, const Tensor* bias, int accumulate, int epilogue,
                         int nd, const int* oshape) {
     const int m = a->shape[a->ndim - 2], k = a->shape[a->ndim - 1], n = b->shape[b->ndim - 1];
     RpbGemm g;
@@ -298,6 +298,7 @@ static int product_into(Tensor* out, const Tensor* a, const Tensor* b, const Ten
     g.a_batch = g.b_batch = g.c_batch = 0;
     g.bias = bias ? bias->data : NULL;
     g.accumulate = accumulate;
+    g.epilogue = epilogue;
     BatchDim bd[RPB_MAX_BATCH_DIMS];
     int nbd = 0;
     for (int i = 0; i < nd; i++) {
@@ -360,7 +361,7 @@ static Tensor* matmul_node(Tensor* a, Tensor* b, Tensor* bias) {
     Tensor* out = rpb_tensor_empty(a->dtype, nd + 2, oshape, a->device_id);
     if (!out) return NULL;
 
-    int rc = product_into(out, a, b, bias, 0, nd, oshape);
+    int rc = product_into(out, a, b, bias, 0, 0, nd, oshape);
     /* callers assume the result is complete on return (every RecPulse device op synchronises) */
     if (rc == 0 && cudaStreamSynchronize(NULL) != cudaSuccess) rc = -1;
     if (rc != 0) { rpb_tensor_release(out); return NULL; }
@@ -525,10 +526,10 @@ static Tensor* linear2_node(Tensor* x, Tensor* w, Tensor* h, Tensor* u, Tensor* 
 
     Tensor* out = rpb_tensor_empty(x->dtype, nd + 2, oshape, x->device_id);
     if (!out) return NULL;
-    int rc = product_into(out, x, w, bias, 0, nd, oshape);
-    if (rc == 0) rc = product_into(out, h, u, NULL, 1, nd, oshape);          /* second product lands in the epilogue's "+= C" */
-    if (rc == 0 && gates)
-        rc = rp_lstm_gates_ex(out->data, (long long)(out->size / (size_t)n), n, n, out->dtype, out->device_id, NULL);
+    int rc = product_into(out, x, w, bias, 0, 0, nd, oshape);
+    /* the second product lands in the epilogue's "+= C"; for the gate block the same epilogue then applies the
+     * non-linearities to the finished sum (or, for plans that cannot, one pass over the output does) */
+    if (rc == 0) rc = product_into(out, h, u, NULL, 1, gates ? RPB_EPILOGUE_LSTM_GATES : 0, nd, oshape);
     if (rc == 0 && cudaStreamSynchronize(NULL) != cudaSuccess) rc = -1;
     if (rc != 0) { rpb_tensor_release(out); return NULL; }
     if (wants_grad(x) || wants_grad(w) || wants_grad(h) || wants_grad(u) || wants_grad(bias)) {

@@ -18,6 +18,7 @@ struct RpbProblem {
     int dtype;                 /* DType code */
     const void* bias;          /* n values of dtype, or NULL */
     int max_sms;               /* 0 = all */
+    int act;                   /* RpbGemm.epilogue: 0 none, 1 LSTM gate non-linearities by column quarter */
 };
 
 #ifdef __CUDACC__
@@ -28,6 +29,16 @@ struct RpbProblem {
  * prologue overlap this kernel's tail.  Both are no-ops for kernels launched the ordinary way. */
 __device__ __forceinline__ void rpb_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void rpb_pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+/* Epilogue non-linearity of the LSTM gate block: columns [2q, 3q) of the n = 4q outputs go through tanh, the
+ * others through the logistic function, as sigmoid_kernel / tanh_kernel of the reference compute them
+ * (functional/functional_device.cu:524-550).  Applied to the finished sum (bias and C included) before rounding. */
+__device__ __forceinline__ float rpb_gate_act(float v, int col, int quarter) {
+    return (col >= 2 * quarter && col < 3 * quarter) ? tanhf(v) : 1.0f / (1.0f + expf(-v));
+}
+__device__ __forceinline__ double rpb_gate_act(double v, int col, int quarter) {
+    return (col >= 2 * quarter && col < 3 * quarter) ? tanh(v) : 1.0 / (1.0 + exp(-v));
+}
 
 #include <cstdlib>
 #include <utility>

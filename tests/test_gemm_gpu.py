@@ -2,6 +2,7 @@
 against the CPU oracle, through the C ABI.  Sizes are kept where the oracle's naive loop
 finishes in seconds; full-size workloads are covered by test_full_size_gpu.py."""
 import ctypes as C
+import os
 
 import numpy as np
 import pytest
@@ -41,7 +42,8 @@ def store(logical, transposed, pad):
     return buf, rs, cs, rows * ld
 
 
-def run_ex(lib, dtype, a, b, ta=False, tb=False, pad_a=0, pad_b=0, c_init=None, expect=None, oracle=True, bias=None):
+def run_ex(lib, dtype, a, b, ta=False, tb=False, pad_a=0, pad_b=0, c_init=None, expect=None, oracle=True, bias=None,
+           gates=False):
     """a: [batch|1, reduce|1, m, k] bits, b: [batch|1, reduce|1, k, n] bits (size-1 dims broadcast)."""
     batch = max(a.shape[0], b.shape[0]); reduce = max(a.shape[1], b.shape[1])
     m, k = a.shape[2:]; n = b.shape[3]
@@ -56,6 +58,7 @@ def run_ex(lib, dtype, a, b, ta=False, tb=False, pad_a=0, pad_b=0, c_init=None, 
     g.b_batch = b_mat * b.shape[1] if b.shape[0] > 1 else 0
     g.c_row, g.c_batch = n, m * n
     g.accumulate = int(c_init is not None)
+    g.epilogue = 1 if gates else 0
     tbias = dev(bias, dtype) if bias is not None else None
     g.bias = tbias.data_ptr if tbias is not None else None
     ta_, tb_ = dev(abuf, dtype), dev(bbuf, dtype)
@@ -75,10 +78,14 @@ def run_ex(lib, dtype, a, b, ta=False, tb=False, pad_a=0, pad_b=0, c_init=None, 
         ref64 = ref64 + f64(bias, dtype)[None, None, :]
     if c_init is not None:
         ref64 = ref64 + f64(c_init, dtype)
+    if gates:                                                   # LSTM gate epilogue: tanh on the third column quarter
+        q = n // 4
+        act = 1 / (1 + np.exp(-ref64)); act[..., 2 * q:3 * q] = np.tanh(ref64[..., 2 * q:3 * q])
+        ref64 = act
     ref = O.narrow(ref64.astype(np.float32), CODE[dtype]) if dtype in ("float16", "bfloat16") else ref64.astype(
         O.storage(CODE[dtype]))
     check_close(got, ref, dtype, k * reduce, what=f"{dtype} m{m} k{k} n{n} b{batch} r{reduce} ta{ta} tb{tb}")
-    if reduce == 1 and c_init is None and bias is None and oracle:
+    if reduce == 1 and c_init is None and bias is None and oracle and not gates:
         # same-dtype reference of the path: the oracle's restatement of rp_matmul
         for bi in range(batch):
             o = O.rp_matmul(np.ascontiguousarray(a[min(bi, a.shape[0] - 1), 0]),
@@ -280,6 +287,38 @@ def test_every_tile_plan_gives_the_same_product(lib, dtype, plan, monkeypatch):
         run_ex(lib, dtype, a, b, c_init=rand_operand(rng, (1, m, n), dtype), expect=UMMA, oracle=False)
     finally:
         lib.rpb_force_kernel(0)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "float64", "float16", "bfloat16"])
+def test_gate_epilogue_in_every_kernel_family(lib, dtype):
+    """RpbGemm.epilogue = LSTM gates: applied inside the epilogue of the plans that write C directly (general-stride,
+    mma.sync fp32 / fp64, tcgen05 register epilogue) and by one pass over C behind the others (K slices, balanced fp64
+    schedule, packed operands); always after bias and "C += AB"."""
+    rng = np.random.default_rng(131)
+    cases = [((64, 512, 2048), None), ((128, 64, 1024), None), ((40, 36, 24), None), ((64, 4096, 64), None),
+             ((1700, 300, 1500), None), ((520, 1160, 776), "128,2,0"), ((520, 1160, 776), "128,1,1")]
+    for (m, k, n), plan in cases:
+        if plan and dtype == "float64":
+            continue
+        a = rand_operand(rng, (1, 1, m, k), dtype); b = rand_operand(rng, (1, 1, k, n), dtype, scale=1 / np.sqrt(k))
+        bias = rand_operand(rng, (n,), dtype); c0 = rand_operand(rng, (1, m, n), dtype)
+        if plan:
+            os.environ["RPB_UMMA_PLAN"] = plan
+            lib.rpb_force_kernel(_lib.KERNEL_UMMA)
+        try:
+            run_ex(lib, dtype, a, b, gates=True)
+            run_ex(lib, dtype, a, b, gates=True, bias=bias, c_init=c0)
+            run_ex(lib, dtype, a, b, tb=True, gates=True, c_init=c0)
+        finally:
+            os.environ.pop("RPB_UMMA_PLAN", None)
+            lib.rpb_force_kernel(0)
+    lib.rpb_force_kernel(_lib.KERNEL_SIMT)
+    a = rand_operand(rng, (2, 1, 33, 20), dtype); b = rand_operand(rng, (2, 1, 20, 16), dtype)
+    run_ex(lib, dtype, a, b, gates=True, expect=(_lib.KERNEL_SIMT,))
+    lib.rpb_force_kernel(0)
+    g = rpb.RpbGemm(); lib.rpb_gemm_packed(C.byref(g), 4, 4, 6); g.epilogue = 1          # n % 4 != 0 is refused
+    t = dev(np.zeros((4, 6), O.storage(CODE[dtype])), dtype)
+    assert lib.rp_matmul_ex(C.c_void_p(t.data_ptr), C.c_void_p(t.data_ptr), C.c_void_p(t.data_ptr), C.byref(g), CODE[dtype], 0, None) == -1
 
 
 @pytest.mark.parametrize("dtype", ["bfloat16", "float16"])
