@@ -71,7 +71,7 @@ def parse():
 # so its figure is the 8192-row capture scaled by the row count (A, C and the per-row-block re-reads of B
 # all grow with the rows).
 NCU_TRAFFIC_BYTES = {
-    "rowsharded_65536x8192x8192": lambda rows: 1.1976e9 * rows / 8192.0,
+    "rowsharded_65536x8192x8192": lambda rows: 1.2109e9 * rows / 8192.0,      # 1.083 GB read + 0.128 GB written
 }
 
 
