@@ -321,6 +321,29 @@ def test_gate_epilogue_in_every_kernel_family(lib, dtype):
     assert lib.rp_matmul_ex(C.c_void_p(t.data_ptr), C.c_void_p(t.data_ptr), C.c_void_p(t.data_ptr), C.byref(g), CODE[dtype], 0, None) == -1
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16", "float64"])
+def test_conv2d_gemm_loops_as_single_launches(lib, dtype):
+    """conv2d in the reference multiplies per image (ops/ops.c:4761-4770 forward, :4536-4550 input gradient,
+    :4575-4617 weight gradient with materialised transposes and an rp_add per image).  Through rp_matmul_ex each
+    loop is ONE launch: the weight is a broadcast batch operand, transposes are stride swaps, and the weight
+    gradient is a summed problem over the images."""
+    rng = np.random.default_rng(151)
+    n_img, c_out, ck, pix = 6, 40, 72, 96                  # images, output channels, C_in*kH*kW, out_H*out_W
+    w = rand_operand(rng, (1, 1, c_out, ck), dtype, scale=1 / np.sqrt(ck))
+    col = rand_operand(rng, (n_img, 1, ck, pix), dtype)
+    gout = rand_operand(rng, (n_img, 1, c_out, pix), dtype)
+    # forward: out[n] = W . col[n]
+    run_ex(lib, dtype, w, col, oracle=False)
+    # input gradient: dcol[n] = W^T . dout[n]  (W read transposed, no wt_buf)
+    wt = np.ascontiguousarray(np.swapaxes(w, -1, -2))
+    run_ex(lib, dtype, wt, gout, ta=True, oracle=False)
+    # weight gradient: dW = sum_n dout[n] . col[n]^T  (col read transposed, images as summed problems, no col_t_buf)
+    g_r = np.ascontiguousarray(np.swapaxes(gout, 0, 1)); colt_r = np.ascontiguousarray(np.swapaxes(np.swapaxes(col, -1, -2), 0, 1))
+    run_ex(lib, dtype, g_r, colt_r, tb=True, oracle=False)
+    # ... and accumulated into an existing weight gradient in the same epilogue (the reference's rp_add)
+    run_ex(lib, dtype, g_r, colt_r, tb=True, oracle=False, c_init=rand_operand(rng, (1, c_out, ck), dtype))
+
+
 @pytest.mark.parametrize("dtype", ["bfloat16", "float16"])
 def test_unaligned_half_operands_take_the_general_path(lib, dtype):
     rng = np.random.default_rng(29)
