@@ -474,6 +474,7 @@ def main():
         d2h = (rows * n + rows * k + k * n) * es
         e2e = {"value": flops_step / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "h2d_bytes_per_step": int(h2d),
                "d2h_bytes_per_step": int(d2h), "ms_per_step": e2e_ms, "steps": args.e2e_steps,
+               "pcie_gbs_each_way": max(h2d, d2h) / (e2e_ms * 1e-3) / 1e9,
                "api": "rp_matmul_fwdbwd_host (C ABI, pinned host buffers, wall clock around the synchronous call)"}
 
     if rank == 0:
