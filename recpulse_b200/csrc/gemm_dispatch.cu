@@ -216,8 +216,6 @@ int launch_simt_cfg(const RpbProblem& p, void* C, const void* A, const void* B, 
         if (get_scratch(d, bytes, stream, &a.partial)) return -1;
     }
     constexpr int NT = (BM / TM) * (BN / TN);
-    a.act = a.splits == 1 ? p.act : 0;
-    if (a.act) t_act_fused = true;
     RPB_CUDA(rpb_launch(rpb_simt::gemm_kernel<T, Acc, BM, BN, BK, TM, TN>, dim3((unsigned)blocks), dim3(NT), 0, stream, 1, a));
     g_launches++;
     if (a.splits > 1) {
@@ -296,8 +294,6 @@ int launch_dmma(const RpbProblem& p, void* C, const void* A, const void* B, Devi
             blocks = sms;
         }
     }
-    a.act = (a.splits == 1 && a.sk_ctas == 0) ? p.act : 0;
-    if (a.act) t_act_fused = true;
     int rc;
     if (!a_mn && !b_mn) rc = launch_dmma_inst<false, false>(a, blocks, stream);
     else if (!a_mn && b_mn) rc = launch_dmma_inst<false, true>(a, blocks, stream);
@@ -360,8 +356,6 @@ int launch_tf32_cfg(const RpbProblem& p, void* C, const void* A, const void* B, 
     const long long blocks = tiles * a.splits;
     if (blocks > 0x7fffffffLL) return 1;
     if (a.splits > 1 && get_scratch(d, sizeof(float) * (size_t)a.splits * p.batch * p.m * p.n, stream, &a.partial)) return -1;
-    a.act = a.splits == 1 ? p.act : 0;
-    if (a.act) t_act_fused = true;
     int rc;
     if (!a_mn && !b_mn) rc = launch_tf32_inst<BM, BN, WM, WN, false, false>(a, blocks, stream);
     else if (!a_mn && b_mn) rc = launch_tf32_inst<BM, BN, WM, WN, false, true>(a, blocks, stream);
@@ -966,8 +960,9 @@ int run_gates_grad(void* dpre, const void* dy, const void* y, long long rows, in
     return 0;
 }
 
-/* The GEMM, then — when an epilogue non-linearity was asked for and the plan that ran could not apply it in its
- * own epilogue (K slices, balanced fp64 schedule, packed or padded operands) — one element-wise pass over C. */
+/* The GEMM, then — when an epilogue non-linearity was asked for and the plan that ran did not apply it in its own
+ * epilogue (only the tcgen05 kernel's register epilogue does; inlined into the mma.sync kernels it slowed the
+ * launch-bound MLP / LSTM steps by a sixth) — one element-wise pass over C. */
 int run_gemm(const RpbProblem& p, void* C, const void* A, const void* B, int device_id, cudaStream_t stream) {
     if (p.act && (p.act != 1 || p.n % 4 != 0)) {
         fprintf(stderr, "recpulse_b200: epilogue %d needs n to be a multiple of 4 (n=%d)\n", p.act, p.n);

@@ -231,7 +231,6 @@ gemm_kernel(const rpb_simt::Args p)
                         double* dst = C + (long long)r * p.c_row + c + e;
                         if (p.bias) v += reinterpret_cast<const double*>(p.bias)[c + e];
                         if (p.accumulate) v += *dst;
-                        if (p.act) v = rpb_gate_act(v, c + e, p.n >> 2);
                         *dst = v;
                     }
                 }

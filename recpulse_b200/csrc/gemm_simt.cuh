@@ -45,7 +45,6 @@ struct Args {
     int sk_ctas = 0;                /* 0 = one CTA per tile (and K slice) */
     long long sk_units = 0;         /* tiles * k_iters */
     double* sk_scratch = nullptr;   /* [sk_ctas - 1][2][128 x 128] partial tiles of the tiles cut between two CTAs */
-    int act = 0;                    /* 1: LSTM gate non-linearities on the finished sum (direct epilogues only) */
 };
 
 template <typename T, typename Acc, int BM, int BN, int BK, int TM, int TN>
@@ -148,7 +147,6 @@ gemm_kernel(const Args p)
                 Acc v = acc[i][j];
                 if (p.bias) v += widen<Acc, T>(reinterpret_cast<const T*>(p.bias)[gj]);
                 if (p.accumulate) v += widen<Acc, T>(*dst);
-                if (p.act) v = rpb_gate_act(v, gj, p.n >> 2);
                 *dst = narrow<T, Acc>(v);
             }
         }

@@ -291,8 +291,8 @@ def test_every_tile_plan_gives_the_same_product(lib, dtype, plan, monkeypatch):
 
 @pytest.mark.parametrize("dtype", ["float32", "float64", "float16", "bfloat16"])
 def test_gate_epilogue_in_every_kernel_family(lib, dtype):
-    """RpbGemm.epilogue = LSTM gates: applied inside the epilogue of the plans that write C directly (general-stride,
-    mma.sync fp32 / fp64, tcgen05 register epilogue) and by one pass over C behind the others (K slices, balanced fp64
+    """RpbGemm.epilogue = LSTM gates: applied inside the tcgen05 kernel's register epilogue when that writes C directly,
+    and by one pass over C behind every other plan (mma.sync and general-stride kernels, K slices, balanced fp64
     schedule, packed operands); always after bias and "C += AB"."""
     rng = np.random.default_rng(131)
     cases = [((64, 512, 2048), None), ((128, 64, 1024), None), ((40, 36, 24), None), ((64, 4096, 64), None),
