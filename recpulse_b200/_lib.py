@@ -74,6 +74,8 @@ SYMBOLS = {
     "rp_matmul_noalloc": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
                                     C.c_void_p, C.POINTER(C.c_int)]),
     "rpb_last_kernel": (C.c_int, []),
+    "rpb_umma_plan": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_int),
+                                C.POINTER(C.c_int), C.POINTER(C.c_int)]),
     "rpb_launch_count": (C.c_ulonglong, []),
     "rpb_force_kernel": (None, [C.c_int]),
     "rpb_device_status": (C.c_int, [C.c_int]),

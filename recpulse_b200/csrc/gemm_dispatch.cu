@@ -1181,6 +1181,19 @@ int rp_matmul_host(void* C, const void* A, const void* B, int m, int k, int n, D
     return rc;
 }
 
+int rpb_umma_plan(int m, int n, int k, int reduce, int batch, DType dtype, int sms, int* rows_of_b, int* k_slices,
+                  int* cta_pair) {
+    const size_t es = rpb_dtype_size((int)dtype);
+    if (m <= 0 || n <= 0 || k <= 0 || reduce <= 0 || batch <= 0 || sms < 2 || (es != 2 && es != 4)) return -1;
+    const int bk = 128 / (int)es;
+    const long long k_iters = (long long)((k + bk - 1) / bk) * reduce;
+    if (k_iters > 0x7fffffffLL) return -1;
+    const TilePlan tp = plan_tiles(m, n, batch, (int)k_iters, sms, es == 4);
+    if (rows_of_b) *rows_of_b = tp.bn;
+    if (k_slices) *k_slices = tp.splits;
+    if (cta_pair) *cta_pair = tp.pair;
+    return 0;
+}
 int rpb_last_kernel(void) { return t_last_kernel; }
 unsigned long long rpb_launch_count(void) { return g_launches.load(); }
 void rpb_force_kernel(int family) { g_force.store(family < 0 ? 0 : family); }

@@ -84,3 +84,29 @@ def test_op_matmul_rejects_bad_operands_on_host_structs():
     assert not lib.op_matmul(C.byref(a), C.byref(b))           # 1-D operand
     a, b = host_struct([2, 3]), host_struct([3, 5])
     assert not lib.op_matmul(C.byref(a), C.byref(b))           # host tensors: no CPU path here
+
+
+def test_tile_plan_model_on_the_host():
+    """rpb_umma_plan is pure host arithmetic: the decisions the measurements behind the model call for."""
+    import ctypes as C
+    from recpulse_b200 import _lib
+    lib = _lib.load()
+
+    def plan(m, n, k, dtype=3, reduce=1, batch=1, sms=148):          # 3 = DTYPE_BFLOAT16, 0 = DTYPE_FLOAT32
+        bn, sl, pr = C.c_int(), C.c_int(), C.c_int()
+        assert lib.rpb_umma_plan(m, n, k, reduce, batch, dtype, sms, C.byref(bn), C.byref(sl), C.byref(pr)) == 0
+        return bn.value, sl.value, pr.value
+
+    assert plan(65536, 8192, 8192) == (128, 1, 1)        # the row-sharded workload: 256 x 256 pair tiles, no K slices
+    assert plan(8192, 8192, 65536) == (128, 1, 1)        # its dB
+    assert plan(8192, 8192, 8192, sms=132) == (128, 1, 1)    # with SMs left to a collective
+    bn, sl, pr = plan(1024, 1024, 1024)                  # few tiles, short K: narrow one-CTA tiles, un-split
+    assert (sl, pr) == (1, 0) and bn in (64, 128)
+    assert plan(4096, 4096, 64) == (256, 1, 0)           # K of one block: the pair's hand-offs do not pay
+    bn, sl, pr = plan(64, 512, 32768)                    # skinny weight gradient: K slices fill the SMs
+    assert sl >= 8 and pr == 0
+    bn, sl, pr = plan(128, 8192, 4096)                   # one row of tiles: no pair (m < 256)
+    assert pr == 0
+    assert plan(65536, 2048, 512, dtype=0)[2] == 1       # fp32 (3xTF32) large output: pair tiles
+    assert lib.rpb_umma_plan(0, 8, 8, 1, 1, 3, 148, None, None, None) == -1
+    assert lib.rpb_umma_plan(8, 8, 8, 1, 1, 1, 148, None, None, None) == -1      # float64 has no tcgen05 plan
