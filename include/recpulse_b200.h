@@ -95,7 +95,11 @@ int rp_matmul(void* C, const void* A, const void* B, int m, int k, int n, DType 
  * additive: strided / transposed 2-D views are read in place (no contiguous
  * copy), and operands with ndim > 2 are accepted as batched matrices whose
  * leading dimensions broadcast NumPy-style.  The result is a new contiguous
- * tensor, refcount 1, owns_data, data from cudaMalloc on the operands' device. */
+ * tensor, refcount 1, owns_data.  Its data comes from the device's default stream-ordered memory
+ * pool (cudaMallocAsync), which RecPulse's free_tensor may release with plain cudaFree; the
+ * library raises that pool's release threshold so that freed blocks are reused instead of returned
+ * to the driver -- a process-wide setting.  RPB_POOL=0 in the environment keeps the pool untouched
+ * and allocates with cudaMalloc exactly like zeros_device_tensor (core/tensor_device.cu:44-46). */
 Tensor* op_matmul(Tensor* a, Tensor* b);
 
 /* Replaces backward_matmul_fn (ops/ops.c:6759-6814): dA = dC . B^T and
@@ -117,9 +121,10 @@ void backward_matmul_fn(GradFn* self, Tensor* grad_output);
 Tensor* op_linear(Tensor* x, Tensor* w, Tensor* bias);
 void backward_linear_fn(GradFn* self, Tensor* grad_output);
 
-/* y = x . w + h . u (+ bias) as ONE node: the gate pre-activations of an LSTM / GRU cell, which RecPulse
- * builds from two op_matmul nodes and an op_add (recpulse/module.py:289, 334-335).  The second product is
- * accumulated into the output inside the GEMM epilogue.  Shapes as for op_linear, both products must have
+/* y = x . w + h . u (+ bias) as ONE node: the gate pre-activations of an LSTM cell, which RecPulse
+ * builds from two op_matmul nodes and an op_add (recpulse/module.py:289).  (A GRU cell keeps the two products
+ * apart -- its candidate gate needs h . u on its own -- and has its own node, op_gru_cell.)  The second
+ * product is accumulated into the output inside the GEMM epilogue.  Shapes as for op_linear, both products must have
  * the same result shape; bias may be NULL.  Backward gives all four matmul gradients and the bias gradient. */
 Tensor* op_linear2(Tensor* x, Tensor* w, Tensor* h, Tensor* u, Tensor* bias);
 void backward_linear2_fn(GradFn* self, Tensor* grad_output);
@@ -166,6 +171,9 @@ typedef struct {
     int epilogue;                   /* 0: none; 1 (RPB_EPILOGUE_LSTM_GATES): after bias and "+= C", columns   */
                                     /* [n/2, 3n/4) go through tanh and the others through 1 / (1 + exp(-x))    */
                                     /* before the one rounding; n must be a multiple of 4                      */
+    int c_float32;                  /* 1: float16 / bfloat16 operands, but C receives the UNROUNDED float32 sums */
+                                    /* (packed [batch][m][n], c_row == n; no bias, accumulation or epilogue):   */
+                                    /* partial gradients that are summed across GPUs before their one rounding  */
 } RpbGemm;
 #define RPB_EPILOGUE_LSTM_GATES 1
 
@@ -207,14 +215,99 @@ int rpb_release_host_pipeline(int device_id);
  *     (roughly m x n <= 2M elements for short K, less for long K).  Pointers 16-byte aligned, k and n
  *     multiples of 8.  Every GPU that loads the library holds the 16 MiB until the process exits.
  *   - The first call on a device looks up the device addresses of the built-in buffers; make that
- *     first call before starting any stream capture on that device.
+ *     first call before starting any stream capture on that device.  Under CUDA's lazy module loading
+ *     that first call (per device, and the first use of each dtype / tile width) is also what loads
+ *     the kernel image and reserves the 16 MiB array, so it can itself fail for lack of memory if the
+ *     caller's pool already holds the whole device: make it BEFORE handing memory to the pool.  Later
+ *     calls leave the device's free memory untouched.
  *   - All calls on a device share the one array: two calls that overlap on the GPU (different
  *     streams, or different threads) race on it.  Serialise them.
  *   - Runs on `stream` (NULL = legacy default stream).  With kernel_status == NULL it returns once the
  *     work is queued.  With a pointer it waits for the result and stores the kernel's status word
- *     (0 = ok; non-zero = a bounded wait inside the kernel ran out, result invalid, return -1). */
+ *     (0 = ok; non-zero = a bounded wait inside the kernel ran out, result invalid, return -1).  The
+ *     word is cleared at the start of every call, so kernel_status is the only way to learn of such
+ *     a failure: a caller that passes NULL and queues another call loses it. */
 int rp_matmul_noalloc(void* C, const void* A, const void* B, int m, int k, int n, DType dtype,
                       int device_id, void* stream, int* kernel_status);
+
+/* ---- additive: the path sharded over the GPUs of one box ---------------------
+ * RecPulse's multi-GPU primitive is the whole-tensor peer copy tensor_copy_device
+ * (core/tensor_device.cu:295-372, cudaDeviceEnablePeerAccess + cudaMemcpyPeer, reached from
+ * tensor_to, core/tensor.c:82-144).  These entry points are what that layer needs for the matmul
+ * path: rows of A (the batch of a batched product, folded into the rows) are split over the ranks,
+ * B is replicated once into every GPU's own memory, forward and dA need no communication and the
+ * dB partials are reduced over NVLink (NCCL) while the dA GEMM runs.  One RpbShard per rank; a rank
+ * is a process or a thread that owns one GPU.  NCCL is located at run time (the process's own
+ * libnccl.so.2, else the system's; RPB_NCCL_LIB overrides).  All calls are asynchronous on `stream`
+ * unless stated otherwise; collectives must be issued by every rank in the same order. */
+typedef struct RpbShard RpbShard;
+#define RPB_SHARD_ID_BYTES 128
+#define RPB_SHARD_SLICE_ONLY 1      /* backward flag: leave dB reduce-scattered (no all-gather) */
+
+/* Rank 0 makes the 128-byte rendezvous id and hands it to the other ranks by any means (a file, a
+ * pipe, MPI, a torch.distributed store ...). */
+int rpb_shard_unique_id(void* id_out);
+/* Joins the communicator of `world` ranks (collective: returns once every rank has called it).
+ * world == 1 needs no id and no NCCL.  NULL on error. */
+RpbShard* rpb_shard_create(const void* unique_id, int rank, int world, int device_id);
+void rpb_shard_destroy(RpbShard* shard);
+int rpb_shard_rank(const RpbShard* shard);
+int rpb_shard_world(const RpbShard* shard);
+/* comm_sms: SMs the dA GEMM leaves free while the dB reduction is in flight (default 16; the GEMM
+ * kernels are persistent and would otherwise keep the collective's thread blocks waiting).
+ * db_wire: 0 (default) = the float16 / bfloat16 dB partials cross NVLink as float32 sums and are
+ * rounded once after the reduction; 1 = all-reduce in the operand type (half the bytes, one extra
+ * rounding per reduction step). */
+int rpb_shard_configure(RpbShard* shard, int comm_sms, int db_wire);
+/* [begin, end) of the rows rank `rank` owns: an even split, the remainder to the first ranks. */
+void rpb_shard_rows(long long rows, int world, int rank, long long* begin, long long* end);
+/* Which elements [begin, end) of the k x n gradient dB rank `rank` holds after
+ * rp_matmul_rowsharded_backward(..., flags, ...): its slice when RPB_SHARD_SLICE_ONLY applies (see there),
+ * else everything.  Pure arithmetic.  0 / -1. */
+int rpb_shard_db_slice_of(int k, int n, DType dtype, int world, int rank, int db_wire, int flags, long long* begin,
+                          long long* end);
+/* Collectives issued by this library since load (all shards of the process). */
+unsigned long long rpb_shard_collective_count(void);
+
+/* Replicates `bytes` bytes at `buf` from rank `root` into every rank's own buffer (ncclBroadcast):
+ * the once-per-weight copy of B that tensor_copy_device does with cudaMemcpyPeer. */
+int rp_shard_replicate(RpbShard* shard, void* buf, size_t bytes, int root, void* stream);
+/* C_rows[rows, n] = A_rows[rows, k] . B[k, n] on this rank's rows; no communication. */
+int rp_matmul_rowsharded_forward(RpbShard* shard, void* C_rows, const void* A_rows, const void* B, long long rows,
+                                 int k, int n, DType dtype, void* stream);
+/* dB[k, n] = sum over ranks of A_rows^T . dC_rows, then dA_rows[rows, k] = dC_rows . B^T.  The
+ * partial dB GEMM is issued first and its reduction overlaps the dA GEMM; both are complete in
+ * `stream` order when the call's work is.  Either of dA_rows / dB may be NULL (all ranks alike).
+ * float16 / bfloat16: partial sums are reduced in float32 and rounded once, so dB has the same
+ * single rounding as on one GPU.  With RPB_SHARD_SLICE_ONLY, and k * n divisible by the ranks
+ * (in 16-byte units, dB of at least 1 MiB in float32), only this rank's k * n / world elements of
+ * dB are written. */
+int rp_matmul_rowsharded_backward(RpbShard* shard, void* dA_rows, void* dB, const void* A_rows, const void* B,
+                                  const void* dC_rows, long long rows, int k, int n, DType dtype, int flags, void* stream);
+/* All-gathers C for callers that need the whole output on every GPU: C_full[world * rows, n] from
+ * every rank's C_rows[rows, n] (the same `rows` on every rank). */
+int rp_matmul_gather_rows(RpbShard* shard, void* C_full, const void* C_rows, long long rows, int n, DType dtype,
+                          void* stream);
+/* rp_matmul_fwdbwd_host for this rank's rows of a sharded product, from HOST buffers, synchronous.
+ * B is read from rank 0's host buffer only (one upload per box, then NVLink; other ranks may pass
+ * NULL), A_rows / dC_rows stream in chunks as in rp_matmul_fwdbwd_host, dB is reduced on the devices
+ * and each rank copies back only its slice: elements [*db_begin, *db_end) of the k x n matrix, at
+ * that offset of `dB` (the whole matrix when it cannot be sliced evenly). */
+int rp_matmul_rowsharded_fwdbwd_host(RpbShard* shard, void* C_rows, void* dA_rows, void* dB, const void* A_rows,
+                                     const void* B, const void* dC_rows, long long rows, int k, int n, DType dtype,
+                                     int chunk_rows, long long* db_begin, long long* db_end);
+
+/* ---- additive: stream-ordered execution of the nodes -------------------------
+ * RecPulse ends every device op with a device synchronisation (core/cuda_helpers.cu:14-26).  By
+ * default the node entry points above (op_matmul ... backward_*_fn) keep that contract on the legacy
+ * default stream.  rpb_node_stream changes it for the CALLING THREAD: the nodes then run on `stream`,
+ * take outputs and gradients from the memory pool in that stream's order, release temporaries in
+ * stream order, and with synchronise == 0 return as soon as their work is queued.  With stream == NULL
+ * and synchronise == 0 everything stays ordered with RecPulse's own (legacy-stream) kernels and the
+ * host simply stops waiting after every matmul.  rpb_node_synchronize waits for the thread's node
+ * stream and reports a kernel that gave up (0 / -1).  rpb_node_stream(NULL, 1) restores the default. */
+void rpb_node_stream(void* stream, int synchronise);
+int rpb_node_synchronize(int device_id);
 
 /* ---- additive: diagnostics and tuning --------------------------------------*/
 
@@ -245,11 +338,22 @@ void rpb_force_kernel(int family);
 int rpb_device_status(int device_id);
 /* Library version string. */
 const char* rpb_version(void);
+/* The per-device scratch buffer (K-slice partial sums, column-sum partials) grows on demand, which frees
+ * and reallocates it.  A CUDA graph captured while the buffer was in use holds its address, so after such
+ * a capture the buffer can no longer grow: a call that needs more fails with -1.  rpb_scratch_reserve sizes
+ * it up front (call before capturing); rpb_scratch_reset frees it and lifts the pin once every graph that
+ * used it has been destroyed.  Eager calls and graph replays that use the scratch on one device must not
+ * overlap in time.  Both synchronise the device. */
+int rpb_scratch_reserve(int device_id, size_t bytes);
+int rpb_scratch_reset(int device_id);
+/* cudaMemGetInfo of `device_id` (diagnostics: lets a caller check that a call allocated nothing). */
+int rpb_mem_info(int device_id, size_t* free_bytes, size_t* total_bytes);
 
 /* ---- additive: minimal tensor helpers for C callers without RecPulse --------
  * They follow RecPulse's allocation conventions (struct, shape, strides and Meta from
- * malloc/calloc, device data from cudaMalloc), so tensors made here can be released by
- * RecPulse's free_tensor and vice versa. */
+ * malloc/calloc, device data releasable with cudaFree: from the stream-ordered pool, or from
+ * cudaMalloc with RPB_POOL=0), so tensors made here can be released by RecPulse's free_tensor
+ * and vice versa. */
 Tensor* rpb_tensor_from_host(const void* host_data, DType dtype, int ndim, const int* shape,
                              int device_id, bool requires_grad);
 Tensor* rpb_tensor_empty(DType dtype, int ndim, const int* shape, int device_id);
@@ -259,6 +363,10 @@ Tensor* rpb_tensor_view(Tensor* base, int ndim, const int* shape, const int* str
                         size_t offset_elems);
 /* Copies a (possibly strided) tensor to a packed host buffer of t->size elements. */
 int rpb_tensor_to_host(const Tensor* t, void* host_out);
+/* Overwrites a packed device tensor's values from a packed host buffer, keeping its device buffer. */
+int rpb_tensor_write_host(Tensor* t, const void* host_data);
+/* Releases t's accumulated gradient and clears the pointer. */
+void rpb_tensor_zero_grad(Tensor* t);
 /* Drops one reference; frees at zero (data, grad, grad_fn with its retained inputs, base). */
 void rpb_tensor_release(Tensor* t);
 /* Runs the backward function recorded on `out` with upstream gradient `grad_output`

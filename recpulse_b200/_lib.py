@@ -44,7 +44,7 @@ class RpbGemm(C.Structure):
     _fields_ = [("m", C.c_int), ("n", C.c_int), ("k", C.c_int), ("batch", C.c_int), ("reduce", C.c_int),
                 ("a_row", C.c_longlong), ("a_col", C.c_longlong), ("a_batch", C.c_longlong), ("a_reduce", C.c_longlong),
                 ("b_row", C.c_longlong), ("b_col", C.c_longlong), ("b_batch", C.c_longlong), ("b_reduce", C.c_longlong),
-                ("c_row", C.c_longlong), ("c_batch", C.c_longlong), ("accumulate", C.c_int), ("bias", C.c_void_p), ("max_sms", C.c_int), ("epilogue", C.c_int)]
+                ("c_row", C.c_longlong), ("c_batch", C.c_longlong), ("accumulate", C.c_int), ("bias", C.c_void_p), ("max_sms", C.c_int), ("epilogue", C.c_int), ("c_float32", C.c_int)]
 
 
 # every symbol include/recpulse_b200.h declares: name -> (restype, argtypes)
@@ -84,8 +84,34 @@ SYMBOLS = {
     "rpb_tensor_empty": (TP, [C.c_int, C.c_int, C.POINTER(C.c_int), C.c_int]),
     "rpb_tensor_view": (TP, [TP, C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_int), C.c_size_t]),
     "rpb_tensor_to_host": (C.c_int, [TP, C.c_void_p]),
+    "rpb_tensor_write_host": (C.c_int, [TP, C.c_void_p]),
+    "rpb_tensor_zero_grad": (None, [TP]),
     "rpb_tensor_release": (None, [TP]),
     "rpb_backward_node": (C.c_int, [TP, TP]),
+    "rpb_shard_unique_id": (C.c_int, [C.c_void_p]),
+    "rpb_shard_create": (C.c_void_p, [C.c_void_p, C.c_int, C.c_int, C.c_int]),
+    "rpb_shard_destroy": (None, [C.c_void_p]),
+    "rpb_shard_rank": (C.c_int, [C.c_void_p]),
+    "rpb_shard_world": (C.c_int, [C.c_void_p]),
+    "rpb_shard_configure": (C.c_int, [C.c_void_p, C.c_int, C.c_int]),
+    "rpb_shard_rows": (None, [C.c_longlong, C.c_int, C.c_int, C.POINTER(C.c_longlong), C.POINTER(C.c_longlong)]),
+    "rpb_shard_collective_count": (C.c_ulonglong, []),
+    "rpb_shard_db_slice_of": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_longlong),
+                                        C.POINTER(C.c_longlong)]),
+    "rp_shard_replicate": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_int, C.c_void_p]),
+    "rp_matmul_rowsharded_forward": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_longlong, C.c_int, C.c_int,
+                                               C.c_int, C.c_void_p]),
+    "rp_matmul_rowsharded_backward": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                                C.c_longlong, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]),
+    "rp_matmul_gather_rows": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_longlong, C.c_int, C.c_int, C.c_void_p]),
+    "rp_matmul_rowsharded_fwdbwd_host": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                                   C.c_void_p, C.c_longlong, C.c_int, C.c_int, C.c_int, C.c_int,
+                                                   C.POINTER(C.c_longlong), C.POINTER(C.c_longlong)]),
+    "rpb_node_stream": (None, [C.c_void_p, C.c_int]),
+    "rpb_node_synchronize": (C.c_int, [C.c_int]),
+    "rpb_scratch_reserve": (C.c_int, [C.c_int, C.c_size_t]),
+    "rpb_scratch_reset": (C.c_int, [C.c_int]),
+    "rpb_mem_info": (C.c_int, [C.c_int, C.POINTER(C.c_size_t), C.POINTER(C.c_size_t)]),
 }
 
 _LIB = None

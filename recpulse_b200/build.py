@@ -3,29 +3,41 @@
     python -m recpulse_b200.build [--verbose]
 
 The library has no Python or PyTorch dependency; it links the CUDA runtime
-statically and resolves the driver's tensor-map encoder at run time.
+statically, resolves the driver's tensor-map encoder at run time and looks NCCL up
+with dlopen only when a sharded entry point is first used.  Translation units are
+compiled side by side (one nvcc per source) and linked at the end.
 """
 from __future__ import annotations
 
+import glob
 import os
 import shutil
 import subprocess
 import sys
+from concurrent.futures import ThreadPoolExecutor
 
 PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, "csrc")
+OBJ = os.path.join(PKG, "_obj")
 LIB = os.path.join(PKG, "librecpulse_b200.so")
-SOURCES = ["gemm_dispatch.cu", "host_pipeline.cu", "op_matmul.c"]
-HEADERS = ["gemm_simt.cuh", "gemm_umma.cuh", "gemm_dmma.cuh", "gemm_tf32x3.cuh", "reduce_cols.cuh", "rpb_common.h",
-           os.path.join("..", "..", "include", "recpulse_b200.h")]
+HEADER = os.path.join(PKG, "..", "include", "recpulse_b200.h")
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
+
+
+def _sources() -> list[str]:
+    return sorted(glob.glob(os.path.join(CSRC, "*.cu")) + glob.glob(os.path.join(CSRC, "*.c")))
+
+
+def _inputs() -> list[str]:
+    """Everything a translation unit can include: any change rebuilds."""
+    return _sources() + sorted(glob.glob(os.path.join(CSRC, "*.cuh")) + glob.glob(os.path.join(CSRC, "*.h"))) + [HEADER]
 
 
 def _stale() -> bool:
     if not os.path.exists(LIB):
         return True
     built = os.path.getmtime(LIB)
-    return any(os.path.getmtime(os.path.join(CSRC, f)) > built for f in SOURCES + HEADERS)
+    return any(os.path.getmtime(f) > built for f in _inputs())
 
 
 def build(force: bool = False, verbose: bool = False) -> str:
@@ -37,12 +49,23 @@ def build(force: bool = False, verbose: bool = False) -> str:
         if os.path.exists(LIB):
             return LIB          # no compiler on this box: keep the prebuilt library
         raise RuntimeError("nvcc not found and no prebuilt librecpulse_b200.so")
-    cmd = [nvcc, *ARCH, "-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC,-Wall", "-shared",
-           "-o", LIB, *[os.path.join(CSRC, s) for s in SOURCES], "-ldl"]
-    if verbose:
-        cmd.insert(1, "-Xptxas=-v")
-        print(" ".join(cmd))
-    subprocess.run(cmd, check=True)
+    os.makedirs(OBJ, exist_ok=True)
+    headers_time = max(os.path.getmtime(f) for f in _inputs() if not f.endswith((".cu", ".c")))
+
+    def compile_one(src: str) -> str:
+        obj = os.path.join(OBJ, os.path.basename(src) + ".o")
+        if not force and os.path.exists(obj) and os.path.getmtime(obj) > max(os.path.getmtime(src), headers_time):
+            return obj
+        cmd = [nvcc, *ARCH, "-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC,-Wall", "-c", src, "-o", obj]
+        if verbose:
+            cmd.insert(1, "-Xptxas=-v")
+            print(" ".join(cmd))
+        subprocess.run(cmd, check=True)
+        return obj
+
+    with ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 1)) as pool:
+        objs = list(pool.map(compile_one, _sources()))
+    subprocess.run([nvcc, *ARCH, "-shared", "-o", LIB, *objs, "-ldl"], check=True)
     return LIB
 
 

@@ -26,7 +26,7 @@ namespace {
 constexpr int MAX_DEVICES = 64;
 
 struct DeviceState {
-    bool ready = false;
+    std::atomic<bool> ready{false};
     int sm_count = 0;
     int cc_major = 0;
     void* scratch = nullptr;
@@ -34,8 +34,16 @@ struct DeviceState {
     cudaEvent_t scratch_free = nullptr;   /* recorded after the last reader of scratch */
     cudaStream_t scratch_stream = nullptr;
     bool scratch_used = false;
-    int* status = nullptr;
+    bool scratch_pinned = false;          /* handed out inside a stream capture: a graph holds its address */
+    int* status = nullptr;                /* this device's word of g_status_words (mapped host memory) */
+    std::mutex mu;                        /* guards the scratch fields: per device, because growing the scratch waits
+                                           * for this device, whose work may in turn wait for another thread's GPU */
 };
+
+/* Kernel status words, one per device, in page-locked host memory that every device can address (the host
+ * pointer is the device pointer under unified addressing).  A tcgen05 kernel whose bounded wait ran out
+ * stores a code there; the host reads the word after the synchronisation it does anyway, without a copy. */
+int* g_status_words = nullptr;
 
 DeviceState g_dev[MAX_DEVICES];
 std::mutex g_mutex;
@@ -112,15 +120,18 @@ int device_state(int device_id, DeviceState** out) {
         return -1;
     }
     DeviceState& d = g_dev[device_id];
-    if (!d.ready) {
+    if (!d.ready.load(std::memory_order_acquire)) {
         std::lock_guard<std::mutex> lock(g_mutex);
-        if (!d.ready) {
-            cudaDeviceProp prop;
-            RPB_CUDA(cudaGetDeviceProperties(&prop, device_id));
-            d.sm_count = prop.multiProcessorCount;
-            d.cc_major = prop.major;
-            RPB_CUDA(cudaMalloc(&d.status, sizeof(int)));
-            RPB_CUDA(cudaMemset(d.status, 0, sizeof(int)));
+        if (!d.ready.load(std::memory_order_relaxed)) {
+            RPB_CUDA(cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, device_id));
+            RPB_CUDA(cudaDeviceGetAttribute(&d.cc_major, cudaDevAttrComputeCapabilityMajor, device_id));
+            if (!g_status_words) {
+                void* w = nullptr;
+                RPB_CUDA(cudaHostAlloc(&w, sizeof(int) * MAX_DEVICES, cudaHostAllocPortable | cudaHostAllocMapped));
+                memset(w, 0, sizeof(int) * MAX_DEVICES);
+                g_status_words = reinterpret_cast<int*>(w);
+            }
+            d.status = g_status_words + device_id;
             RPB_CUDA(cudaEventCreateWithFlags(&d.scratch_free, cudaEventDisableTiming));
             {   /* temporaries for packed operands come from the stream-ordered pool: let it keep freed blocks */
                 const char* e = getenv("RPB_POOL");
@@ -140,7 +151,7 @@ int device_state(int device_id, DeviceState** out) {
                 }
                 g_encode = reinterpret_cast<EncodeTiledFn>(fn);
             }
-            d.ready = true;
+            d.ready.store(true, std::memory_order_release);
         }
     }
     *out = &d;
@@ -155,12 +166,20 @@ bool capturing(cudaStream_t stream) {
 }
 
 int get_scratch(DeviceState* d, size_t bytes, cudaStream_t stream, void** out) {
-    std::lock_guard<std::mutex> lock(g_mutex);
+    std::lock_guard<std::mutex> lock(d->mu);
     const bool cap = capturing(stream);
     if (bytes > d->scratch_bytes) {
         if (cap) {
             fprintf(stderr, "recpulse_b200: the K-split scratch would have to grow during stream capture; run the same "
-                            "shapes once before capturing\n");
+                            "shapes once before capturing (or size it with rpb_scratch_reserve)\n");
+            return -1;
+        }
+        if (d->scratch_pinned) {
+            /* a captured graph has this buffer's address in its kernel arguments and tensor maps: freeing it
+             * would make the next replay write freed memory */
+            fprintf(stderr, "recpulse_b200: the K-split scratch (%zu bytes) was used inside a stream capture and cannot "
+                            "grow to %zu bytes any more; call rpb_scratch_reserve before capturing, or rpb_scratch_reset "
+                            "once every graph that used it is destroyed\n", d->scratch_bytes, bytes);
             return -1;
         }
         if (d->scratch) RPB_CUDA(cudaFree(d->scratch));       /* synchronises the device */
@@ -169,6 +188,7 @@ int get_scratch(DeviceState* d, size_t bytes, cudaStream_t stream, void** out) {
         RPB_CUDA(cudaMalloc(&d->scratch, want));
         d->scratch_bytes = want;
     }
+    if (cap) d->scratch_pinned = true;
     /* inside a capture the graph's own edges order the users of the scratch; the guard event stays out of it */
     if (!cap && d->scratch_used && d->scratch_stream != stream)
         RPB_CUDA(cudaStreamWaitEvent(stream, d->scratch_free, 0));
@@ -176,7 +196,7 @@ int get_scratch(DeviceState* d, size_t bytes, cudaStream_t stream, void** out) {
     return 0;
 }
 int release_scratch(DeviceState* d, cudaStream_t stream) {
-    std::lock_guard<std::mutex> lock(g_mutex);
+    std::lock_guard<std::mutex> lock(d->mu);
     if (capturing(stream)) return 0;
     RPB_CUDA(cudaEventRecord(d->scratch_free, stream));
     d->scratch_stream = stream;
@@ -662,7 +682,14 @@ int launch_umma(const RpbProblem& p, void* C, const void* A, const void* B, Devi
      * epilogue handles "C += AB" and odd alignments */
     CUtensorMap mc = ma;
     a.tma_store = 0;
-    if (a.splits > 1) {
+    a.c_f32 = (p.c_f32 && a.splits == 1) ? 1 : 0;
+    if (a.c_f32) {
+        /* unrounded fp32 output of 16-bit operands: written like a K slice, straight into the caller's buffer */
+        a.partial = reinterpret_cast<float*>(C);
+        if (p.n % 4 == 0 && (reinterpret_cast<uintptr_t>(C) & 15u) == 0 &&
+            encode_store_map(&mc, C, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, p.n, p.m, p.batch, p.n, (long long)p.m * p.n, 32) == 0)
+            a.tma_store = 1;
+    } else if (a.splits > 1) {
         if (p.n % 4 == 0 &&
             encode_store_map(&mc, a.partial, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, p.n, p.m, (long long)a.splits * p.batch,
                              p.n, (long long)p.m * p.n, 32) == 0)
@@ -686,7 +713,7 @@ int launch_umma(const RpbProblem& p, void* C, const void* A, const void* B, Devi
         const long long units = pair ? sms / 2 : sms;
         const long long rem = units > 0 ? tiles % units : 0;
         /* the extra reduction launch costs ~4 us: measured break-even at about 96 K blocks per tile */
-        if (env && a.splits == 1 && p.batch == 1 && a.tma_store == 1 && tiles > units && rem > 0 && rem * 2 <= units &&
+        if (env && a.splits == 1 && !p.c_f32 && p.batch == 1 && a.tma_store == 1 && tiles > units && rem > 0 && rem * 2 <= units &&
             a.k_iters >= (env > 1 ? 16 : 96)) {
             long long ts = units / rem;
             if (ts > 4) ts = 4;
@@ -727,7 +754,13 @@ int launch_umma(const RpbProblem& p, void* C, const void* A, const void* B, Devi
         RPB_CUDA(cudaGetLastError());
         if (release_scratch(d, stream)) return -1;
     }
-    if (a.splits > 1) {
+    if (a.splits > 1 && p.c_f32) {
+        rpb_simt::launch_splitk_reduce<float, float>(a.partial, reinterpret_cast<float*>(C), a.splits, p.batch, p.m, p.n, p.n,
+                                                     (long long)p.m * p.n, 0, nullptr, d->sm_count, stream);
+        g_launches++;
+        RPB_CUDA(cudaGetLastError());
+        if (release_scratch(d, stream)) return -1;
+    } else if (a.splits > 1) {
         rpb_simt::launch_splitk_reduce<T, float>(a.partial, reinterpret_cast<T*>(C), a.splits, p.batch, p.m, p.n, p.c_row,
                                                  p.c_batch, p.accumulate, p.bias, d->sm_count, stream);
         g_launches++;
@@ -818,7 +851,7 @@ int launch_umma_packed(const RpbProblem& p, void* C, const void* A, const void* 
         const int nr = (p.reduce > 1 && reduce_s != 0) ? p.reduce : 1;
         const size_t mat = (size_t)outer * inner_pad;
         const size_t elems = (size_t)nb * nr * mat;
-        RPB_CUDA(cudaMallocAsync(&tmp[which], elems * ES, stream));
+        RPB_CUDA(cudaMallocAsync(&tmp[which], elems * ES, stream));     /* released by the caller on every exit */
         long long blocks = (long long)((elems + 255) / 256);
         if (blocks > d->sm_count * 16) blocks = d->sm_count * 16;
         RPB_CUDA(rpb_launch(pack_operand_kernel<T>, dim3((unsigned)blocks), dim3(256), 0, stream, 1, reinterpret_cast<T*>(tmp[which]),
@@ -838,20 +871,29 @@ int launch_umma_packed(const RpbProblem& p, void* C, const void* A, const void* 
     void* C2 = C;
     const int n_pad = (p.n + AL - 1) / AL * AL;
     if (!rc && c_odd) {
-        RPB_CUDA(cudaMallocAsync(&tmp[2], (size_t)p.batch * p.m * n_pad * ES, stream));
-        C2 = tmp[2];
-        q.c_row = n_pad; q.c_batch = (long long)p.m * n_pad;
+        if (cudaMallocAsync(&tmp[2], (size_t)p.batch * p.m * n_pad * ES, stream) != cudaSuccess) {
+            fprintf(stderr, "recpulse_b200: no memory for the padded output: %s\n", cudaGetErrorString(cudaGetLastError()));
+            rc = -1;
+        } else {
+            C2 = tmp[2];
+            q.c_row = n_pad; q.c_batch = (long long)p.m * n_pad;
+        }
     }
     if (!rc) rc = launch_umma<T>(q, C2, A2, B2, d, stream);
     if (!rc && c_odd) {
         const long long elems = (long long)p.batch * p.m * p.n;
         long long blocks = (elems + 255) / 256;
         if (blocks > d->sm_count * 16) blocks = d->sm_count * 16;
-        RPB_CUDA(rpb_launch(unpack_rows_kernel<T>, dim3((unsigned)blocks), dim3(256), 0, stream, 1, reinterpret_cast<T*>(C),
-                            reinterpret_cast<const T*>(C2), (long long)p.m, p.n, p.c_row, (long long)n_pad, p.batch, p.c_batch,
-                            (long long)p.m * n_pad));
-        g_launches++;
+        if (rpb_launch(unpack_rows_kernel<T>, dim3((unsigned)blocks), dim3(256), 0, stream, 1, reinterpret_cast<T*>(C),
+                       reinterpret_cast<const T*>(C2), (long long)p.m, p.n, p.c_row, (long long)n_pad, p.batch, p.c_batch,
+                       (long long)p.m * n_pad) != cudaSuccess) {
+            fprintf(stderr, "recpulse_b200: unpad launch failed: %s\n", cudaGetErrorString(cudaGetLastError()));
+            rc = -1;
+        } else {
+            g_launches++;
+        }
     }
+    /* every exit passes here: the temporaries go back to the pool in stream order */
     for (int i = 0; i < 3; ++i) if (tmp[i]) cudaFreeAsync(tmp[i], stream);
     return rc;
 }
@@ -892,6 +934,18 @@ int run_gemm_planned(const RpbProblem& in, void* C, const void* A, const void* B
     if (device_state(device_id, &d)) return -1;
     const int forced = forced_family();
     const bool half_type = p.dtype == DTYPE_FLOAT16 || p.dtype == DTYPE_BFLOAT16;
+    if (p.c_f32) {
+        /* unrounded float32 output: a capability of the tcgen05 kernel only */
+        if (!half_type || p.accumulate || p.bias || p.act || p.c_row != p.n || (p.batch > 1 && p.c_batch != (long long)p.m * p.n)) {
+            fprintf(stderr, "recpulse_b200: a float32 output needs float16 / bfloat16 operands, a packed C and no bias, "
+                            "accumulation or epilogue\n");
+            return -1;
+        }
+        int rc = p.dtype == DTYPE_BFLOAT16 ? launch_umma<__nv_bfloat16>(p, C, A, B, d, stream)
+                                           : launch_umma<__half>(p, C, A, B, d, stream);
+        if (rc == 1) fprintf(stderr, "recpulse_b200: float32 output: the operand layout is not TMA-addressable\n");
+        return rc ? -1 : 0;
+    }
     if (half_type && forced != RPB_KERNEL_SIMT) {
         /* large problems with an operand or output the TMA engine cannot address are packed / padded first */
         int rc = p.dtype == DTYPE_BFLOAT16 ? launch_umma_packed<__nv_bfloat16>(p, C, A, B, d, stream)
@@ -1035,6 +1089,7 @@ void* reference_symbol(const char* name) {
 extern "C" {
 
 void* rpb_reference_symbol(const char* name) { return reference_symbol(name); }
+int rpb_take_status(int device_id);
 
 void rpb_gemm_packed(RpbGemm* g, int m, int k, int n) {
     memset(g, 0, sizeof(*g));
@@ -1054,7 +1109,7 @@ int rp_matmul_ex(void* C, const void* A, const void* B, const RpbGemm* g, DType 
     p.a_row = g->a_row; p.a_col = g->a_col; p.a_batch = g->a_batch; p.a_reduce = g->a_reduce;
     p.b_row = g->b_row; p.b_col = g->b_col; p.b_batch = g->b_batch; p.b_reduce = g->b_reduce;
     p.c_row = g->c_row; p.c_batch = g->c_batch; p.accumulate = g->accumulate; p.dtype = (int)dtype;
-    p.bias = g->bias; p.max_sms = g->max_sms; p.act = g->epilogue;
+    p.bias = g->bias; p.max_sms = g->max_sms; p.act = g->epilogue; p.c_f32 = g->c_float32;
     int prev = -1;
     RPB_CUDA(cudaGetDevice(&prev));
     if (prev != device_id) RPB_CUDA(cudaSetDevice(device_id));
@@ -1141,9 +1196,10 @@ int matmul_kernel_device(void* C, const void* A, const void* B, int m, int k, in
     p.a_row = g.a_row; p.a_col = 1; p.a_batch = 0; p.a_reduce = 0;
     p.b_row = g.b_row; p.b_col = 1; p.b_batch = 0; p.b_reduce = 0;
     p.c_row = n; p.c_batch = 0; p.accumulate = 0; p.dtype = (int)dtype; p.bias = nullptr; p.max_sms = 0; p.act = 0;
+    p.c_f32 = 0;
     if (run_gemm(p, C, A, B, dev, nullptr)) return -1;
     RPB_CUDA(cudaStreamSynchronize(nullptr));
-    return 0;
+    return rpb_take_status(dev) ? -1 : 0;
 }
 
 int rp_matmul(void* C, const void* A, const void* B, int m, int k, int n, DType dtype, int device_id) {
@@ -1177,6 +1233,7 @@ int rp_matmul_host(void* C, const void* A, const void* B, int m, int k, int n, D
     }
     if (!rc && cudaMemcpyAsync(C, dC, cb, cudaMemcpyDeviceToHost, nullptr) != cudaSuccess) rc = -1;
     if (cudaStreamSynchronize(nullptr) != cudaSuccess) rc = -1;
+    if (rpb_take_status(device_id)) rc = -1;
     cudaFree(buf);
     return rc;
 }
@@ -1199,20 +1256,73 @@ unsigned long long rpb_launch_count(void) { return g_launches.load(); }
 void rpb_force_kernel(int family) { g_force.store(family < 0 ? 0 : family); }
 const char* rpb_version(void) { return RPB_VERSION; }
 
+/* Reads and clears the status word of `device_id` WITHOUT synchronising: for entry points that have just
+ * synchronised the stream their kernels ran on.  0 = ok (also when the device was never used). */
+int rpb_take_status(int device_id) {
+    if (device_id < 0 || device_id >= MAX_DEVICES || !g_status_words) return 0;
+    volatile int* w = g_status_words + device_id;
+    const int v = *w;
+    if (v != 0) {
+        *w = 0;
+        fprintf(stderr, "recpulse_b200: a bounded wait inside the tcgen05 kernel ran out on device %d (code %d); the "
+                        "result is invalid\n", device_id, v);
+    }
+    return v;
+}
+
 int rpb_device_status(int device_id) {
     DeviceState* d = nullptr;
     int prev = -1;
     if (cudaGetDevice(&prev) != cudaSuccess) return -1;
     if (prev != device_id && cudaSetDevice(device_id) != cudaSuccess) return -1;
     int v = -1;
-    if (device_state(device_id, &d) == 0) {
-        if (cudaDeviceSynchronize() == cudaSuccess) {
-            if (cudaMemcpy(&v, d->status, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) v = -1;
-            else if (v != 0) cudaMemset(d->status, 0, sizeof(int));
-        }
+    if (device_state(device_id, &d) == 0 && cudaDeviceSynchronize() == cudaSuccess) {
+        volatile int* w = d->status;
+        v = *w;
+        if (v != 0) *w = 0;
     }
     if (prev != device_id) cudaSetDevice(prev);
     return v;
+}
+
+int rpb_scratch_reserve(int device_id, size_t bytes) {
+    DeviceState* d = nullptr;
+    int prev = -1;
+    RPB_CUDA(cudaGetDevice(&prev));
+    if (prev != device_id) RPB_CUDA(cudaSetDevice(device_id));
+    int rc = device_state(device_id, &d);
+    void* p = nullptr;
+    if (!rc) rc = get_scratch(d, bytes, nullptr, &p);
+    if (prev != device_id) cudaSetDevice(prev);
+    return rc;
+}
+
+int rpb_scratch_reset(int device_id) {
+    DeviceState* d = nullptr;
+    int prev = -1;
+    RPB_CUDA(cudaGetDevice(&prev));
+    if (prev != device_id) RPB_CUDA(cudaSetDevice(device_id));
+    int rc = device_state(device_id, &d);
+    if (!rc) {
+        std::lock_guard<std::mutex> lock(d->mu);
+        if (d->scratch && cudaFree(d->scratch) != cudaSuccess) rc = -1;    /* synchronises the device */
+        d->scratch = nullptr; d->scratch_bytes = 0; d->scratch_used = false; d->scratch_pinned = false;
+    }
+    if (prev != device_id) cudaSetDevice(prev);
+    return rc;
+}
+
+int rpb_mem_info(int device_id, size_t* free_bytes, size_t* total_bytes) {
+    int prev = -1;
+    RPB_CUDA(cudaGetDevice(&prev));
+    if (prev != device_id) RPB_CUDA(cudaSetDevice(device_id));
+    size_t f = 0, t = 0;
+    cudaError_t e = cudaMemGetInfo(&f, &t);
+    if (prev != device_id) cudaSetDevice(prev);
+    if (e != cudaSuccess) return -1;
+    if (free_bytes) *free_bytes = f;
+    if (total_bytes) *total_bytes = t;
+    return 0;
 }
 
 }  // extern "C"
@@ -1240,7 +1350,7 @@ static __device__ int g_noalloc_status;
 namespace {
 
 struct NoAllocDevice {
-    bool ready = false;
+    std::atomic<bool> ready{false};
     float* scratch = nullptr;       /* device address of g_noalloc_scratch on this device */
     int* status = nullptr;          /* device address of g_noalloc_status on this device */
     int sm_count = 0;
@@ -1256,9 +1366,9 @@ int noalloc_setup(int device_id, NoAllocDevice** out) {
         return -1;
     }
     NoAllocDevice& d = g_noalloc_dev[device_id];
-    if (!d.ready) {
+    if (!d.ready.load(std::memory_order_acquire)) {
         std::lock_guard<std::mutex> lock(g_mutex);
-        if (!d.ready) {
+        if (!d.ready.load(std::memory_order_relaxed)) {
             void* p = nullptr;
             RPB_CUDA(cudaGetSymbolAddress(&p, g_noalloc_scratch));
             d.scratch = reinterpret_cast<float*>(p);
@@ -1276,7 +1386,7 @@ int noalloc_setup(int device_id, NoAllocDevice** out) {
                 }
                 g_encode = reinterpret_cast<EncodeTiledFn>(fn);
             }
-            d.ready = true;
+            d.ready.store(true, std::memory_order_release);
         }
     }
     *out = &d;

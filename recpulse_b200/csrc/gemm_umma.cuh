@@ -92,6 +92,8 @@ struct Args {
     uint32_t a_kstep, b_kstep;           /* descriptor advance per UMMA_K, in 16-byte units */
     int* status;
     int act;               /* 1: LSTM gate non-linearities on the finished sum (register epilogue, no K slices) */
+    int c_f32;             /* 1: the output is packed float32 [batch][m][n] (unrounded sums of 16-bit operands); the
+                            * epilogue then writes it like a K slice: `partial` = the output when splits == 1 */
 };
 
 /* ------------------------------------------------------------------ PTX wrappers */
@@ -131,7 +133,11 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
         }
     }
     *abort_flag = 1;
-    atomicCAS(status, 0, code);
+    /* the status word may live in mapped host memory (read by the host without a copy), where device atomics are
+     * not defined: a plain store of the first code seen is enough, any non-zero value means "result invalid" */
+    volatile int* st = status;
+    if (*st == 0) *st = code;
+    __threadfence_system();
     return false;
 }
 /* One lane of a converged warp.  The producer and MMA warps run their loops with all 32 lanes and elect the
@@ -590,7 +596,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                 const uint32_t my_row = (uint32_t)lane * 128u;
                 const uint32_t sw = (uint32_t)lane & 7u;
                 const bool tail_item = w >= args.tail_begin;
-                const bool partial_out = args.splits > 1 || tail_item;
+                const bool partial_out = args.splits > 1 || tail_item || args.c_f32;
                 const bool wide = partial_out || SPLIT;                     /* rows of fp32: 32 columns per 128 bytes */
                 const int cols_per_box = wide ? 32 : 64;                    /* 128 bytes of fp32 or of 16-bit T */
                 const int zc = partial_out ? split * args.batch + bz : bz;
@@ -654,7 +660,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                 const int col = nt * ACC_N + c0;
                 if (!row_ok || col >= args.n) {
                     /* nothing to store for this lane */
-                } else if (args.splits > 1) {
+                } else if (args.splits > 1 || args.c_f32) {
                     float* dst = args.partial + (((long long)split * args.batch + bz) * args.m + row) * (long long)args.n + col;
                     if (col + 32 <= args.n && ((reinterpret_cast<uintptr_t>(dst) & 15u) == 0)) {
 #pragma unroll

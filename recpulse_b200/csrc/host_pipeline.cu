@@ -16,6 +16,9 @@
 #include <cuda_runtime.h>
 
 #include "rpb_common.h"
+#include "shard_internal.h"
+
+extern "C" int rpb_take_status(int device_id);   /* gemm_dispatch.cu */
 
 namespace {
 
@@ -30,7 +33,7 @@ struct HostPipe {
     bool ready = false;
 };
 HostPipe g_pipe[64];
-std::mutex g_pipe_mutex;
+std::mutex g_pipe_mutex[64];         /* per device: a sharded call waits inside for the other ranks' GPUs */
 
 #define HP_CUDA(call)                                                                           \
     do {                                                                                        \
@@ -65,21 +68,22 @@ int pipe_setup(HostPipe& p, size_t need, int chunks) {
     return 0;
 }
 
-}  // namespace
-
-extern "C" {
-
-int rp_matmul_fwdbwd_host(void* C, void* dA, void* dB, const void* A, const void* B, const void* dC,
-                          int m, int k, int n, DType dtype, int device_id, int chunk_rows) {
+/* `sh` == nullptr: one GPU.  Otherwise this rank's rows of a product sharded over sh's ranks: B comes from rank
+ * 0's host buffer (one upload per box, then NVLink), dB is reduced on the devices and only this rank's slice
+ * [*db_begin, *db_end) of its elements is copied back. */
+int fwdbwd_host(RpbShard* sh, void* C, void* dA, void* dB, const void* A, const void* B, const void* dC,
+                int m, int k, int n, DType dtype, int device_id, int chunk_rows, long long* db_begin, long long* db_end) {
     const size_t es = rpb_dtype_size((int)dtype);
-    if (!A || !B || m <= 0 || k <= 0 || n <= 0 || !es || device_id < 0 || device_id >= 64) return -1;
+    const int world = rpb_shard_world_of(sh), rank = rpb_shard_rank_of(sh);
+    const bool b_local = world == 1 || rank == 0;          /* this rank uploads B */
+    if (!A || (b_local && !B) || m <= 0 || k <= 0 || n <= 0 || !es || device_id < 0 || device_id >= 64) return -1;
     if (!C && !dA && !dB) return -1;
     const bool bwd = dA || dB;
     if (bwd && !dC) { fprintf(stderr, "recpulse_b200: backward needs dC\n"); return -1; }
     int prev = -1;
     HP_CUDA(cudaGetDevice(&prev));
     if (prev != device_id) HP_CUDA(cudaSetDevice(device_id));
-    std::lock_guard<std::mutex> lock(g_pipe_mutex);
+    std::lock_guard<std::mutex> lock(g_pipe_mutex[device_id]);
     HostPipe& p = g_pipe[device_id];
 
     if (chunk_rows <= 0) {
@@ -111,7 +115,8 @@ int rp_matmul_fwdbwd_host(void* C, void* dA, void* dB, const void* A, const void
         return -1;
     };
 
-    if (cudaMemcpyAsync(dBm, B, es * k * n, cudaMemcpyHostToDevice, p.s_in) != cudaSuccess) return fail("copy of B");
+    if (b_local && cudaMemcpyAsync(dBm, B, es * k * n, cudaMemcpyHostToDevice, p.s_in) != cudaSuccess) return fail("copy of B");
+    if (world > 1 && rpb_shard_broadcast_bytes(sh, dBm, es * k * n, 0, p.s_in)) return fail("broadcast of B");
     if (cudaEventRecord(p.b_ready, p.s_in) != cudaSuccess) return fail("event");
     if (cudaStreamWaitEvent(p.s_mm, p.b_ready, 0) != cudaSuccess) return fail("wait");
 
@@ -142,15 +147,25 @@ int rp_matmul_fwdbwd_host(void* C, void* dA, void* dB, const void* A, const void
         if (dA && cudaMemcpyAsync((char*)dA + offA, ddA + offA, es * rows * k, cudaMemcpyDeviceToHost, p.s_out) != cudaSuccess)
             return fail("copy of dA rows");
     }
-    if (dB) {                                        /* dB = A^T . dC over all rows, one rounding */
-        RpbGemm g;
-        rpb_gemm_packed(&g, k, m, n);
-        g.a_row = 1; g.a_col = k;
-        if (rp_matmul_ex(ddB, dAm, dGm, &g, dtype, device_id, p.s_mm)) return fail("dB GEMM");
+    long long s_begin = 0, s_end = (long long)k * n;
+    if (dB) {                                        /* dB = A^T . dC over all rows (of all ranks), one rounding */
+        if (world > 1) {
+            rpb_shard_db_slice(sh, k, n, (int)dtype, RPB_SHARD_SLICE_ONLY, &s_begin, &s_end);
+            if (rpb_shard_db_begin(sh, ddB, dAm, dGm, m, k, n, (int)dtype, RPB_SHARD_SLICE_ONLY, p.s_mm) ||
+                rpb_shard_db_end(sh, p.s_mm)) return fail("dB GEMM + reduction");
+        } else {
+            RpbGemm g;
+            rpb_gemm_packed(&g, k, m, n);
+            g.a_row = 1; g.a_col = k;
+            if (rp_matmul_ex(ddB, dAm, dGm, &g, dtype, device_id, p.s_mm)) return fail("dB GEMM");
+        }
         cudaEventRecord(p.db_done, p.s_mm);
         cudaStreamWaitEvent(p.s_out, p.db_done, 0);
-        if (cudaMemcpyAsync(dB, ddB, es * k * n, cudaMemcpyDeviceToHost, p.s_out) != cudaSuccess) return fail("copy of dB");
+        if (cudaMemcpyAsync((char*)dB + es * s_begin, ddB + es * s_begin, es * (size_t)(s_end - s_begin), cudaMemcpyDeviceToHost,
+                            p.s_out) != cudaSuccess) return fail("copy of dB");
     }
+    if (db_begin) *db_begin = s_begin;
+    if (db_end) *db_end = s_end;
     cudaError_t e1 = cudaStreamSynchronize(p.s_out);
     cudaError_t e2 = cudaStreamSynchronize(p.s_mm);
     cudaError_t e3 = cudaStreamSynchronize(p.s_in);
@@ -159,13 +174,30 @@ int rp_matmul_fwdbwd_host(void* C, void* dA, void* dB, const void* A, const void
         fprintf(stderr, "recpulse_b200: rp_matmul_fwdbwd_host: %s\n", cudaGetErrorString(e1 != cudaSuccess ? e1 : (e2 != cudaSuccess ? e2 : e3)));
         return -1;
     }
-    return 0;
+    return rpb_take_status(device_id) ? -1 : 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+int rp_matmul_fwdbwd_host(void* C, void* dA, void* dB, const void* A, const void* B, const void* dC,
+                          int m, int k, int n, DType dtype, int device_id, int chunk_rows) {
+    return fwdbwd_host(nullptr, C, dA, dB, A, B, dC, m, k, n, dtype, device_id, chunk_rows, nullptr, nullptr);
+}
+
+int rp_matmul_rowsharded_fwdbwd_host(RpbShard* shard, void* C_rows, void* dA_rows, void* dB, const void* A_rows, const void* B,
+                                     const void* dC_rows, long long rows, int k, int n, DType dtype, int chunk_rows,
+                                     long long* db_begin, long long* db_end) {
+    if (!shard || rows <= 0 || rows > 0x7fffffffLL) return -1;
+    return fwdbwd_host(shard, C_rows, dA_rows, dB, A_rows, B, dC_rows, (int)rows, k, n, dtype, rpb_shard_device_of(shard),
+                       chunk_rows, db_begin, db_end);
 }
 
 /* Frees the device buffers that rp_matmul_fwdbwd_host keeps between calls on `device_id`. */
 int rpb_release_host_pipeline(int device_id) {
     if (device_id < 0 || device_id >= 64) return -1;
-    std::lock_guard<std::mutex> lock(g_pipe_mutex);
+    std::lock_guard<std::mutex> lock(g_pipe_mutex[device_id]);
     HostPipe& p = g_pipe[device_id];
     if (!p.buf) return 0;
     int prev = -1;

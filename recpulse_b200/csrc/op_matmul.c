@@ -19,7 +19,34 @@
 #define RPB_MAX_BATCH_DIMS 8
 
 void* rpb_reference_symbol(const char* name);   /* gemm_dispatch.cu */
+int rpb_take_status(int device_id);             /* gemm_dispatch.cu: kernel status word, read without a copy */
 static void bias_grad_into(Tensor* bias, Tensor* grad_output);
+
+/* ------------------------------------------------------------------ where and how the nodes run
+ * RecPulse ends every device op with a device synchronisation (core/cuda_helpers.cu:14-26) and its callers
+ * rely on results being complete on return; that is the default here too (legacy default stream, stream
+ * synchronised before an entry point returns).  rpb_node_stream() changes it for the calling thread: the
+ * nodes then launch on the given stream, take their outputs from the pool in that stream's order, give
+ * temporaries back in stream order and -- with synchronise == 0 -- return as soon as the work is queued. */
+static __thread cudaStream_t t_stream = NULL;
+static __thread int t_sync = 1;
+
+void rpb_node_stream(void* stream, int synchronise) {
+    t_stream = (cudaStream_t)stream;
+    t_sync = synchronise != 0;
+}
+
+/* end of an entry point: wait (unless told not to) and report a kernel that gave up */
+static int node_finish(int device_id) {
+    if (!t_sync) return 0;
+    if (cudaStreamSynchronize(t_stream) != cudaSuccess) return -1;
+    return rpb_take_status(device_id) ? -1 : 0;
+}
+
+int rpb_node_synchronize(int device_id) {
+    if (cudaStreamSynchronize(t_stream) != cudaSuccess) return -1;
+    return rpb_take_status(device_id) ? -1 : 0;
+}
 
 /* ------------------------------------------------------------------ tensor helpers */
 
@@ -68,7 +95,7 @@ static int device_alloc(void** out, size_t bytes, int device_id) {
         }
     }
     if (device_id >= 0 && device_id < 64 && pool_state[device_id] == 1) {
-        if (cudaMallocAsync(out, bytes, NULL) == cudaSuccess) return 0;
+        if (cudaMallocAsync(out, bytes, t_stream) == cudaSuccess) return 0;
         cudaGetLastError();
     }
     return cudaMalloc(out, bytes) == cudaSuccess ? 0 : -1;
@@ -127,6 +154,23 @@ Tensor* rpb_tensor_view(Tensor* base, int ndim, const int* shape, const int* str
     return t;
 }
 
+/* Overwrites the values of a packed device tensor in place (same buffer: what a captured graph reads). */
+int rpb_tensor_write_host(Tensor* t, const void* host_data) {
+    if (!t || !host_data || t->device_id < 0 || !t->data) return -1;
+    long long s = 1;
+    for (int d = t->ndim - 1; d >= 0; d--) { if (t->strides[d] != s) return -1; s *= t->shape[d]; }
+    if (cudaSetDevice(t->device_id) != cudaSuccess) return -1;
+    if (t_stream && cudaStreamSynchronize(t_stream) != cudaSuccess) return -1;
+    return cudaMemcpy(t->data, host_data, t->size * rpb_dtype_size(t->dtype), cudaMemcpyHostToDevice) == cudaSuccess ? 0 : -1;
+}
+
+/* Drops the accumulated gradient (the next backward assigns a fresh one). */
+void rpb_tensor_zero_grad(Tensor* t) {
+    if (!t || !t->metadata || !t->metadata->grad) return;
+    rpb_tensor_release(t->metadata->grad);
+    t->metadata->grad = NULL;
+}
+
 static bool is_contiguous(const Tensor* t) {      /* functional/functional.c:1117-1128 */
     long long s = 1;
     for (int d = t->ndim - 1; d >= 0; d--) {
@@ -140,6 +184,7 @@ int rpb_tensor_to_host(const Tensor* t, void* host_out) {
     if (!t || !host_out || t->device_id < 0 || t->ndim > RPB_MAX_BATCH_DIMS + 2) return -1;
     const size_t es = rpb_dtype_size(t->dtype);
     if (cudaSetDevice(t->device_id) != cudaSuccess) return -1;
+    if (t_stream && cudaStreamSynchronize(t_stream) != cudaSuccess) return -1;   /* work queued by asynchronous nodes */
     if (is_contiguous(t))
         return cudaMemcpy(host_out, t->data, t->size * es, cudaMemcpyDeviceToHost) == cudaSuccess ? 0 : -1;
     /* strided view: one 2-D copy per innermost row pair (diagnostic path, not a hot path) */
@@ -176,7 +221,12 @@ void rpb_tensor_release(Tensor* t) {              /* core/tensor.c:360-379, core
         if (t->metadata->grad) rpb_tensor_release(t->metadata->grad);
     }
     if (t->owns_data && t->data) {
-        if (t->device_id >= 0) { cudaSetDevice(t->device_id); cudaFree(t->data); }
+        if (t->device_id >= 0) {
+            cudaSetDevice(t->device_id);
+            /* a thread that runs its nodes asynchronously frees in stream order too (cudaFree would wait for
+             * the device, and is not allowed while the stream is being captured) */
+            if (t_sync || cudaFreeAsync(t->data, t_stream) != cudaSuccess) cudaFree(t->data);
+        }
         else free(t->data);
     }
     free_dims(t);
@@ -249,7 +299,7 @@ static int run_batched(void* C, const void* A, const void* B, RpbGemm g, BatchDi
         }
         g.accumulate = base_acc || later_reduce;
         if (rp_matmul_ex((char*)C + oc * (long long)es, (const char*)A + oa * (long long)es,
-                         (const char*)B + ob * (long long)es, &g, dtype, device_id, NULL) != 0) return -1;
+                         (const char*)B + ob * (long long)es, &g, dtype, device_id, t_stream) != 0) return -1;
         int d = nl - 1;
         for (; d >= 0; d--) { if (++idx[d] < loop[d].extent) break; idx[d] = 0; }
         if (d < 0) break;
@@ -363,7 +413,7 @@ static Tensor* matmul_node(Tensor* a, Tensor* b, Tensor* bias) {
 
     int rc = product_into(out, a, b, bias, 0, 0, nd, oshape);
     /* callers assume the result is complete on return (every RecPulse device op synchronises) */
-    if (rc == 0 && cudaStreamSynchronize(NULL) != cudaSuccess) rc = -1;
+    if (rc == 0) rc = node_finish(a->device_id);
     if (rc != 0) { rpb_tensor_release(out); return NULL; }
 
     if (wants_grad(a) || wants_grad(b) || wants_grad(bias)) {
@@ -431,7 +481,7 @@ static int grad_into(Tensor* x, const Tensor* other, const Tensor* grad_output, 
         }
     }
     int rc = run_batched(grad->data, A, B, g, bd, nb, rd, nr, x->dtype, x->device_id);
-    if (rc == 0 && cudaStreamSynchronize(NULL) != cudaSuccess) rc = -1;
+    if (rc == 0) rc = node_finish(x->device_id);
     if (rc != 0) {
         if (fresh) rpb_tensor_release(grad);
         return -1;
@@ -500,8 +550,8 @@ static void bias_grad_into(Tensor* bias, Tensor* grad_output) {
     } else if (!is_contiguous(grad) || grad->size != bias->size) {
         return;
     }
-    int rc = rp_colsum_ex(grad->data, grad_output->data, rows, n, n, bias->dtype, fresh ? 0 : 1, bias->device_id, NULL);
-    if (rc == 0 && cudaStreamSynchronize(NULL) != cudaSuccess) rc = -1;
+    int rc = rp_colsum_ex(grad->data, grad_output->data, rows, n, n, bias->dtype, fresh ? 0 : 1, bias->device_id, t_stream);
+    if (rc == 0) rc = node_finish(bias->device_id);
     if (rc != 0) { if (fresh) rpb_tensor_release(grad); return; }
     if (fresh) bias->metadata->grad = grad;
 }
@@ -530,7 +580,7 @@ static Tensor* linear2_node(Tensor* x, Tensor* w, Tensor* h, Tensor* u, Tensor* 
     /* the second product lands in the epilogue's "+= C"; for the gate block the same epilogue then applies the
      * non-linearities to the finished sum (or, for plans that cannot, one pass over the output does) */
     if (rc == 0) rc = product_into(out, h, u, NULL, 1, gates ? RPB_EPILOGUE_LSTM_GATES : 0, nd, oshape);
-    if (rc == 0 && cudaStreamSynchronize(NULL) != cudaSuccess) rc = -1;
+    if (rc == 0) rc = node_finish(x->device_id);
     if (rc != 0) { rpb_tensor_release(out); return NULL; }
     if (wants_grad(x) || wants_grad(w) || wants_grad(h) || wants_grad(u) || wants_grad(bias)) {
         Tensor* in[5] = {x, w, h, u, bias};
@@ -567,7 +617,7 @@ void backward_lstm_gates_fn(GradFn* self, Tensor* grad_output) {
     Tensor* dpre = rpb_tensor_empty(y->dtype, y->ndim, y->shape, y->device_id);
     if (!dpre) return;
     int rc = rp_lstm_gates_grad_ex(dpre->data, grad_output->data, y->data, (long long)(y->size / (size_t)n), n, n, n, n,
-                                   y->dtype, y->device_id, NULL);
+                                   y->dtype, y->device_id, t_stream);
     if (rc == 0) backward_linear2_fn(self, dpre);
     rpb_tensor_release(dpre);
 }

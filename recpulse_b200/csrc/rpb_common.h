@@ -19,6 +19,7 @@ struct RpbProblem {
     const void* bias;          /* n values of dtype, or NULL */
     int max_sms;               /* 0 = all */
     int act;                   /* RpbGemm.epilogue: 0 none, 1 LSTM gate non-linearities by column quarter */
+    int c_f32;                 /* RpbGemm.c_float32: C is packed float32 although the operands are 16-bit */
 };
 
 #ifdef __CUDACC__

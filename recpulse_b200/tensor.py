@@ -172,6 +172,15 @@ class Tensor:
         if _lib.load().rpb_backward_node(self._p, grad_output._p) != 0:
             raise RuntimeError("backward operation failed")      # python/tensor_python.c:1349-1362
 
+    def zero_grad(self) -> None:
+        _lib.load().rpb_tensor_zero_grad(self._p)
+
+    def copy_from_numpy(self, arr: np.ndarray) -> None:
+        """New values into the SAME device buffer (what a captured CUDA graph keeps reading)."""
+        arr = np.ascontiguousarray(arr.view(np.uint16) if arr.dtype == np.float16 else arr, _NP[self._t.dtype])
+        if arr.shape != self.shape or _lib.load().rpb_tensor_write_host(self._p, arr.ctypes.data_as(C.c_void_p)) != 0:
+            raise RuntimeError("copy_from_numpy failed")
+
     def to_numpy(self) -> np.ndarray:
         out = np.empty(self.shape, _NP[self._t.dtype])
         if _lib.load().rpb_tensor_to_host(self._p, out.ctypes.data_as(C.c_void_p)) != 0:

@@ -129,3 +129,54 @@ def test_accumulate_is_linear_at_full_size():
     x1 = f64(out1.to_numpy(), dtype); x2 = f64(out2.to_numpy(), dtype)
     assert np.linalg.norm(x2 - 2 * x1) / np.linalg.norm(2 * x1) < 4e-3
     assert lib.rpb_device_status(0) == 0
+
+
+def test_bf16_row_sharded_65536_full():
+    """The benchmark's own shape on one GPU: 65536 x 8192 x 8192 forward + backward through rp_matmul_ex.  512 row
+    tiles per column group, A and C larger than 2^31 bytes' worth of offsets, 256 two-CTA tile rows.  Inputs are
+    generated on the device (the bits that are checked are copied back, so both sides see the same values);
+    sampled rows of C and dA against the oracle, sampled entries of dB against float64, and the three column-sum
+    identities over every tile."""
+    import torch
+    dtype = "bfloat16"
+    lib = rpb.load()
+    m, k, n = 65536, 8192, 8192
+    gen = torch.Generator(device="cuda"); gen.manual_seed(5)
+    A = (torch.randn((m, k), generator=gen, device="cuda") / np.sqrt(k)).to(torch.bfloat16)
+    B = torch.randn((k, n), generator=gen, device="cuda").to(torch.bfloat16)
+    dC = torch.randn((m, n), generator=gen, device="cuda").to(torch.bfloat16)
+    Cc = torch.empty((m, n), device="cuda", dtype=torch.bfloat16); dA = torch.empty_like(A); dB = torch.empty_like(B)
+
+    def gemm(c, a, b, mm, kk, nn, a_strides, b_strides):
+        g = rpb.RpbGemm(); lib.rpb_gemm_packed(C.byref(g), mm, kk, nn)
+        g.a_row, g.a_col = a_strides; g.b_row, g.b_col = b_strides
+        assert lib.rp_matmul_ex(C.c_void_p(c.data_ptr()), C.c_void_p(a.data_ptr()), C.c_void_p(b.data_ptr()), C.byref(g),
+                                CODE[dtype], 0, None) == 0
+        assert lib.rpb_last_kernel() == _lib.KERNEL_UMMA
+    gemm(Cc, A, B, m, k, n, (k, 1), (n, 1))
+    gemm(dA, dC, B, m, n, k, (n, 1), (1, n))            # B^T through swapped strides
+    gemm(dB, A, dC, k, m, n, (1, k), (n, 1))            # A^T through swapped strides
+    torch.cuda.synchronize()
+    assert lib.rpb_device_status(0) == 0
+    bits = lambda t: t.contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
+    rng = np.random.default_rng(9)
+    # rows from the first tile, the last tile and past the 2^31-byte offset of A and C
+    ri = np.array([5, 40000, m - 1])
+    idx = torch.as_tensor(ri, device="cuda")
+    b_bits = bits(B)
+    check_close(bits(Cc[idx]), O.rp_matmul(bits(A[idx]), b_bits, CODE[dtype]), dtype, k, "C rows")
+    check_close(bits(dA[idx]), O.rp_matmul(bits(dC[idx]), np.ascontiguousarray(b_bits.T), CODE[dtype]), dtype, n, "dA rows")
+    ii = torch.as_tensor(rng.integers(0, k, 64), device="cuda"); jj = torch.as_tensor(rng.integers(0, n, 64), device="cuda")
+    want = (A[:, ii].double() * dC[:, jj].double()).sum(dim=0)
+    got = dB[ii, jj].double()
+    assert float((got - want).norm() / want.norm()) <= 4e-3
+    colsum = lambda t: t.sum(dim=0, dtype=torch.float64)
+    rms = lambda t: float(t.float().pow(2).mean().sqrt())
+    Bd = B.double()
+    assert float((colsum(Cc) - colsum(A) @ Bd).abs().max()) / (np.sqrt(m) * rms(Cc)) < 2e-2
+    assert float((colsum(dA) - colsum(dC) @ Bd.t()).abs().max()) / (np.sqrt(m) * rms(dA)) < 2e-2
+    rs = dC.sum(dim=1, dtype=torch.float64)
+    rhs = torch.zeros(k, device="cuda", dtype=torch.float64)
+    for s in range(0, m, 4096):
+        rhs += A[s:s + 4096].double().t() @ rs[s:s + 4096]
+    assert float((dB.sum(dim=1, dtype=torch.float64) - rhs).abs().max()) / (np.sqrt(n) * rms(dB)) < 2e-2

@@ -1,5 +1,5 @@
-"""Row-sharded forward + backward on two real GPUs (NCCL), through the library's CUDA GEMMs.
-Skipped on boxes with fewer than two GPUs."""
+"""The sharded entry points on two real GPUs (NCCL issued by the library itself): as two processes, and as
+two threads of one process.  Skipped on boxes with fewer than two GPUs."""
 import os
 import subprocess
 import sys
@@ -7,53 +7,48 @@ import sys
 import pytest
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+CHILD = os.path.join(ROOT, "tests", "sharded_child.py")
 
-CHILD = r'''
-import os, sys
-sys.path.insert(0, %r)
-import torch, torch.distributed as dist
-from recpulse_b200.sharded import RowShardedMatmul, row_partition
-rank = int(os.environ["RANK"]); world = int(os.environ["WORLD_SIZE"])
-torch.cuda.set_device(rank)
-dev = torch.device("cuda", rank)
-dist.init_process_group("nccl", device_id=dev)
-g = torch.Generator(device="cpu").manual_seed(11)
-m, k, n = 1000, 512, 768
-A = (torch.randn(m, k, generator=g) / k ** 0.5).to(torch.bfloat16); B = torch.randn(k, n, generator=g).to(torch.bfloat16)
-dC = torch.randn(m, n, generator=g).to(torch.bfloat16)
-r0, r1 = row_partition(m, world, rank)
-b_local = B.to(dev) if rank == 0 else torch.zeros(k, n, dtype=torch.bfloat16, device=dev)
-op = RowShardedMatmul(b_local)
-a_rows = A[r0:r1].to(dev); dc_rows = dC[r0:r1].to(dev)
-c = op.forward(a_rows)
-da, db = op.backward(a_rows, dc_rows)
-torch.cuda.synchronize()
-def rel(x, ref):
-    return float((x.double().cpu() - ref).norm() / ref.norm())
-Ad, Bd, Gd = A.double(), B.double(), dC.double()
-errs = (rel(c, Ad[r0:r1] @ Bd), rel(da, Gd[r0:r1] @ Bd.t()), rel(db, Ad.t() @ Gd))
-assert all(e < 1e-2 for e in errs), errs
-m2 = 256 * world
-A2 = torch.randn(m2, k, generator=g).to(torch.bfloat16)
-s0, s1 = row_partition(m2, world, rank)
-full = op.gather_output(op.forward(A2[s0:s1].to(dev)))
-assert full.shape == (m2, n) and rel(full, A2.double() @ Bd) < 1e-2
-dist.barrier()
-if rank == 0:
-    print("SHARDED OK", errs)
-dist.destroy_process_group()
-''' % ROOT
+
+def _two_gpus():
+    import torch
+    return torch.cuda.is_available() and torch.cuda.device_count() >= 2
 
 
 @pytest.mark.gpu
-def test_two_gpu_row_sharded_forward_backward(tmp_path):
-    import torch
-    if torch.cuda.device_count() < 2:
+def test_two_process_row_sharded_forward_backward():
+    if not _two_gpus():
         pytest.skip("needs two GPUs")
-    script = tmp_path / "child.py"
-    script.write_text(CHILD)
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
-                        "--master-addr", "127.0.0.1", "--master-port", "29533", str(script)],
+                        "--master-addr", "127.0.0.1", "--master-port", "29533", CHILD],
                        capture_output=True, text=True, timeout=600, env=env)
     assert r.returncode == 0 and "SHARDED OK" in r.stdout, r.stdout[-2000:] + r.stderr[-3000:]
+
+
+@pytest.mark.gpu
+def test_two_threads_of_one_process():
+    if not _two_gpus():
+        pytest.skip("needs two GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    r = subprocess.run([sys.executable, CHILD, "--threads"], capture_output=True, text=True, timeout=600, env=env)
+    assert r.returncode == 0 and "SHARDED OK (threads)" in r.stdout, r.stdout[-2000:] + r.stderr[-3000:]
+
+
+@pytest.mark.gpu
+def test_single_rank_shard_needs_no_nccl():
+    """world == 1: the same entry points on one GPU, no communicator."""
+    import torch
+    from recpulse_b200 import sharded
+    g = torch.Generator().manual_seed(3)
+    m, k, n = 300, 256, 384
+    A = (torch.randn(m, k, generator=g) / 16).to(torch.bfloat16); B = torch.randn(k, n, generator=g).to(torch.bfloat16)
+    dC = torch.randn(m, n, generator=g).to(torch.bfloat16)
+    op = sharded.RowShardedMatmul(B.cuda())
+    c = op.forward(A.cuda()); da, db = op.backward(A.cuda(), dC.cuda())
+    full = op.gather_output(c)
+    torch.cuda.synchronize()
+    rel = lambda x, ref: float((x.double().cpu() - ref).norm() / ref.norm())
+    assert rel(c, A.double() @ B.double()) < 4e-3 and rel(da, dC.double() @ B.double().t()) < 4e-3
+    assert rel(db, A.double().t() @ dC.double()) < 4e-3 and torch.equal(full, c)
+    op.close()

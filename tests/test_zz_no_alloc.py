@@ -12,7 +12,8 @@ import pytest
 
 import recpulse_b200 as rpb
 from recpulse_b200 import _lib
-from helpers import CODE, HALF_FROB_TIGHT, f64, rand_operand
+from oracle import oracle as O
+from helpers import CODE, HALF_FROB_TIGHT, check_close, f64, rand_operand
 
 pytestmark = pytest.mark.gpu
 
@@ -35,6 +36,8 @@ def test_noalloc_matches_regular_entry_point_on_consecutive_calls(dtype):
         a = rand_operand(rng, (m, k), dtype); b = rand_operand(rng, (k, n), dtype, scale=1 / np.sqrt(k))
         ta = rpb.Tensor.from_numpy(a, dtype=dtype); tb = rpb.Tensor.from_numpy(b, dtype=dtype)
         ref = _regular(lib, ta, tb, m, k, n, dtype)
+        want = O.rp_matmul(a, b, CODE[dtype])                 # the reference's own algorithm on the same bits
+        free_before = None
         for call in range(2):
             out = rpb.Tensor.from_numpy(np.full((m, n), 0x7FC0, np.uint16), dtype=dtype)    # NaN-filled output
             status = C.c_int(-1)
@@ -47,6 +50,14 @@ def test_noalloc_matches_regular_entry_point_on_consecutive_calls(dtype):
             assert np.isfinite(g64).all()
             err = np.linalg.norm(g64 - r64) / np.linalg.norm(r64)
             assert err <= HALF_FROB_TIGHT[dtype], (dtype, m, k, n, call, err)
+            check_close(got, want, dtype, k, f"rp_matmul_noalloc vs oracle, call {call}")
+            # nothing was allocated: after the first call on the device (which loads the kernel and resolves the
+            # built-in buffers) the free device memory does not move
+            free_now, total = C.c_size_t(), C.c_size_t()
+            assert lib.rpb_mem_info(0, C.byref(free_now), C.byref(total)) == 0
+            if call == 1:
+                assert free_now.value == free_before, (free_before, free_now.value)
+            free_before = free_now.value
 
 
 def test_noalloc_rejects_what_it_cannot_hold():
