@@ -149,6 +149,54 @@ int rp_lstm_gates_grad_ex(void* dpre, const void* dy, const void* y, long long r
 int rp_colsum_ex(void* out, const void* in, long long rows, int cols, long long row_stride, DType dtype,
                  int accumulate, int device_id, void* stream);
 
+/* A whole GRU cell step as ONE node: h' = (1 - z) n + z h with r = sigmoid(gi_r + gh_r), z = sigmoid(gi_z + gh_z),
+ * n = tanh(gi_n + r gh_n), gi = x . w_ih (+ b_ih), gh = h . w_hh (+ b_hh); 3 * hidden columns in the order r, z, n.
+ * RecPulse's GRUCell.forward (recpulse/module.py:329-348) keeps gi and gh apart (the candidate gate needs gh_n on its
+ * own) and builds the step from two op_matmul, two op_add, two chunk and eleven element-wise nodes.  Here: two GEMMs
+ * with the bias in their epilogues and one element-wise pass forward; one element-wise pass, four GEMMs and two
+ * column sums backward, to all six leaves.  x: [m, k], w_ih: [k, 3 hidden], h: [m, hidden], w_hh: [hidden, 3 hidden],
+ * b_ih / b_hh: 3 hidden elements or NULL.  The node keeps the activated gates and gh as two extra inputs without
+ * gradient, which RecPulse's free_grad_fn releases like any retained input. */
+Tensor* op_gru_cell(Tensor* x, Tensor* w_ih, Tensor* h, Tensor* w_hh, Tensor* b_ih, Tensor* b_hh);
+void backward_gru_cell_fn(GradFn* self, Tensor* grad_output);
+
+/* The two element-wise passes of op_gru_cell on raw device pointers, on `stream`, without synchronising.
+ * gi, gh, dgi, dgh: packed [rows, 3 hidden]; h_next, g, dh: packed [rows, hidden]; h: row stride h_stride.
+ * rp_gru_gates_ex overwrites gi with the activated (r, z, n).  rp_gru_gates_grad_ex writes the gradients of gi and
+ * gh and, when dh is not NULL, the direct part g z of dL/dh (added to dh when dh_accumulate).  0 / -1. */
+int rp_gru_gates_ex(void* h_next, void* gi, const void* gh, const void* h, long long rows, int hidden, long long h_stride,
+                    DType dtype, int device_id, void* stream);
+int rp_gru_gates_grad_ex(void* dgi, void* dgh, void* dh, int dh_accumulate, const void* g, const void* gi_act, const void* gh,
+                         const void* h, long long rows, int hidden, long long h_stride, DType dtype, int device_id, void* stream);
+
+/* ---- additive: conv2d on the GEMM path ---------------------------------------
+ * RecPulse's conv2d loops over the images: im2col + rp_matmul per image forward (ops/ops.c:4761-4770), and in the
+ * backward a materialised W^T, a materialised col^T per image and an rp_add per image (ops/ops.c:4536-4550,
+ * 4575-4617), each step followed by a device synchronisation.  These entry points do the same arithmetic for ALL
+ * images at once: one im2col pass into a resident [N, C_in kH kW, out_H out_W] buffer, then single GEMM launches --
+ * the weight as a broadcast batch operand, transposes as stride swaps, the weight gradient as one summed problem
+ * over the images (fp32 sums, one rounding, optionally added to an existing gradient in the same epilogue) -- and
+ * one col2im pass that gathers in a fixed order (the reference scatters with atomicAdd).  Layouts are RecPulse's:
+ * input [N, C_in, H, W], weight [C_out, C_in, kH, kW], output [N, C_out, out_H, out_W], all packed; bias is the
+ * caller's.  Asynchronous on `stream`. */
+typedef struct {
+    int N, C_in, H, W, C_out, kH, kW;
+    int stride_h, stride_w, pad_h, pad_w, dilation_h, dilation_w;
+} RpbConv2d;
+/* out_H / out_W of the convolution (ops/ops.c:4739-4740); -1 for an invalid geometry. */
+int rp_conv2d_out_shape(const RpbConv2d* c, int* out_h, int* out_w);
+/* Elements of the im2col buffer of all images (N * C_in kH kW * out_H out_W); -1 for an invalid geometry. */
+long long rp_conv2d_col_elems(const RpbConv2d* c);
+/* col_all = im2col(input) for every image (kept by the caller for the backward), out[img] = weight . col_all[img]. */
+int rp_conv2d_forward_ex(void* out, const void* input, const void* weight, void* col_all, const RpbConv2d* c, DType dtype,
+                         int device_id, void* stream);
+/* grad_weight (+)= sum over images of grad_out[img] . col_all[img]^T (when grad_weight is not NULL), and
+ * grad_input (+)= col2im(weight^T . grad_out[img]) (when grad_input is not NULL; dcol_ws is a workspace of
+ * rp_conv2d_col_elems elements). */
+int rp_conv2d_backward_ex(void* grad_input, int accumulate_input, void* grad_weight, int accumulate_weight, const void* grad_out,
+                          const void* weight, const void* col_all, void* dcol_ws, const RpbConv2d* c, DType dtype, int device_id,
+                          void* stream);
+
 /* ---- additive: strided / batched GEMM on raw pointers ----------------------*/
 
 typedef struct {
@@ -336,6 +384,13 @@ void rpb_force_kernel(int family);
  * bounded wait inside the kernel ran out (the kernel returned early; results invalid).
  * Synchronises the device. */
 int rpb_device_status(int device_id);
+/* Bound of each wait on a barrier inside the tcgen05 kernels (default about 2 s of SM clock; also
+ * RPB_WAIT_LIMIT_MS).  ms <= 0 restores the default. */
+void rpb_set_wait_limit_ms(int ms);
+/* Exercises that bound by itself: one small kernel waits, with `limit_cycles` (at most 2e8), on a barrier
+ * nobody signals; the wait gives up, status code 9 is recorded and the kernel returns normally.  0 when the
+ * kernel completed; rpb_device_status() then reports 9 once and 0 afterwards. */
+int rpb_selftest_bounded_wait(int device_id, long long limit_cycles);
 /* Library version string. */
 const char* rpb_version(void);
 /* The per-device scratch buffer (K-slice partial sums, column-sum partials) grows on demand, which frees

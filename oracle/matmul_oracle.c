@@ -397,3 +397,151 @@ int orc_lstm_gates_grad(void* dpre, const void* dY, const void* Y, long long row
         }
     return 0;
 }
+
+/* ------------------------------------------------------------------ GRU cell, recpulse/module.py:329-348
+ * The cell is restated node by node, each node's output rounded to the storage dtype exactly where the
+ * reference rounds it (float16 / bfloat16: widen, compute in float, narrow -- functional/functional.c's HALF
+ * branches and ops/grad_host.c:61-79; float32 / float64: native arithmetic). */
+
+typedef double (*Ew2)(double, double);          /* only used to name the operation; arithmetic is per dtype below */
+enum { EW_ADD, EW_MUL, EW_RSUB1, EW_SIGMOID, EW_TANH, EW_NEG, EW_DSIGMOID, EW_DTANH };
+
+/* out[i] = op(a[i], b[i]) in the storage dtype.  EW_RSUB1: 1 - a (functional_host.c:226-240); EW_SIGMOID / EW_TANH
+ * (functional_host.c:498-545); EW_NEG: -a (backwards_sub_x2, grad_host.c:149); EW_DSIGMOID: a * b * (1 - b) and
+ * EW_DTANH: a * (1 - b * b) with a = upstream gradient, b = the node's output (grad_host.c:365-385, 622-640). */
+static void ew(void* out, const void* a, const void* b, size_t n, int op, int dtype) {
+    for (size_t i = 0; i < n; i++) {
+        if (dtype == ORC_F64) {
+            const double x = ((const double*)a)[i], y = b ? ((const double*)b)[i] : 0.0;
+            double r;
+            switch (op) {
+                case EW_ADD: r = x + y; break;
+                case EW_MUL: r = x * y; break;
+                case EW_RSUB1: r = 1.0 - x; break;
+                case EW_SIGMOID: r = 1.0 / (1.0 + exp(-x)); break;
+                case EW_TANH: r = tanh(x); break;
+                case EW_NEG: r = -x; break;
+                case EW_DSIGMOID: r = x * y * (1.0 - y); break;
+                default: r = x * (1.0 - y * y); break;
+            }
+            ((double*)out)[i] = r;
+        } else {
+            float x, y = 0.0f, r;
+            if (dtype == ORC_F32) { x = ((const float*)a)[i]; if (b) y = ((const float*)b)[i]; }
+            else { orc_widen((const uint16_t*)a + i, &x, 1, dtype); if (b) orc_widen((const uint16_t*)b + i, &y, 1, dtype); }
+            switch (op) {
+                case EW_ADD: r = x + y; break;
+                case EW_MUL: r = x * y; break;
+                case EW_RSUB1: r = 1.0f - x; break;
+                case EW_SIGMOID: r = 1.0f / (1.0f + expf(-x)); break;
+                case EW_TANH: r = tanhf(x); break;
+                case EW_NEG: r = -x; break;
+                case EW_DSIGMOID: r = x * y * (1.0f - y); break;
+                default: r = x * (1.0f - y * y); break;
+            }
+            if (dtype == ORC_F32) ((float*)out)[i] = r; else orc_narrow(&r, (uint16_t*)out + i, 1, dtype);
+        }
+    }
+}
+
+/* columns [c0, c0 + w) of a packed [rows, cols] matrix as a packed [rows, w] copy (chunk + contiguous) */
+static void take_cols(void* out, const void* in, int rows, int cols, int c0, int w, size_t es) {
+    for (int i = 0; i < rows; i++)
+        memcpy((char*)out + (size_t)i * w * es, (const char*)in + ((size_t)i * cols + c0) * es, (size_t)w * es);
+}
+static void put_cols(void* out, const void* in, int rows, int cols, int c0, int w, size_t es) {
+    for (int i = 0; i < rows; i++)
+        memcpy((char*)out + ((size_t)i * cols + c0) * es, (const char*)in + (size_t)i * w * es, (size_t)w * es);
+}
+/* out[i][j] = a[i][j] + bias[j]: the broadcast op_add (ops/ops.c:129-210) */
+static void add_bias_rows(void* out, const void* a, const void* bias, int rows, int cols, int dtype) {
+    const size_t es = esize(dtype);
+    for (int i = 0; i < rows; i++)
+        ew((char*)out + (size_t)i * cols * es, (const char*)a + (size_t)i * cols * es, bias, (size_t)cols, EW_ADD, dtype);
+}
+
+typedef struct { void *gi, *gh, *r, *z, *n, *hn, *t1, *h_next; } GruState;
+
+static void gru_free(GruState* s) {
+    free(s->gi); free(s->gh); free(s->r); free(s->z); free(s->n); free(s->hn); free(s->t1); free(s->h_next);
+}
+
+static int gru_forward_state(GruState* s, const void* X, const void* Wih, const void* H, const void* Whh, const void* bih,
+                             const void* bhh, int m, int kx, int hd, int dtype) {
+    const size_t es = esize(dtype), mh = (size_t)m * hd, m3 = 3 * mh;
+    memset(s, 0, sizeof(*s));
+    s->gi = malloc(m3 * es); s->gh = malloc(m3 * es);
+    s->r = malloc(mh * es); s->z = malloc(mh * es); s->n = malloc(mh * es); s->hn = malloc(mh * es);
+    s->t1 = malloc(mh * es); s->h_next = malloc(mh * es);
+    void* a = malloc(mh * es); void* b = malloc(mh * es);
+    int rc = (s->gi && s->gh && s->r && s->z && s->n && s->hn && s->t1 && s->h_next && a && b) ? 0 : -1;
+    if (!rc) rc = orc_rp_matmul(s->gi, X, Wih, m, kx, 3 * hd, dtype);
+    if (!rc) rc = orc_rp_matmul(s->gh, H, Whh, m, hd, 3 * hd, dtype);
+    if (!rc) {
+        if (bih) add_bias_rows(s->gi, s->gi, bih, m, 3 * hd, dtype);
+        if (bhh) add_bias_rows(s->gh, s->gh, bhh, m, 3 * hd, dtype);
+        take_cols(a, s->gi, m, 3 * hd, 0, hd, es); take_cols(b, s->gh, m, 3 * hd, 0, hd, es);
+        ew(a, a, b, mh, EW_ADD, dtype); ew(s->r, a, NULL, mh, EW_SIGMOID, dtype);             /* r = sigmoid(i_r + h_r) */
+        take_cols(a, s->gi, m, 3 * hd, hd, hd, es); take_cols(b, s->gh, m, 3 * hd, hd, hd, es);
+        ew(a, a, b, mh, EW_ADD, dtype); ew(s->z, a, NULL, mh, EW_SIGMOID, dtype);             /* z = sigmoid(i_z + h_z) */
+        take_cols(a, s->gi, m, 3 * hd, 2 * hd, hd, es); take_cols(s->hn, s->gh, m, 3 * hd, 2 * hd, hd, es);
+        ew(b, s->r, s->hn, mh, EW_MUL, dtype);                                                /* r * h_n */
+        ew(a, a, b, mh, EW_ADD, dtype); ew(s->n, a, NULL, mh, EW_TANH, dtype);                /* n = tanh(i_n + r h_n) */
+        ew(s->t1, s->z, NULL, mh, EW_RSUB1, dtype);                                           /* 1 - z */
+        ew(a, s->t1, s->n, mh, EW_MUL, dtype);                                                /* (1 - z) n */
+        ew(b, s->z, H, mh, EW_MUL, dtype);                                                    /* z h */
+        ew(s->h_next, a, b, mh, EW_ADD, dtype);
+    }
+    free(a); free(b);
+    return rc;
+}
+
+int orc_gru_cell_forward(void* Hn, const void* X, const void* Wih, const void* H, const void* Whh, const void* bih,
+                         const void* bhh, int m, int kx, int hd, int dtype) {
+    if (!Hn || !X || !Wih || !H || !Whh || m <= 0 || kx <= 0 || hd <= 0 || !esize(dtype)) return -1;
+    GruState s;
+    int rc = gru_forward_state(&s, X, Wih, H, Whh, bih, bhh, m, kx, hd, dtype);
+    if (!rc) memcpy(Hn, s.h_next, (size_t)m * hd * esize(dtype));
+    gru_free(&s);
+    return rc;
+}
+
+/* The backward chain of the same nodes (ops/ops.c:77-127 add, :322-420 mul, :1564-1660 tanh / sigmoid, :6260-6283
+ * rsub_scalar, chunk / slice scatter, matmul :6759-6814, bias through reduce_grad_to_shape) for the upstream
+ * gradient G of h'.  Gradients that collect two contributions (z, h) add them with one rounding, as rp_add does. */
+int orc_gru_cell_backward(void* dX, void* dWih, void* dH, void* dWhh, void* dbih, void* dbhh, const void* G, const void* X,
+                          const void* Wih, const void* H, const void* Whh, const void* bih, const void* bhh,
+                          int m, int kx, int hd, int dtype) {
+    if (!G || !X || !Wih || !H || !Whh || m <= 0 || kx <= 0 || hd <= 0 || !esize(dtype)) return -1;
+    const size_t es = esize(dtype), mh = (size_t)m * hd, m3 = 3 * mh;
+    GruState s;
+    int rc = gru_forward_state(&s, X, Wih, H, Whh, bih, bhh, m, kx, hd, dtype);
+    void *dn = malloc(mh * es), *dz = malloc(mh * es), *t = malloc(mh * es), *dan = malloc(mh * es), *daz = malloc(mh * es),
+         *dar = malloc(mh * es), *dhn = malloc(mh * es), *dh1 = malloc(mh * es), *dgi = malloc(m3 * es), *dgh = malloc(m3 * es),
+         *dh2 = malloc(mh * es);
+    if (!dn || !dz || !t || !dan || !daz || !dar || !dhn || !dh1 || !dgi || !dgh || !dh2) rc = -1;
+    if (!rc) {
+        ew(t, G, s.n, mh, EW_MUL, dtype);                /* d(1 - z) = G n                      */
+        ew(dn, G, s.t1, mh, EW_MUL, dtype);              /* dn = G (1 - z)                      */
+        ew(dz, G, H, mh, EW_MUL, dtype);                 /* dz (from z h) = G h                 */
+        ew(dh1, G, s.z, mh, EW_MUL, dtype);              /* dh (from z h) = G z                 */
+        ew(t, t, NULL, mh, EW_NEG, dtype);               /* through 1 - z: -G n                 */
+        ew(dz, dz, t, mh, EW_ADD, dtype);                /* both uses of z                      */
+        ew(dan, dn, s.n, mh, EW_DTANH, dtype);           /* through tanh                        */
+        ew(dar, dan, s.hn, mh, EW_MUL, dtype);           /* dr = da_n h_n                       */
+        ew(dhn, dan, s.r, mh, EW_MUL, dtype);            /* dh_n = da_n r                       */
+        ew(dar, dar, s.r, mh, EW_DSIGMOID, dtype);       /* through sigmoid                     */
+        ew(daz, dz, s.z, mh, EW_DSIGMOID, dtype);
+        put_cols(dgi, dar, m, 3 * hd, 0, hd, es); put_cols(dgi, daz, m, 3 * hd, hd, hd, es); put_cols(dgi, dan, m, 3 * hd, 2 * hd, hd, es);
+        put_cols(dgh, dar, m, 3 * hd, 0, hd, es); put_cols(dgh, daz, m, 3 * hd, hd, hd, es); put_cols(dgh, dhn, m, 3 * hd, 2 * hd, hd, es);
+        int sx[2] = {kx, 1}, swi[2] = {3 * hd, 1}, sh[2] = {hd, 1};
+        rc = orc_matmul_backward(dX, dWih, X, sx, Wih, swi, dgi, m, kx, 3 * hd, dtype, 0);
+        if (!rc) rc = orc_matmul_backward(dh2, dWhh, H, sh, Whh, swi, dgh, m, hd, 3 * hd, dtype, 0);
+        if (!rc && dH) ew(dH, dh1, dh2, mh, EW_ADD, dtype);
+        if (!rc && dbih) rc = orc_bias_grad(dbih, dgi, m, 3 * hd, dtype);
+        if (!rc && dbhh) rc = orc_bias_grad(dbhh, dgh, m, 3 * hd, dtype);
+    }
+    free(dn); free(dz); free(t); free(dan); free(daz); free(dar); free(dhn); free(dh1); free(dgi); free(dgh); free(dh2);
+    gru_free(&s);
+    return rc;
+}

@@ -86,6 +86,18 @@ int orc_lstm_gates_forward(void* Y, const void* X, const void* W, const void* H,
  * g * (1 - y * y) for the tanh columns (ops/grad_host.c:365-385, 622-640), in float (double for float64). */
 int orc_lstm_gates_grad(void* dpre, const void* dY, const void* Y, long long rows, int n, int dtype);
 
+/* One GRU cell step as RecPulse's GRUCell.forward composes it (recpulse/module.py:329-348), node by node with
+ * every node's output rounded to the storage dtype: gi = X.Wih (+ bih), gh = H.Whh (+ bhh), chunks (r, z, n),
+ * r = sigmoid(i_r + h_r), z = sigmoid(i_z + h_z), n = tanh(i_n + r * h_n), h' = (1 - z) * n + z * h.
+ * X: m x kx, Wih: kx x 3hd, H: m x hd, Whh: hd x 3hd, biases 3hd elements or NULL. */
+int orc_gru_cell_forward(void* Hn, const void* X, const void* Wih, const void* H, const void* Whh, const void* bih,
+                         const void* bhh, int m, int kx, int hd, int dtype);
+/* Gradients of all six leaves for the upstream gradient G of h' (any output pointer may be NULL except dX / dWih /
+ * dWhh, which orc_matmul_backward fills). */
+int orc_gru_cell_backward(void* dX, void* dWih, void* dH, void* dWhh, void* dbih, void* dbhh, const void* G, const void* X,
+                          const void* Wih, const void* H, const void* Whh, const void* bih, const void* bhh,
+                          int m, int kx, int hd, int dtype);
+
 #ifdef __cplusplus
 }
 #endif

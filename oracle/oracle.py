@@ -199,3 +199,103 @@ def lstm_gates_grad(dy, y, dtype):
     if rc != 0:
         raise RuntimeError("orc_lstm_gates_grad failed")
     return out
+
+
+def gru_cell_forward(x, w_ih, h, w_hh, b_ih, b_hh, dtype):
+    """One GRU cell step as RecPulse's GRUCell.forward composes it (recpulse/module.py:329-348)."""
+    x = np.ascontiguousarray(x, _NP[dtype]); w_ih = np.ascontiguousarray(w_ih, _NP[dtype])
+    h = np.ascontiguousarray(h, _NP[dtype]); w_hh = np.ascontiguousarray(w_hh, _NP[dtype])
+    m, kx = x.shape; hd = h.shape[1]
+    bi = None if b_ih is None else np.ascontiguousarray(b_ih, _NP[dtype]).reshape(-1)
+    bh = None if b_hh is None else np.ascontiguousarray(b_hh, _NP[dtype]).reshape(-1)
+    out = np.empty((m, hd), _NP[dtype])
+    rc = lib().orc_gru_cell_forward(_p(out), _p(x), _p(w_ih), _p(h), _p(w_hh), _p(bi), _p(bh), m, kx, hd, dtype)
+    if rc != 0:
+        raise RuntimeError("orc_gru_cell_forward failed")
+    return out
+
+
+def gru_cell_backward(g, x, w_ih, h, w_hh, b_ih, b_hh, dtype):
+    """(dx, dw_ih, dh, dw_hh, db_ih, db_hh) of the same composition for the upstream gradient g of h'."""
+    x = np.ascontiguousarray(x, _NP[dtype]); w_ih = np.ascontiguousarray(w_ih, _NP[dtype])
+    h = np.ascontiguousarray(h, _NP[dtype]); w_hh = np.ascontiguousarray(w_hh, _NP[dtype])
+    g = np.ascontiguousarray(g, _NP[dtype])
+    m, kx = x.shape; hd = h.shape[1]
+    bi = None if b_ih is None else np.ascontiguousarray(b_ih, _NP[dtype]).reshape(-1)
+    bh = None if b_hh is None else np.ascontiguousarray(b_hh, _NP[dtype]).reshape(-1)
+    dx = np.empty_like(x); dwi = np.empty_like(w_ih); dh = np.empty_like(h); dwh = np.empty_like(w_hh)
+    dbi = None if bi is None else np.empty_like(bi); dbh = None if bh is None else np.empty_like(bh)
+    rc = lib().orc_gru_cell_backward(_p(dx), _p(dwi), _p(dh), _p(dwh), _p(dbi), _p(dbh), _p(g), _p(x), _p(w_ih), _p(h), _p(w_hh),
+                                     _p(bi), _p(bh), m, kx, hd, dtype)
+    if rc != 0:
+        raise RuntimeError("orc_gru_cell_backward failed")
+    return dx, dwi, dh, dwh, dbi, dbh
+
+
+def _conv_geometry(x_shape, w_shape, stride, pad, dil):
+    n, c, hh, ww = x_shape; oc, c2, kh, kw = w_shape
+    assert c == c2
+    oh = (hh + 2 * pad[0] - dil[0] * (kh - 1) - 1) // stride[0] + 1          # ops/ops.c:4739-4740
+    ow = (ww + 2 * pad[1] - dil[1] * (kw - 1) - 1) // stride[1] + 1
+    return n, c, hh, ww, oc, kh, kw, oh, ow
+
+
+def _im2col(img, kh, kw, stride, pad, dil, oh, ow):
+    """functional/functional_host.c im2col: col[(c kH + kh) kW + kw, oh out_W + ow], zeros outside the image."""
+    c, hh, ww = img.shape
+    col = np.zeros((c * kh * kw, oh * ow), img.dtype)
+    for ch in range(c):
+        for i in range(kh):
+            for j in range(kw):
+                row = (ch * kh + i) * kw + j
+                for a in range(oh):
+                    hi = a * stride[0] + i * dil[0] - pad[0]
+                    if hi < 0 or hi >= hh:
+                        continue
+                    for b in range(ow):
+                        wi = b * stride[1] + j * dil[1] - pad[1]
+                        if 0 <= wi < ww:
+                            col[row, a * ow + b] = img[ch, hi, wi]
+    return col
+
+
+def conv2d_forward(x, w, stride, pad, dil, dtype):
+    """op_conv2d without bias (ops/ops.c:4735-4770): per image im2col, then rp_matmul(weight, col).  float32 / float64."""
+    assert dtype in (F32, F64)
+    n, c, hh, ww, oc, kh, kw, oh, ow = _conv_geometry(x.shape, w.shape, stride, pad, dil)
+    w2 = np.ascontiguousarray(w.reshape(oc, c * kh * kw))
+    out = np.empty((n, oc, oh, ow), _NP[dtype])
+    for i in range(n):
+        out[i] = rp_matmul(w2, _im2col(x[i], kh, kw, stride, pad, dil, oh, ow), dtype).reshape(oc, oh, ow)
+    return out
+
+
+def conv2d_backward(x, w, gout, stride, pad, dil, dtype):
+    """(dx, dw) of the same (ops/ops.c:4480-4620): per image W^T . dout through col2im in (c, kh, kw, oh, ow) order
+    (functional_host.c:1291-1313), and dW = sum over images, in image order, of dout . col^T, each product rounded
+    and added by rp_add."""
+    assert dtype in (F32, F64)
+    n, c, hh, ww, oc, kh, kw, oh, ow = _conv_geometry(x.shape, w.shape, stride, pad, dil)
+    w2 = np.ascontiguousarray(w.reshape(oc, c * kh * kw))
+    wt = np.ascontiguousarray(w2.T)
+    dx = np.zeros(x.shape, _NP[dtype]); dw = np.zeros((oc, c * kh * kw), _NP[dtype])
+    for i in range(n):
+        g2 = np.ascontiguousarray(gout[i].reshape(oc, oh * ow))
+        dcol = rp_matmul(wt, g2, dtype)
+        gim = np.zeros((c, hh, ww), _NP[dtype])
+        for ch in range(c):
+            for a in range(kh):
+                for b in range(kw):
+                    row = (ch * kh + a) * kw + b
+                    for p in range(oh):
+                        hi = p * stride[0] + a * dil[0] - pad[0]
+                        if hi < 0 or hi >= hh:
+                            continue
+                        for q in range(ow):
+                            wi = q * stride[1] + b * dil[1] - pad[1]
+                            if 0 <= wi < ww:
+                                gim[ch, hi, wi] = gim[ch, hi, wi] + dcol[row, p * ow + q]
+        dx[i] = dx[i] + gim
+        col = _im2col(x[i], kh, kw, stride, pad, dil, oh, ow)
+        dw = dw + rp_matmul(g2, np.ascontiguousarray(col.T), dtype)
+    return dx, dw.reshape(w.shape)

@@ -40,6 +40,11 @@ GradFn._fields_ = [("backward", C.c_void_p), ("inputs", C.POINTER(C.POINTER(CTen
                    ("saved_data", C.c_void_p), ("owner", C.POINTER(CTensor))]
 
 
+class RpbConv2d(C.Structure):
+    _fields_ = [(f, C.c_int) for f in ("N", "C_in", "H", "W", "C_out", "kH", "kW", "stride_h", "stride_w", "pad_h", "pad_w",
+                                       "dilation_h", "dilation_w")]
+
+
 class RpbGemm(C.Structure):
     _fields_ = [("m", C.c_int), ("n", C.c_int), ("k", C.c_int), ("batch", C.c_int), ("reduce", C.c_int),
                 ("a_row", C.c_longlong), ("a_col", C.c_longlong), ("a_batch", C.c_longlong), ("a_reduce", C.c_longlong),
@@ -63,6 +68,18 @@ SYMBOLS = {
     "rp_lstm_gates_ex": (C.c_int, [C.c_void_p, C.c_longlong, C.c_int, C.c_longlong, C.c_int, C.c_int, C.c_void_p]),
     "rp_lstm_gates_grad_ex": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_longlong, C.c_int, C.c_longlong, C.c_longlong,
                                         C.c_longlong, C.c_int, C.c_int, C.c_void_p]),
+    "op_gru_cell": (TP, [TP, TP, TP, TP, TP, TP]),
+    "backward_gru_cell_fn": (None, [C.POINTER(GradFn), TP]),
+    "rp_gru_gates_ex": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_longlong, C.c_int, C.c_longlong, C.c_int,
+                                  C.c_int, C.c_void_p]),
+    "rp_gru_gates_grad_ex": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                       C.c_longlong, C.c_int, C.c_longlong, C.c_int, C.c_int, C.c_void_p]),
+    "rp_conv2d_out_shape": (C.c_int, [C.POINTER(RpbConv2d), C.POINTER(C.c_int), C.POINTER(C.c_int)]),
+    "rp_conv2d_col_elems": (C.c_longlong, [C.POINTER(RpbConv2d)]),
+    "rp_conv2d_forward_ex": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(RpbConv2d), C.c_int, C.c_int,
+                                       C.c_void_p]),
+    "rp_conv2d_backward_ex": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                        C.POINTER(RpbConv2d), C.c_int, C.c_int, C.c_void_p]),
     "rp_colsum_ex": (C.c_int, [C.c_void_p, C.c_void_p, C.c_longlong, C.c_int, C.c_longlong, C.c_int, C.c_int, C.c_int,
                                C.c_void_p]),
     "rpb_gemm_packed": (None, [C.POINTER(RpbGemm), C.c_int, C.c_int, C.c_int]),
@@ -80,6 +97,8 @@ SYMBOLS = {
     "rpb_force_kernel": (None, [C.c_int]),
     "rpb_device_status": (C.c_int, [C.c_int]),
     "rpb_version": (C.c_char_p, []),
+    "rpb_set_wait_limit_ms": (None, [C.c_int]),
+    "rpb_selftest_bounded_wait": (C.c_int, [C.c_int, C.c_longlong]),
     "rpb_tensor_from_host": (TP, [C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_int), C.c_int, C.c_bool]),
     "rpb_tensor_empty": (TP, [C.c_int, C.c_int, C.POINTER(C.c_int), C.c_int]),
     "rpb_tensor_view": (TP, [TP, C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_int), C.c_size_t]),

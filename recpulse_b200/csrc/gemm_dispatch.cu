@@ -101,6 +101,23 @@ struct MapCache {
 };
 MapCache g_maps;
 
+/* Bound of one mbarrier wait inside the tcgen05 kernels, in SM clock cycles: about 2 s by default,
+ * rpb_set_wait_limit_ms() or RPB_WAIT_LIMIT_MS changes it (a caller with a watchdog of its own wants less). */
+std::atomic<long long> g_wait_limit{0};
+long long wait_limit_cycles() {
+    long long v = g_wait_limit.load(std::memory_order_relaxed);
+    if (v > 0) return v;
+    v = rpb_umma::WAIT_LIMIT_CYCLES;
+    if (const char* e = getenv("RPB_WAIT_LIMIT_MS")) { const long long ms = atoll(e); if (ms > 0) v = ms * 2000000ll; }
+    g_wait_limit.store(v, std::memory_order_relaxed);
+    return v;
+}
+uint32_t epilogue_sleep_ns() {
+    static int v = -1;
+    if (v < 0) { const char* e = getenv("RPB_EPI_SLEEP_NS"); v = e ? atoi(e) : 0; if (v < 0) v = 0; }
+    return (uint32_t)v;
+}
+
 int forced_family() {
     int f = g_force.load();
     if (f >= 0) return f;
@@ -671,6 +688,8 @@ int launch_umma(const RpbProblem& p, void* C, const void* A, const void* B, Devi
     a.a_kstep = pa.mn_major ? mn_step : 32 >> 4;
     a.b_kstep = pb.mn_major ? mn_step : 32 >> 4;
     a.status = d->status;
+    a.wait_limit = wait_limit_cycles();
+    a.epi_sleep_ns = epilogue_sleep_ns();
 
     CUtensorMap ma, mb;
     const CUtensorMapDataType dt = F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
@@ -1285,6 +1304,29 @@ int rpb_device_status(int device_id) {
     return v;
 }
 
+void rpb_set_wait_limit_ms(int ms) { g_wait_limit.store(ms > 0 ? (long long)ms * 2000000ll : rpb_umma::WAIT_LIMIT_CYCLES); }
+
+void rpb_count_launches(int n) { g_launches += (unsigned long long)n; }
+
+/* Runs the kernels' bounded wait on a barrier that nobody will ever signal, with a short limit: the wait must
+ * give up, leave its code in the device's status word and let the kernel return.  One CTA of one warp, no TMA, no
+ * tensor memory.  Returns 0 when the kernel ran to completion (the status is then read with rpb_device_status). */
+int rpb_selftest_bounded_wait(int device_id, long long limit_cycles) {
+    if (limit_cycles <= 0 || limit_cycles > 200000000ll) return -1;       /* at most ~0.1 s */
+    DeviceState* d = nullptr;
+    int prev = -1;
+    RPB_CUDA(cudaGetDevice(&prev));
+    if (prev != device_id) RPB_CUDA(cudaSetDevice(device_id));
+    int rc = device_state(device_id, &d);
+    if (!rc) {
+        rpb_umma::wait_selftest_kernel<<<1, 32>>>(d->status, limit_cycles);
+        g_launches++;
+        if (cudaGetLastError() != cudaSuccess || cudaDeviceSynchronize() != cudaSuccess) rc = -1;
+    }
+    if (prev != device_id) cudaSetDevice(prev);
+    return rc;
+}
+
 int rpb_scratch_reserve(int device_id, size_t bytes) {
     DeviceState* d = nullptr;
     int prev = -1;
@@ -1440,6 +1482,8 @@ int noalloc_launch(void* C, const void* A, const void* B, int m, int k, int n, i
     a.a_kstep = pa.mn_major ? (2 * 1024) >> 4 : 32 >> 4;
     a.b_kstep = pb.mn_major ? (2 * 1024) >> 4 : 32 >> 4;
     a.status = d->status;
+    a.wait_limit = wait_limit_cycles();
+    a.epi_sleep_ns = 0;
 
     CUtensorMap ma, mb;
     const CUtensorMapDataType dt = bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;

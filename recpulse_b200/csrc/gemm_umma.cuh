@@ -49,7 +49,7 @@ template <typename T> struct Elem {
     static constexpr int CHUNK = 128 / BYTES;            /* MN-major operands: elements per 128-byte chunk */
     static constexpr int THREADS = (2 + EPI_WARPS + (SPLIT ? SPLIT_WARPS : 0)) * 32;
 };
-constexpr long long WAIT_LIMIT_CYCLES = 4000000000ll;   /* about 2 s of SM clock per wait */
+constexpr long long WAIT_LIMIT_CYCLES = 4000000000ll;   /* default bound of one wait: about 2 s of SM clock */
 constexpr int SMEM_LIMIT = 227 * 1024;
 
 template <int BN, bool SPLIT = false> struct Config {
@@ -92,6 +92,8 @@ struct Args {
     uint32_t a_kstep, b_kstep;           /* descriptor advance per UMMA_K, in 16-byte units */
     int* status;
     int act;               /* 1: LSTM gate non-linearities on the finished sum (register epilogue, no K slices) */
+    long long wait_limit;  /* bound of every mbarrier wait, in SM clock cycles */
+    uint32_t epi_sleep_ns; /* back-off between polls of the epilogue warps' wait for a finished accumulator (0 = spin) */
     int c_f32;             /* 1: the output is packed float32 [batch][m][n] (unrounded sums of 16-bit operands); the
                             * epilogue then writes it like a K slice: `partial` = the output when splits == 1 */
 };
@@ -119,17 +121,20 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
         : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok;
 }
-/* Bounded wait: gives up after WAIT_LIMIT_CYCLES of the SM clock (about 2 s).  false = gave up (or
- * another role already did): the caller leaves its main loop and the kernel tears down. */
+/* Bounded wait: gives up after `limit` cycles of the SM clock (Args.wait_limit; about 2 s by default).
+ * false = gave up (or another role already did): the caller leaves its main loop and the kernel tears down. */
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          int* status, int code) {
+                                          int* status, int code, long long limit, uint32_t sleep_ns = 0) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     for (uint32_t i = 0;; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((i & 255u) == 255u) {
+        /* long waits (an epilogue warp waits a whole tile time for its accumulator) may back off between polls
+         * instead of keeping 32 lanes on the barrier: fewer issue slots and less power for the same result */
+        if (sleep_ns) __nanosleep(sleep_ns);
+        if ((i & 255u) == 255u || (sleep_ns && (i & 7u) == 7u)) {
             if (*abort_flag) return false;
-            if (clock64() - t0 > WAIT_LIMIT_CYCLES) break;
+            if (clock64() - t0 > limit) break;
         }
     }
     *abort_flag = 1;
@@ -152,8 +157,8 @@ __device__ __forceinline__ bool elect_one() {
 }
 /* all lanes of a converged warp wait; the verdict is uniform */
 __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                               int* status, int code) {
-    const bool ok = mbar_wait(bar, parity, abort_flag, status, code);
+                                               int* status, int code, long long limit) {
+    const bool ok = mbar_wait(bar, parity, abort_flag, status, code, limit);
     return __all_sync(0xffffffffu, ok);
 }
 /* PAIR: the copy may signal an mbarrier in the other CTA of the pair (cta_group::2); never multicast */
@@ -445,7 +450,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                 int a_r = r0 * args.a_reduce_mul, b_r = r0 * args.b_reduce_mul;
                 const int a_b = bz * args.a_batch_mul, b_b = bz * args.b_batch_mul;
                 for (int left = it1 - it0; left > 0; --left) {
-                    if (!mbar_wait_warp(eb, parity, abort_flag, args.status, 1)) { alive = false; break; }
+                    if (!mbar_wait_warp(eb, parity, abort_flag, args.status, 1, args.wait_limit)) { alive = false; break; }
                     if (elect_one()) {
                         const uint32_t sb = sa + Cfg::A_BYTES;
                         uint32_t tb = fb;
@@ -499,13 +504,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                 int it0, it1; k_range(w, split, it0, it1);
                 const uint32_t ab = local_tile & 1u;
                 const uint32_t acc_phase = (local_tile >> 1) & 1u;
-                if (!mbar_wait_warp(tempty_bar(ab), acc_phase ^ 1u, abort_flag, args.status, 2)) { alive = false; break; }
+                if (!mbar_wait_warp(tempty_bar(ab), acc_phase ^ 1u, abort_flag, args.status, 2, args.wait_limit)) { alive = false; break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + ab * ACC_N;
                 uint32_t acc = 0u;                                  /* the first instruction of a tile overwrites */
                 for (int left = it1 - it0; left > 0; --left) {
                     /* float32: the stage is usable once the split warps (of both CTAs of a pair) are done with it */
-                    if (!mbar_wait_warp(wb, phase, abort_flag, args.status, 3)) { alive = false; break; }
+                    if (!mbar_wait_warp(wb, phase, abort_flag, args.status, 3, args.wait_limit)) { alive = false; break; }
                     tc_fence_after();
                     if (elect_one()) {
 #pragma unroll
@@ -545,7 +550,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             int mt, nt, split, bz; decode(w, mt, nt, split, bz);
             int it0, it1; k_range(w, split, it0, it1);
             for (int it = it0; it < it1; ++it) {
-                if (!mbar_wait(full_bar(stage), phase, abort_flag, args.status, 5)) { alive = false; break; }
+                if (!mbar_wait(full_bar(stage), phase, abort_flag, args.status, 5, args.wait_limit)) { alive = false; break; }
                 const uint32_t base = smem_base + stage * Cfg::STAGE_BYTES;
 #pragma unroll 4
                 for (int i = st; i < Cfg::LOAD_BYTES / 16; i += SPLIT_WARPS * 32) {
@@ -581,7 +586,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             int mt, nt, split, bz; decode(w, mt, nt, split, bz);
             const uint32_t ab = local_tile & 1u;
             const uint32_t acc_phase = (local_tile >> 1) & 1u;
-            if (!mbar_wait(tfull_bar(ab), acc_phase, abort_flag, args.status, 4)) { alive = false; break; }
+            if (!mbar_wait(tfull_bar(ab), acc_phase, abort_flag, args.status, 4, args.wait_limit, args.epi_sleep_ns)) { alive = false; break; }
             __syncwarp();
             tc_fence_after();
             const int row = mt * TILE_M + (int)cta_rank * BLOCK_M + quarter * 32 + lane;
@@ -785,6 +790,21 @@ __global__ void tail_reduce_kernel(const float* __restrict__ scratch, T* c, cons
         if (bias) x += to_f32<T>(bias[col + e]);
         dst[e] = from_f32<T>(x);
     }
+}
+
+/* The bounded wait on its own: a barrier that expects one arrival and never gets it.  Every lane polls with the
+ * given limit, the wait gives up, code 9 goes to *status and the kernel returns. */
+__global__ void wait_selftest_kernel(int* status, long long limit_cycles) {
+    __shared__ __align__(8) unsigned long long bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&bar), 1);
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    const bool ok = mbar_wait(smem_u32(&bar), 0, &abort_flag, status, 9, limit_cycles);
+    if (ok && threadIdx.x == 0) { volatile int* st = status; *st = -9; }     /* cannot happen: nobody arrives */
 }
 
 }  // namespace rpb_umma

@@ -622,6 +622,101 @@ void backward_lstm_gates_fn(GradFn* self, Tensor* grad_output) {
     rpb_tensor_release(dpre);
 }
 
+/* ------------------------------------------------------------------ GRU cell (recpulse/module.py:329-348) */
+
+typedef struct { int has_b_ih, has_b_hh; } GruSaved;     /* flat: RecPulse's free_grad_fn releases it with free() */
+
+static bool packed_2d(const Tensor* t) { return t && t->ndim == 2 && is_contiguous(t); }
+
+Tensor* op_gru_cell(Tensor* x, Tensor* w_ih, Tensor* h, Tensor* w_hh, Tensor* b_ih, Tensor* b_hh) {
+    if (!operands_ok(x, w_ih) || !operands_ok(h, w_hh)) return NULL;
+    if (x->ndim != 2 || h->ndim != 2 || w_ih->ndim != 2 || w_hh->ndim != 2) return NULL;
+    if (x->dtype != h->dtype || x->device_id != h->device_id || x->shape[0] != h->shape[0]) return NULL;
+    if (x->device_id < 0) {
+        fprintf(stderr, "recpulse_b200: op_gru_cell on host tensors: this library has no CPU path\n");
+        return NULL;
+    }
+    const int m = x->shape[0], hidden = h->shape[1], n3 = 3 * hidden;
+    if (w_ih->shape[1] != n3 || w_hh->shape[1] != n3 || w_hh->shape[0] != hidden) return NULL;
+    if (h->strides[1] != 1) return NULL;
+    if ((b_ih && !bias_ok(b_ih, x, n3)) || (b_hh && !bias_ok(b_hh, x, n3))) return NULL;
+    int gshape[2] = {m, n3}, oshape[2] = {m, hidden};
+    Tensor* gi = rpb_tensor_empty(x->dtype, 2, gshape, x->device_id);
+    Tensor* gh = rpb_tensor_empty(x->dtype, 2, gshape, x->device_id);
+    Tensor* out = rpb_tensor_empty(x->dtype, 2, oshape, x->device_id);
+    int rc = (gi && gh && out) ? 0 : -1;
+    /* the two products stay apart (the candidate gate multiplies gh_n by r before the sum); biases ride in the epilogues */
+    if (rc == 0) rc = product_into(gi, x, w_ih, b_ih, 0, 0, 0, gshape);
+    if (rc == 0) rc = product_into(gh, h, w_hh, b_hh, 0, 0, 0, gshape);
+    if (rc == 0) rc = rp_gru_gates_ex(out->data, gi->data, gh->data, h->data, m, hidden, h->strides[0], x->dtype, x->device_id, t_stream);
+    if (rc == 0) rc = node_finish(x->device_id);
+    if (rc != 0) { rpb_tensor_release(gi); rpb_tensor_release(gh); rpb_tensor_release(out); return NULL; }
+    if (wants_grad(x) || wants_grad(w_ih) || wants_grad(h) || wants_grad(w_hh) || wants_grad(b_ih) || wants_grad(b_hh)) {
+        /* inputs: x, w_ih, h, w_hh, [b_ih], [b_hh], activated gates, gh.  The last two carry no Meta: RecPulse's
+         * tensor_backward skips them (core/tensor.c:251, 296) and free_grad_fn releases them (ops/ops.c:7227-7322). */
+        Tensor* in[8];
+        int n_in = 0;
+        in[n_in++] = x; in[n_in++] = w_ih; in[n_in++] = h; in[n_in++] = w_hh;
+        if (b_ih) in[n_in++] = b_ih;
+        if (b_hh) in[n_in++] = b_hh;
+        in[n_in++] = gi; in[n_in++] = gh;
+        GruSaved* saved = (GruSaved*)malloc(sizeof(GruSaved));
+        if (!saved || attach_node(out, backward_gru_cell_fn, in, n_in)) {
+            free(saved); rpb_tensor_release(gi); rpb_tensor_release(gh); rpb_tensor_release(out);
+            return NULL;
+        }
+        saved->has_b_ih = b_ih != NULL; saved->has_b_hh = b_hh != NULL;
+        out->metadata->grad_fn->saved_data = saved;
+    }
+    rpb_tensor_release(gi);             /* the node (if any) holds its own references */
+    rpb_tensor_release(gh);
+    return out;
+}
+
+void backward_gru_cell_fn(GradFn* self, Tensor* grad_output) {
+    if (!self || !grad_output || !self->inputs || !self->saved_data || !self->owner) return;
+    const GruSaved* saved = (const GruSaved*)self->saved_data;
+    const int n_in = 6 + saved->has_b_ih + saved->has_b_hh;
+    if (self->num_inputs != n_in) return;
+    Tensor** in = self->inputs;
+    Tensor *x = in[0], *w_ih = in[1], *h = in[2], *w_hh = in[3];
+    Tensor* b_ih = saved->has_b_ih ? in[4] : NULL;
+    Tensor* b_hh = saved->has_b_hh ? in[4 + saved->has_b_ih] : NULL;
+    Tensor *gi = in[n_in - 2], *gh = in[n_in - 1];
+    if (!x || !w_ih || !h || !w_hh || !gi || !gh || x->device_id < 0) return;
+    const int m = x->shape[0], hidden = h->shape[1];
+    if (grad_output->dtype != x->dtype || grad_output->device_id != x->device_id || !packed_2d(grad_output) ||
+        grad_output->shape[0] != m || grad_output->shape[1] != hidden) {
+        fprintf(stderr, "recpulse_b200: op_gru_cell backward: upstream gradient must be a packed [m, hidden] tensor\n");
+        return;
+    }
+    Tensor* dgi = rpb_tensor_empty(x->dtype, 2, gi->shape, x->device_id);
+    Tensor* dgh = rpb_tensor_empty(x->dtype, 2, gi->shape, x->device_id);
+    if (!dgi || !dgh) { rpb_tensor_release(dgi); rpb_tensor_release(dgh); return; }
+    /* the direct part of dL/dh (g z) opens h's gradient; the GEMM below then adds dgh . w_hh^T in its epilogue */
+    void* dh = NULL;
+    int dh_acc = 0;
+    Tensor* fresh_dh = NULL;
+    if (wants_grad(h)) {
+        if (h->metadata->grad) {
+            if (is_contiguous(h->metadata->grad) && h->metadata->grad->size == h->size) { dh = h->metadata->grad->data; dh_acc = 1; }
+        } else {
+            fresh_dh = rpb_tensor_empty(h->dtype, h->ndim, h->shape, h->device_id);
+            if (fresh_dh) dh = fresh_dh->data;
+        }
+    }
+    int rc = rp_gru_gates_grad_ex(dgi->data, dgh->data, dh, dh_acc, grad_output->data, gi->data, gh->data, h->data, m, hidden,
+                                  h->strides[0], x->dtype, x->device_id, t_stream);
+    if (rc == 0 && fresh_dh) { h->metadata->grad = fresh_dh; fresh_dh = NULL; }
+    if (rc == 0) rc = matmul_grads(x, w_ih, dgi);
+    if (rc == 0) rc = matmul_grads(h, w_hh, dgh);
+    if (rc == 0 && b_ih) bias_grad_into(b_ih, dgi);
+    if (rc == 0 && b_hh) bias_grad_into(b_hh, dgh);
+    rpb_tensor_release(fresh_dh);
+    rpb_tensor_release(dgi);
+    rpb_tensor_release(dgh);
+}
+
 int rpb_backward_node(Tensor* out, Tensor* grad_output) {
     if (!out || !grad_output || !out->metadata || !out->metadata->grad_fn) return -1;
     GradFn* fn = out->metadata->grad_fn;

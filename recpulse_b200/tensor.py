@@ -167,6 +167,16 @@ class Tensor:
             raise RuntimeError("op_lstm_gates operation failed")
         return Tensor(p, keepalive=(self, weight, h, u, bias))
 
+    def op_gru_cell(self, w_ih: "Tensor", h: "Tensor", w_hh: "Tensor", b_ih: "Tensor | None" = None,
+                    b_hh: "Tensor | None" = None) -> "Tensor":
+        """h' of one GRU cell step for input `self` and state `h`, as one node; the composition of
+        recpulse/module.py:329-348."""
+        p = _lib.load().op_gru_cell(self._p, w_ih._p, h._p, w_hh._p, b_ih._p if b_ih is not None else None,
+                                    b_hh._p if b_hh is not None else None)
+        if not p:
+            raise RuntimeError("op_gru_cell operation failed")
+        return Tensor(p, keepalive=(self, w_ih, h, w_hh, b_ih, b_hh))
+
     def backward(self, grad_output: "Tensor") -> None:
         """Run this node's backward with an explicit upstream gradient and free the node."""
         if _lib.load().rpb_backward_node(self._p, grad_output._p) != 0:

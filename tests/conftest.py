@@ -44,3 +44,23 @@ def lstm_gates_golden():
         name, dtype, field = key.split("/")
         cases.setdefault((name, dtype), {})[field] = z[key]
     return cases
+
+
+def _load_cases(fname):
+    import numpy as np
+    z = np.load(os.path.join(ROOT, "tests", "golden", fname))
+    cases = {}
+    for key in z.files:
+        name, dtype, field = key.split("/")
+        cases.setdefault((name, dtype), {})[field] = z[key]
+    return cases
+
+
+@pytest.fixture(scope="session")
+def gru_cell_golden():
+    return _load_cases("gru_cell_golden.npz")
+
+
+@pytest.fixture(scope="session")
+def conv2d_golden():
+    return _load_cases("conv2d_golden.npz")

@@ -1,4 +1,4 @@
-"""Generate tests/golden/{matmul,linear,lstm_gates}_golden.npz from the UNMODIFIED reference.
+"""Generate tests/golden/{matmul,linear,lstm_gates,gru_cell,conv2d}_golden.npz from the UNMODIFIED reference.
 
 Run in a container where the reference tree is mounted and compiled by
 ``make -C oracle ref`` (produces oracle/_ref/recpulse_cuda.so):
@@ -109,6 +109,52 @@ def run_lstm_gates(name, dtype, m, kx, kh, hidden, rng):
     return {f"{name}/{dtype}/{key}": val for key, val in out.items()}
 
 
+def run_gru_cell(name, dtype, m, kx, hidden, rng, bias=True):
+    """One step of GRUCell.forward (recpulse/module.py:329-348), op by op as the module composes it,
+    with loss = sum(h_next * g)."""
+    n = 3 * hidden
+    x64 = rng.uniform(-1, 1, (m, kx)); wi64 = rng.uniform(-1, 1, (kx, n)) / np.sqrt(kx)
+    h64 = rng.uniform(-1, 1, (m, hidden)); wh64 = rng.uniform(-1, 1, (hidden, n)) / np.sqrt(hidden)
+    bi64 = rng.uniform(-1, 1, (n,)); bh64 = rng.uniform(-1, 1, (n,)); g64 = rng.uniform(-1, 1, (m, hidden))
+    x = to_rp(x64, dtype); wi = to_rp(wi64, dtype); h = to_rp(h64, dtype); wh = to_rp(wh64, dtype)
+    bi = to_rp(bi64, dtype); bh = to_rp(bh64, dtype); g = to_rp(g64, dtype)
+    leaves = [x, wi, h, wh] + ([bi, bh] if bias else [])
+    for t in leaves:
+        t.requires_grad_(True)
+    gi = x.op_matmul(wi); gh = h.op_matmul(wh)
+    if bias:
+        gi = gi.op_add(bi); gh = gh.op_add(bh)
+    i_r, i_z, i_n = gi.chunk(3, 1)
+    h_r, h_z, h_n = gh.chunk(3, 1)
+    r = i_r.op_add(h_r).op_sigmoid()
+    z = i_z.op_add(h_z).op_sigmoid()
+    nn = i_n.op_add(r.op_mul(h_n)).op_tanh()
+    h_next = z.op_rsub_scalar(1.0).op_mul(nn).op_add(z.op_mul(h))
+    loss = h_next.op_mul(g).op_sum_all()
+    loss.backward()
+    out = {"x": bits(x), "wi": bits(wi), "h": bits(h), "wh": bits(wh), "g": bits(g), "hn": bits(h_next),
+           "dx": bits(x.grad), "dwi": bits(wi.grad), "dh": bits(h.grad), "dwh": bits(wh.grad),
+           "meta": np.array([m, kx, hidden, int(bias)], np.int64)}
+    if bias:
+        out.update({"bi": bits(bi), "bh": bits(bh), "dbi": bits(bi.grad), "dbh": bits(bh.grad)})
+    return {f"{name}/{dtype}/{key}": val for key, val in out.items()}
+
+
+def run_conv2d(name, dtype, n, c, hh, ww, oc, kh, kw, stride, pad, dil, rng):
+    """op_conv2d without bias + backward (ops/ops.c:4480-4770) on the CPU, loss = sum(y * g).  float32 / float64 only:
+    the reference's host conv2d leaves its transposed buffers unset for the 16-bit types."""
+    x64 = rng.uniform(-1, 1, (n, c, hh, ww)); w64 = rng.uniform(-1, 1, (oc, c, kh, kw)) / np.sqrt(c * kh * kw)
+    x = to_rp(x64, dtype); w = to_rp(w64, dtype)
+    x.requires_grad_(True); w.requires_grad_(True)
+    y = x.op_conv2d(w, None, stride[0], stride[1], pad[0], pad[1], dil[0], dil[1])
+    g = to_rp(rng.uniform(-1, 1, tuple(y.shape)), dtype)
+    loss = y.op_mul(g).op_sum_all()
+    loss.backward()
+    out = {"x": bits(x), "w": bits(w), "g": bits(g), "y": bits(y), "dx": bits(x.grad), "dw": bits(w.grad),
+           "meta": np.array([n, c, hh, ww, oc, kh, kw, *stride, *pad, *dil], np.int64)}
+    return {f"{name}/{dtype}/{key}": val for key, val in out.items()}
+
+
 def main():
     rng = np.random.default_rng(20240607)
     store = {}
@@ -137,6 +183,22 @@ def main():
             gates.update(run_lstm_gates(f"gates_{m}x{kx}x{kh}x{hidden}", dtype, m, kx, kh, hidden, rng))
     np.savez_compressed(os.path.join(HERE, "lstm_gates_golden.npz"), **gates)
     print("lstm gate cases:", len(gates) // 12)
+    gru = {}
+    rng = np.random.default_rng(20240610)
+    for dtype in DT:
+        for (m, kx, hidden, bias) in [(3, 5, 2, True), (16, 24, 8, True), (9, 33, 5, False), (7, 12, 16, True)]:
+            gru.update(run_gru_cell(f"gru_{m}x{kx}x{hidden}_{'b' if bias else 'nb'}", dtype, m, kx, hidden, rng, bias))
+    np.savez_compressed(os.path.join(HERE, "gru_cell_golden.npz"), **gru)
+    print("gru cell cases:", sum(1 for k in gru if k.endswith("/meta")))
+    conv = {}
+    rng = np.random.default_rng(20240611)
+    for dtype in ("float32", "float64"):
+        conv.update(run_conv2d("conv_3x3_same", dtype, 2, 3, 7, 6, 4, 3, 3, (1, 1), (1, 1), (1, 1), rng))
+        conv.update(run_conv2d("conv_2x3_strided_dilated", dtype, 3, 2, 9, 8, 5, 2, 3, (2, 1), (0, 1), (1, 2), rng))
+        conv.update(run_conv2d("conv_1x1", dtype, 2, 8, 5, 5, 16, 1, 1, (1, 1), (0, 0), (1, 1), rng))
+        conv.update(run_conv2d("conv_5x5_stride2", dtype, 4, 3, 12, 12, 8, 5, 5, (2, 2), (2, 2), (1, 1), rng))
+    np.savez_compressed(os.path.join(HERE, "conv2d_golden.npz"), **conv)
+    print("conv2d cases:", sum(1 for k in conv if k.endswith("/meta")))
 
 
 if __name__ == "__main__":

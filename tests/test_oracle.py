@@ -169,3 +169,42 @@ def test_lstm_gates_composition_bit_exact_vs_reference_fixtures(lstm_gates_golde
         assert np.array_equal(dh, case["dh"]) and np.array_equal(du, case["du"]), name
         assert np.array_equal(O.bias_grad(dpre, code), case["db"]), name
     assert seen == 3
+
+
+@pytest.mark.parametrize("dtype", list(CODE))
+def test_gru_cell_composition_bit_exact_vs_reference_fixtures(gru_cell_golden, dtype):
+    """GRUCell.forward (recpulse/module.py:329-348) op by op, and its backward to all six leaves, against the
+    unmodified reference's own run: every bit of h' and of every gradient."""
+    code = CODE[dtype]
+    seen = 0
+    for (name, dt), case in gru_cell_golden.items():
+        if dt != dtype:
+            continue
+        seen += 1
+        bi, bh = case.get("bi"), case.get("bh")
+        hn = O.gru_cell_forward(case["x"], case["wi"], case["h"], case["wh"], bi, bh, code)
+        assert np.array_equal(hn, case["hn"]), name
+        dx, dwi, dh, dwh, dbi, dbh = O.gru_cell_backward(case["g"], case["x"], case["wi"], case["h"], case["wh"], bi, bh, code)
+        for got, key in ((dx, "dx"), (dwi, "dwi"), (dh, "dh"), (dwh, "dwh")):
+            assert np.array_equal(got, case[key]), (name, key)
+        if bi is not None:
+            assert np.array_equal(dbi, case["dbi"]) and np.array_equal(dbh, case["dbh"]), name
+    assert seen == 4
+
+
+@pytest.mark.parametrize("dtype", ["float32", "float64"])
+def test_conv2d_restatement_bit_exact_vs_reference_fixtures(conv2d_golden, dtype):
+    """op_conv2d + backward (ops/ops.c:4480-4770: per-image im2col, rp_matmul, col2im, rp_add) against the
+    unmodified reference's CPU run.  float32 / float64: the reference's host conv2d does not handle the 16-bit types."""
+    code = CODE[dtype]
+    seen = 0
+    for (name, dt), case in conv2d_golden.items():
+        if dt != dtype:
+            continue
+        seen += 1
+        mt = [int(v) for v in case["meta"]]
+        st, pd, dl = tuple(mt[7:9]), tuple(mt[9:11]), tuple(mt[11:13])
+        assert np.array_equal(O.conv2d_forward(case["x"], case["w"], st, pd, dl, code), case["y"]), name
+        dx, dw = O.conv2d_backward(case["x"], case["w"], case["g"], st, pd, dl, code)
+        assert np.array_equal(dx, case["dx"]) and np.array_equal(dw, case["dw"]), name
+    assert seen == 4

@@ -26,7 +26,7 @@ def dev(arr, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["bfloat16", "float16"])
-@pytest.mark.parametrize("shape", [(520, 1160, 776), (64, 4096, 128), (300, 200, 130), (2048, 512, 1024)])
+@pytest.mark.parametrize("shape", [(520, 1160, 776), (64, 4096, 128), (304, 200, 136), (2048, 512, 1024)])
 def test_float32_output_is_the_unrounded_sum(lib, dtype, shape, monkeypatch):
     """RpbGemm.c_float32: the dB partials of the sharded path.  Checked against float64 at float32 accuracy,
     with A^T read through swapped strides (the dB form), one-slice and K-sliced plans, TMA and register stores."""
