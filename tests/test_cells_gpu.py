@@ -25,6 +25,21 @@ def T(bits, dtype, grad=False):
     return rpb.Tensor.from_numpy(np.ascontiguousarray(bits), dtype=dtype, requires_grad=grad)
 
 
+def chain_close(got, ref, exact, dtype, k, what):
+    """For results behind a CHAIN of nodes.  float32 / float64: the path's bound against the reference.  16-bit types:
+    the reference rounds after every one of its dozen nodes, this library once per stored tensor, so on a handful of
+    elements the two can differ by more than 1e-2 while both sit inside 1e-2 of the exact (float64) chain; accepted
+    is 1e-2 against the reference, or -- where the reference itself is that far from exact -- 1e-2 against the exact
+    chain for both."""
+    if dtype in ("float32", "float64"):
+        return check_close(got, ref, dtype, k, what, tight=False)
+    g, r = f64(got, dtype), f64(ref, dtype)
+    rel = lambda a, b: float(np.linalg.norm(a - b) / (np.linalg.norm(b) or 1.0))
+    if rel(g, r) <= 1e-2:
+        return
+    assert rel(g, exact) <= 1e-2 and rel(r, exact) <= 1e-2, (what, rel(g, r), rel(g, exact), rel(r, exact))
+
+
 @pytest.mark.parametrize("dtype", ["float32", "float64", "float16", "bfloat16"])
 def test_gru_cell_node_vs_reference_fixtures(lib, gru_cell_golden, dtype):
     """op_gru_cell against the reference's own run of GRUCell.forward and its backward down to all six leaves."""
@@ -36,13 +51,16 @@ def test_gru_cell_node_vs_reference_fixtures(lib, gru_cell_golden, dtype):
         bi = T(case["bi"], dtype, True) if bias else None; bh = T(case["bh"], dtype, True) if bias else None
         hn = x.op_gru_cell(wi, h, wh, bi, bh)
         assert hn.shape == (m, hidden)
-        check_close(hn.to_numpy(), case["hn"], dtype, kx + hidden, f"{name} h'", tight=False)
+        w64 = lambda key: f64(case[key], dtype) if key in case else None
+        ex_hn = O.gru_cell_forward(w64("x"), w64("wi"), w64("h"), w64("wh"), w64("bi"), w64("bh"), O.F64)
+        ex = O.gru_cell_backward(w64("g"), w64("x"), w64("wi"), w64("h"), w64("wh"), w64("bi"), w64("bh"), O.F64)
+        chain_close(hn.to_numpy(), case["hn"], ex_hn, dtype, kx + hidden, f"{name} h'")
         hn.backward(T(case["g"], dtype))
-        for t, key, kk in ((x, "dx", 3 * hidden), (wi, "dwi", m), (h, "dh", 3 * hidden), (wh, "dwh", m)):
-            check_close(t.grad.to_numpy(), case[key], dtype, kk, f"{name} {key}", tight=False)
+        for t, key, kk, e in ((x, "dx", 3 * hidden, ex[0]), (wi, "dwi", m, ex[1]), (h, "dh", 3 * hidden, ex[2]), (wh, "dwh", m, ex[3])):
+            chain_close(t.grad.to_numpy(), case[key], e, dtype, kk, f"{name} {key}")
         if bias:
-            check_close(bi.grad.to_numpy(), case["dbi"], dtype, m, f"{name} dbi", tight=False)
-            check_close(bh.grad.to_numpy(), case["dbh"], dtype, m, f"{name} dbh", tight=False)
+            chain_close(bi.grad.to_numpy(), case["dbi"], ex[4], dtype, m, f"{name} dbi")
+            chain_close(bh.grad.to_numpy(), case["dbh"], ex[5], dtype, m, f"{name} dbh")
 
 
 @pytest.mark.parametrize("dtype", ["float32", "float64", "float16", "bfloat16"])
@@ -60,12 +78,14 @@ def test_gru_cell_node_cell_sizes(lib, dtype):
     hn = X.op_gru_cell(WI, H, WH, BI, BH)
     if dtype in ("float16", "bfloat16"):
         assert lib.rpb_last_kernel() in (_lib.KERNEL_UMMA, _lib.KERNEL_UMMA_SPLITK, _lib.KERNEL_SIMT)
-    check_close(hn.to_numpy(), O.gru_cell_forward(x, wi, h, wh, bi, bh, code), dtype, kx + hd, "h'", tight=False)
+    w64 = [f64(v, dtype) for v in (x, wi, h, wh, bi, bh)]
+    chain_close(hn.to_numpy(), O.gru_cell_forward(x, wi, h, wh, bi, bh, code), O.gru_cell_forward(*w64, O.F64), dtype, kx + hd, "h'")
     hn.backward(T(g, dtype))
     ref = O.gru_cell_backward(g, x, wi, h, wh, bi, bh, code)
-    for t, r, kk, what in ((X, ref[0], 3 * hd, "dx"), (WI, ref[1], m, "dwi"), (H, ref[2], 3 * hd, "dh"), (WH, ref[3], m, "dwh"),
-                           (BI, ref[4], m, "dbi"), (BH, ref[5], m, "dbh")):
-        check_close(t.grad.to_numpy(), r, dtype, kk, what, tight=False)
+    ex = O.gru_cell_backward(f64(g, dtype), *w64, O.F64)
+    for t, r, e, kk, what in ((X, ref[0], ex[0], 3 * hd, "dx"), (WI, ref[1], ex[1], m, "dwi"), (H, ref[2], ex[2], 3 * hd, "dh"),
+                              (WH, ref[3], ex[3], m, "dwh"), (BI, ref[4], ex[4], m, "dbi"), (BH, ref[5], ex[5], m, "dbh")):
+        chain_close(t.grad.to_numpy(), r, e, dtype, kk, what)
     # a second step from h' with the same weights: every leaf's gradient is accumulated, not replaced
     first = [f64(t.grad.to_numpy(), dtype) for t in (WI, WH, BI, BH, H)]
     hn2 = X.op_gru_cell(WI, H, WH, BI, BH)
