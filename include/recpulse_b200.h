@@ -391,6 +391,13 @@ void rpb_set_wait_limit_ms(int ms);
  * nobody signals; the wait gives up, status code 9 is recorded and the kernel returns normally.  0 when the
  * kernel completed; rpb_device_status() then reports 9 once and 0 afterwards. */
 int rpb_selftest_bounded_wait(int device_id, long long limit_cycles);
+/* Where a tcgen05 launch's time goes: with tracing on, the first and the last CTA of every such launch stamp the GPU's
+ * nanosecond timer at their milestones -- [0] entry, [1] set-up done, [2] first TMA copy issued, [3] first stage
+ * landed, [4] last MMA committed, [6] last store drained, [5] teardown, and from [8] four stamps per work item (MMA
+ * start, MMA committed, epilogue start, epilogue end) -- into two rows of 64 slots.  rpb_trace_read copies up to
+ * `count` stamps out (synchronise first) and clears them; it returns how many, or -1 when tracing is off. */
+int rpb_trace_enable(int on);
+int rpb_trace_read(unsigned long long* out, int count);
 /* Library version string. */
 const char* rpb_version(void);
 /* The per-device scratch buffer (K-slice partial sums, column-sum partials) grows on demand, which frees

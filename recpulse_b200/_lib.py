@@ -97,6 +97,8 @@ SYMBOLS = {
     "rpb_force_kernel": (None, [C.c_int]),
     "rpb_device_status": (C.c_int, [C.c_int]),
     "rpb_version": (C.c_char_p, []),
+    "rpb_trace_enable": (C.c_int, [C.c_int]),
+    "rpb_trace_read": (C.c_int, [C.POINTER(C.c_ulonglong), C.c_int]),
     "rpb_set_wait_limit_ms": (None, [C.c_int]),
     "rpb_selftest_bounded_wait": (C.c_int, [C.c_int, C.c_longlong]),
     "rpb_tensor_from_host": (TP, [C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_int), C.c_int, C.c_bool]),

@@ -24,6 +24,7 @@
 namespace {
 
 constexpr int MAX_DEVICES = 64;
+constexpr int BAL_MAX_UNITS = 1024;       /* CTAs (pairs) a balanced launch may use: far above any SM count */
 
 struct DeviceState {
     std::atomic<bool> ready{false};
@@ -36,6 +37,9 @@ struct DeviceState {
     bool scratch_used = false;
     bool scratch_pinned = false;          /* handed out inside a stream capture: a graph holds its address */
     int* status = nullptr;                /* this device's word of g_status_words (mapped host memory) */
+    int* bal_flags = nullptr;             /* hand-off counters of the balanced schedule: [slot][rank][ready, done], all
+                                           * zero between launches (the kernel clears what it used) */
+    std::atomic<bool> bal_dirty{false};   /* a kernel gave up part-way: clear the counters before the next use */
     std::mutex mu;                        /* guards the scratch fields: per device, because growing the scratch waits
                                            * for this device, whose work may in turn wait for another thread's GPU */
 };
@@ -101,6 +105,10 @@ struct MapCache {
 };
 MapCache g_maps;
 
+/* Diagnostics: rpb_trace_enable() makes every tcgen05 launch stamp its milestones (rpb_umma::trace_mark) into a
+ * small mapped host buffer that rpb_trace_read() copies out. */
+unsigned long long* g_trace_buffer = nullptr;
+
 /* Bound of one mbarrier wait inside the tcgen05 kernels, in SM clock cycles: about 2 s by default,
  * rpb_set_wait_limit_ms() or RPB_WAIT_LIMIT_MS changes it (a caller with a watchdog of its own wants less). */
 std::atomic<long long> g_wait_limit{0};
@@ -113,9 +121,9 @@ long long wait_limit_cycles() {
     return v;
 }
 uint32_t epilogue_sleep_ns() {
-    static int v = -1;
-    if (v < 0) { const char* e = getenv("RPB_EPI_SLEEP_NS"); v = e ? atoi(e) : 0; if (v < 0) v = 0; }
-    return (uint32_t)v;
+    const char* e = getenv("RPB_EPI_SLEEP_NS");          /* read per launch: lets one process compare settings */
+    const int v = e ? atoi(e) : 0;
+    return (uint32_t)(v < 0 ? 0 : v);
 }
 
 int forced_family() {
@@ -149,6 +157,8 @@ int device_state(int device_id, DeviceState** out) {
                 g_status_words = reinterpret_cast<int*>(w);
             }
             d.status = g_status_words + device_id;
+            RPB_CUDA(cudaMalloc(&d.bal_flags, sizeof(int) * 4 * BAL_MAX_UNITS));
+            RPB_CUDA(cudaMemset(d.bal_flags, 0, sizeof(int) * 4 * BAL_MAX_UNITS));
             RPB_CUDA(cudaEventCreateWithFlags(&d.scratch_free, cudaEventDisableTiming));
             {   /* temporaries for packed operands come from the stream-ordered pool: let it keep freed blocks */
                 const char* e = getenv("RPB_POOL");
@@ -496,14 +506,21 @@ int encode_map(CUtensorMap* map, const void* base, const OperandPlan& o, int mn,
     /* 32-bit operands read MN-major by the tensor cores need the 128-byte swizzle with 32-byte atoms (the only
      * shared-memory layout tcgen05 accepts for transposed tf32); everything else uses the plain 128-byte swizzle */
     const CUtensorMapSwizzle swz = (es == 4 && o.mn_major) ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B;
+    /* L2 promotion of the operand loads: 256 bytes measured best; RPB_L2_PROMO=0..3 (none, 64, 128, 256) for experiments */
+    CUtensorMapL2promotion promo = CU_TENSOR_MAP_L2_PROMOTION_L2_256B;
+    if (const char* e = getenv("RPB_L2_PROMO")) {
+        const int v = atoi(e);
+        promo = v == 0 ? CU_TENSOR_MAP_L2_PROMOTION_NONE : v == 1 ? CU_TENSOR_MAP_L2_PROMOTION_L2_64B
+              : v == 2 ? CU_TENSOR_MAP_L2_PROMOTION_L2_128B : CU_TENSOR_MAP_L2_PROMOTION_L2_256B;
+    }
     MapKey key;
     memset(&key, 0, sizeof(key));
-    key.base = base; key.dt = (int)dt; key.rank = 4; key.swz = 16 + (int)swz;
+    key.base = base; key.dt = (int)dt; key.rank = 4; key.swz = 16 + (int)swz + 64 * (int)promo;
     for (int i = 0; i < 4; ++i) { key.d[i] = dims[i]; key.box[i] = box[i]; }
     for (int i = 0; i < 3; ++i) key.s[i] = strides[i];
     if (g_maps.get(key, map)) return 0;
     CUresult r = g_encode(map, dt, 4, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                          swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                          swz, promo, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r == CUDA_SUCCESS) g_maps.put(key, *map);
     if (r != CUDA_SUCCESS) {
         fprintf(stderr, "recpulse_b200: cuTensorMapEncodeTiled failed (%d) dims=[%llu,%llu,%llu,%llu] strides=[%llu,%llu,%llu]\n",
@@ -665,6 +682,10 @@ int launch_umma(const RpbProblem& p, void* C, const void* A, const void* B, Devi
     a.splits = (a.k_iters + a.iters_per_split - 1) / a.iters_per_split;
     a.total_work = tiles * a.splits;
     a.group_n = raster_group(pair ? d->sm_count / 2 : d->sm_count, tile_m, tile_n, a.tiles_n);
+    if (const char* e = getenv("RPB_GROUP_N")) {            /* experiments: n-tiles per rasterisation group */
+        const int v = atoi(e);
+        if (v >= 1) a.group_n = v < a.tiles_n ? v : a.tiles_n;
+    }
     a.a_batch_mul = pa.batch_mul; a.a_reduce_mul = pa.reduce_mul;
     a.b_batch_mul = pb.batch_mul; a.b_reduce_mul = pb.reduce_mul;
     a.c = C; a.c_row = p.c_row; a.c_batch = p.c_batch; a.accumulate = p.accumulate;
@@ -690,6 +711,7 @@ int launch_umma(const RpbProblem& p, void* C, const void* A, const void* B, Devi
     a.status = d->status;
     a.wait_limit = wait_limit_cycles();
     a.epi_sleep_ns = epilogue_sleep_ns();
+    a.trace = g_trace_buffer;
 
     CUtensorMap ma, mb;
     const CUtensorMapDataType dt = F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
@@ -721,30 +743,78 @@ int launch_umma(const RpbProblem& p, void* C, const void* A, const void* B, Devi
     /* the gate non-linearity lives in the register epilogue (it follows "C += AB" in its only user) */
     if (p.act && a.splits == 1) a.tma_store = 0;
     a.act = a.splits == 1 ? p.act : 0;
+    /* Balanced schedule: with only a few waves of tiles, a last wave that is partly empty costs whole per cents
+     * (4096^3 bf16: 256 tiles on 74 pairs = 3.46 waves run as 3.5 + a reduction launch).  Deal tiles x K-blocks evenly
+     * instead; each CTA (pair) cuts at most two tiles, computes the piece at the end of its range first (fp32, to
+     * scratch) and finishes the piece at the start of its range last, adding its neighbour's partial in the epilogue. */
+    CUtensorMap mp = ma;
+    a.bal = 0;
+    {
+        /* Off by default: measured on bf16 4096^3 it does not beat the K-sliced last wave (96.4 vs 94.6 us per GEMM;
+         * the tiles in flight are spread over the whole output instead of sharing panels, and every CTA pays a
+         * finishing epilogue at the very end).  RPB_BALANCED=1: where the last wave is sparse; 2: wherever it applies. */
+        const char* be = getenv("RPB_BALANCED");
+        const int env = be ? atoi(be) : 0;
+        const long long units = pair ? sms / 2 : sms;
+        if (env && a.splits == 1 && p.batch == 1 && !p.c_f32 && a.tma_store == 1 && units >= 2 &&
+            units <= BAL_MAX_UNITS && tiles > units && a.k_iters >= 16) {
+            const long long waves = (tiles + units - 1) / units;
+            const double idle = (double)(waves * units) / (double)tiles - 1.0;
+            if (env > 1 || (idle >= 0.04 && waves <= 8)) {
+                const size_t bytes = sizeof(float) * (size_t)units * tile_m * tile_n;      /* one fp32 tile per boundary */
+                void* ws = nullptr;
+                if (get_scratch(d, bytes, stream, &ws)) return -1;
+                {
+                    const long long total_units = tiles * a.k_iters;
+                    a.bal = 1;
+                    a.bal_per = total_units / units;
+                    a.bal_extra = (int)(total_units % units);
+                    a.bal_scratch = reinterpret_cast<float*>(ws);
+                    a.bal_flags = d->bal_flags;
+                    a.total_work = units;                    /* one CTA (pair) per range */
+                    if (d->bal_dirty.exchange(false))
+                        RPB_CUDA(cudaMemsetAsync(d->bal_flags, 0, sizeof(int) * 4 * BAL_MAX_UNITS, stream));
+                }
+            }
+        }
+    }
     /* Tail split: if the last wave of tiles would keep fewer than half of the CTAs (or CTA pairs) busy, cut
      * its tiles along K so that the wave is short instead of sparse (4096^3: 256 tiles on 74 pairs = 3 waves +
      * 34 tiles; with two K slices each the run takes 3.5 tile times instead of 4). */
-    CUtensorMap mp = ma;
     a.tail_begin = a.total_work; a.tail_splits = 1; a.tail_iters = a.k_iters;
     {
-        static int env = -1;
-        if (env < 0) { const char* e = getenv("RPB_TAIL_SPLIT"); env = e ? atoi(e) : 1; }
+        const char* te = getenv("RPB_TAIL_SPLIT");        /* 0: off; 2: from 16 K blocks per tile on (tests) */
+        const int env = te ? atoi(te) : 1;
         const long long units = pair ? sms / 2 : sms;
         const long long rem = units > 0 ? tiles % units : 0;
-        /* the extra reduction launch costs ~4 us: measured break-even at about 96 K blocks per tile */
-        if (env && a.splits == 1 && !p.c_f32 && p.batch == 1 && a.tma_store == 1 && tiles > units && rem > 0 && rem * 2 <= units &&
-            a.k_iters >= (env > 1 ? 16 : 96)) {
+        const char* fe = getenv("RPB_TAIL_FUSE");
+        const bool may_fuse = !(fe && atoi(fe) == 0) && rem * 64 <= 4 * BAL_MAX_UNITS;
+        if (env && !a.bal && a.splits == 1 && !p.c_f32 && p.batch == 1 && a.tma_store == 1 && tiles > units && rem > 0 && rem * 2 <= units) {
             long long ts = units / rem;
             if (ts > 4) ts = 4;
             if (ts > a.k_iters / 8) ts = a.k_iters / 8;
+            /* Three or four slices need a reduction launch (~4 us): measured break-even at about 96 K blocks per tile.
+             * Two slices are finished inside the kernel and pay from about 32 K blocks on (bf16 4096^3: 64). */
+            const int min_iters = env > 1 ? 16 : ((ts == 2 && may_fuse) ? 32 : 96);
+            if (a.k_iters < min_iters) ts = 1;
             if (ts >= 2) {
                 const int per = (int)((a.k_iters + ts - 1) / ts);
                 ts = (a.k_iters + per - 1) / per;
                 const size_t bytes = sizeof(float) * (size_t)rem * ts * tile_m * tile_n;
                 void* ws = nullptr;
                 if (get_scratch(d, bytes, stream, &ws)) return -1;
-                if (encode_store_map(&mp, ws, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, tile_n, tile_m, rem * ts, tile_n,
-                                     (long long)tile_m * tile_n, 32) == 0) {
+                /* two slices: finished inside the kernel (whichever slice is second adds the first one's sums);
+                 * more: fp32 tiles through map_p and a reduction launch */
+                if (ts == 2 && may_fuse) {
+                    a.tail_fuse = 1;
+                    a.bal_scratch = reinterpret_cast<float*>(ws);
+                    a.bal_flags = d->bal_flags;
+                    a.tail_begin = tiles - rem; a.tail_splits = 2; a.tail_iters = per;
+                    a.total_work = a.tail_begin + rem * 2;
+                    if (d->bal_dirty.exchange(false))
+                        RPB_CUDA(cudaMemsetAsync(d->bal_flags, 0, sizeof(int) * 4 * BAL_MAX_UNITS, stream));
+                } else if (encode_store_map(&mp, ws, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, tile_n, tile_m, rem * ts, tile_n,
+                                            (long long)tile_m * tile_n, 32) == 0) {
                     a.partial = reinterpret_cast<float*>(ws);
                     a.tail_begin = tiles - rem; a.tail_splits = (int)ts; a.tail_iters = per;
                     a.total_work = a.tail_begin + rem * ts;
@@ -764,7 +834,8 @@ int launch_umma(const RpbProblem& p, void* C, const void* A, const void* B, Devi
     else if (BN == 128) rc = launch_umma_bn<T, 128>(pa.mn_major, pb.mn_major, ma, mb, mc, mp, a, grid, stream);
     else rc = launch_umma_bn<T, 256>(pa.mn_major, pb.mn_major, ma, mb, mc, mp, a, grid, stream);
     if (rc) return -1;
-    if (a.tail_splits > 1) {
+    if ((a.bal || a.tail_fuse) && release_scratch(d, stream)) return -1;
+    if (a.tail_splits > 1 && !a.tail_fuse) {
         const int rem = (int)(tiles - a.tail_begin);
         RPB_CUDA(rpb_launch(rpb_umma::tail_reduce_kernel<T>, dim3(rem, tile_m), dim3(tile_n / 4), 0, stream, 1,
                             (const float*)a.partial, reinterpret_cast<T*>(C), reinterpret_cast<const T*>(p.bias), p.m, p.n,
@@ -1283,6 +1354,7 @@ int rpb_take_status(int device_id) {
     const int v = *w;
     if (v != 0) {
         *w = 0;
+        g_dev[device_id].bal_dirty.store(true);
         fprintf(stderr, "recpulse_b200: a bounded wait inside the tcgen05 kernel ran out on device %d (code %d); the "
                         "result is invalid\n", device_id, v);
     }
@@ -1298,7 +1370,7 @@ int rpb_device_status(int device_id) {
     if (device_state(device_id, &d) == 0 && cudaDeviceSynchronize() == cudaSuccess) {
         volatile int* w = d->status;
         v = *w;
-        if (v != 0) *w = 0;
+        if (v != 0) { *w = 0; d->bal_dirty.store(true); }
     }
     if (prev != device_id) cudaSetDevice(prev);
     return v;
@@ -1307,6 +1379,28 @@ int rpb_device_status(int device_id) {
 void rpb_set_wait_limit_ms(int ms) { g_wait_limit.store(ms > 0 ? (long long)ms * 2000000ll : rpb_umma::WAIT_LIMIT_CYCLES); }
 
 void rpb_count_launches(int n) { g_launches += (unsigned long long)n; }
+
+int rpb_trace_enable(int on) {
+    if (on && !g_trace_buffer) {
+        void* w = nullptr;
+        RPB_CUDA(cudaHostAlloc(&w, sizeof(unsigned long long) * 2 * rpb_umma::TRACE_SLOTS, cudaHostAllocPortable | cudaHostAllocMapped));
+        memset(w, 0, sizeof(unsigned long long) * 2 * rpb_umma::TRACE_SLOTS);
+        g_trace_buffer = reinterpret_cast<unsigned long long*>(w);
+    } else if (!on && g_trace_buffer) {
+        cudaDeviceSynchronize();
+        cudaFreeHost(g_trace_buffer);
+        g_trace_buffer = nullptr;
+    }
+    return 0;
+}
+
+int rpb_trace_read(unsigned long long* out, int count) {
+    if (!out || !g_trace_buffer || count <= 0) return -1;
+    const int n = count < 2 * rpb_umma::TRACE_SLOTS ? count : 2 * rpb_umma::TRACE_SLOTS;
+    memcpy(out, g_trace_buffer, sizeof(unsigned long long) * n);
+    memset(g_trace_buffer, 0, sizeof(unsigned long long) * 2 * rpb_umma::TRACE_SLOTS);
+    return n;
+}
 
 /* Runs the kernels' bounded wait on a barrier that nobody will ever signal, with a short limit: the wait must
  * give up, leave its code in the device's status word and let the kernel return.  One CTA of one warp, no TMA, no

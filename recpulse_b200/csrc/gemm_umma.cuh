@@ -51,6 +51,8 @@ template <typename T> struct Elem {
 };
 constexpr long long WAIT_LIMIT_CYCLES = 4000000000ll;   /* default bound of one wait: about 2 s of SM clock */
 constexpr int SMEM_LIMIT = 227 * 1024;
+constexpr int TRACE_SLOTS = 64;        /* 0 entry, 1 set-up done, 2 first TMA issued, 3 first stage landed, 4 last MMA committed,
+                                        * 5 kernel end; 8 + 4 i .. : item i  MMA start / MMA committed / epilogue start / epilogue end */
 
 template <int BN, bool SPLIT = false> struct Config {
     static constexpr int A_BYTES = BLOCK_M * 128;
@@ -92,6 +94,27 @@ struct Args {
     uint32_t a_kstep, b_kstep;           /* descriptor advance per UMMA_K, in 16-byte units */
     int* status;
     int act;               /* 1: LSTM gate non-linearities on the finished sum (register epilogue, no K slices) */
+    /* Balanced schedule (bal != 0; needs splits == batch == 1 and at least one tile per CTA or pair): the
+     * tiles x K-block units are dealt evenly and contiguously, bal_per units to every CTA (pair) and one more to the
+     * first bal_extra of them.  A range starts / ends inside at most one tile each.  Of the two pieces of a cut tile
+     * the SHORTER one is computed first thing by its holder and goes as an fp32 tile to the scratch slot of that
+     * boundary; the LONGER one is computed last by the neighbour, whose epilogue adds the slot before it writes C.
+     * The two are handed over through bal_flags: per slot and CTA rank a `ready` count (the writer's epilogue warps)
+     * and a `done` count (the reader's; the last one resets both). */
+    /* tail_fuse != 0 (tail_splits == 2): the two K slices of a tail tile run side by side in the last wave; per
+     * epilogue warp, whichever slice reaches its epilogue first leaves its fp32 sums in bal_scratch (slot = tail tile)
+     * and the other adds them and writes C -- a + b in either order, so the result does not depend on who was first.
+     * bal_flags holds [tail tile][rank][warp][ticket, ready]; the finishing warp clears both. */
+    int tail_fuse;
+    /* Diagnostics: when not null, CTA 0 and the last CTA stamp %globaltimer (ns) at the kernel's milestones into
+     * trace[cta == 0 ? 0 : 1][TRACE_SLOTS] (see trace_mark): where a launch's fixed cost goes. */
+    unsigned long long* trace;
+    int bal;
+    long long bal_per;
+    int bal_extra;
+    float* bal_scratch;         /* fp32 partial tiles, one per boundary between neighbours: [slot][CTA rank][lane
+                                 * quarter][32-column chunk][8][32 lanes] float4, so that a warp's accesses are contiguous */
+    int* bal_flags;             /* [slots][2 ranks][ready, done] */
     long long wait_limit;  /* bound of every mbarrier wait, in SM clock cycles */
     uint32_t epi_sleep_ns; /* back-off between polls of the epilogue warps' wait for a finished accumulator (0 = spin) */
     int c_f32;             /* 1: the output is packed float32 [batch][m][n] (unrounded sums of 16-bit operands); the
@@ -328,6 +351,14 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
     nt = g * group_n + (r - mt * gn);
 }
 
+__device__ __forceinline__ void trace_mark(unsigned long long* trace, int slot) {
+    if (trace && slot < TRACE_SLOTS && (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1)) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        trace[(blockIdx.x == 0 ? 0 : TRACE_SLOTS) + slot] = t;
+    }
+}
+
 /* ------------------------------------------------------------------ kernel */
 
 /* PAIR = false: one CTA per output tile of 128 x BN  (tcgen05 cta_group::1).
@@ -368,6 +399,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) trace_mark(args.trace, 0);
     uint32_t cta_rank = 0;
     if (PAIR) asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(cta_rank));
     const bool leader = cta_rank == 0;
@@ -383,7 +415,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
         if (args.tma_store) asm volatile("prefetch.tensormap [%0];" ::"l"(&map_c) : "memory");
-        if (args.tail_splits > 1) asm volatile("prefetch.tensormap [%0];" ::"l"(&map_p) : "memory");
+        if (args.tail_splits > 1 || args.bal) asm volatile("prefetch.tensormap [%0];" ::"l"(&map_p) : "memory");
     }
     if (warp == 1) {
         if (PAIR) {
@@ -401,6 +433,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     if (PAIR) { __syncwarp(); cluster_sync(); }   /* the peer's barriers are initialised before anyone signals them */
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    if (threadIdx.x == 0) trace_mark(args.trace, 1);
     rpb_pdl_trigger();          /* the next kernel in the stream may begin its own set-up */
     rpb_pdl_wait();             /* everything below touches memory the previous kernel may still be writing */
 
@@ -411,25 +444,72 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     /* Work items are dealt round-robin, so the items in flight are consecutive indices.  Within one
      * (batch, split) the output tiles are walked in column groups of `group_n` n-tiles, n fastest:
      * the tiles in flight then cover a near-square block of C and share their A row panels and B
-     * column panels in L2 instead of streaming all of A once per wave. */
-    auto decode = [&](long long w, int& mt, int& nt, int& split, int& bz) {
+     * column panels in L2 instead of streaming all of A once per wave.
+     * kind 0: a whole tile (or K slice when splits > 1); kind 1: a piece whose fp32 partial goes to scratch slot
+     * `slot` through map_p (a K slice of a tail tile, or the head piece of the balanced schedule); kind 2: the tail
+     * piece of the balanced schedule, finished with the partial in `slot`. */
+    struct Item { int mt, nt, split, bz, it0, it1, kind, slot; };
+    const long long unit_id = PAIR ? blockIdx.x / 2 : blockIdx.x;     /* this CTA's (pair's) index */
+    auto next_item = [&](long long& w, int& phase, Item& o) -> bool {
+        if (args.bal) {
+            /* This CTA's (pair's) range [s, e) of tile x K-block units starts inside tile ta (at K block ka) and ends
+             * inside tile tb (at kb).  A cut tile is FINISHED by whoever holds its longer piece, as that one's last
+             * work; the shorter piece is computed first thing by its holder and travels as fp32 through slot =
+             * index of the boundary between the two neighbours.  Order: partial pieces, whole tiles, finishing pieces. */
+            const long long s = unit_id * args.bal_per + min(unit_id, (long long)args.bal_extra);
+            const long long e = s + args.bal_per + (unit_id < args.bal_extra ? 1 : 0);
+            const long long ta = s / args.k_iters, tb = e / args.k_iters;
+            const int ka = (int)(s - ta * args.k_iters), kb = (int)(e - tb * args.k_iters);
+            const bool tail_fin = ka != 0 && 2 * ka <= args.k_iters;        /* my piece [ka, K) is the longer one */
+            const bool head_fin = kb != 0 && 2 * kb > args.k_iters;         /* my piece [0, kb) is the longer one */
+            o.split = 0; o.bz = 0;
+            for (;;) {
+                const int ph = phase++;
+                if (ph == 0) { w = ta + (ka ? 1 : 0); }
+                if ((ph == 0 && ka && !tail_fin) || (ph == 3 && ka && tail_fin)) {          /* piece [ka, K) of tile ta */
+                    tile_coords((int)ta, args.tiles_m, args.tiles_n, args.group_n, o.mt, o.nt);
+                    o.it0 = ka; o.it1 = args.k_iters; o.kind = ph == 0 ? 1 : 2; o.slot = (int)unit_id - 1;
+                    return true;
+                }
+                if ((ph == 1 && kb && !head_fin) || (ph == 4 && kb && head_fin)) {          /* piece [0, kb) of tile tb */
+                    tile_coords((int)tb, args.tiles_m, args.tiles_n, args.group_n, o.mt, o.nt);
+                    o.it0 = 0; o.it1 = kb; o.kind = ph == 1 ? 1 : 2; o.slot = (int)unit_id;
+                    return true;
+                }
+                if (ph == 2) {
+                    if (w < tb) {
+                        tile_coords((int)w, args.tiles_m, args.tiles_n, args.group_n, o.mt, o.nt);
+                        o.it0 = 0; o.it1 = args.k_iters; o.kind = 0; o.slot = 0;
+                        ++w;
+                        phase = 2;                       /* stay in this phase until the whole tiles are done */
+                        return true;
+                    }
+                }
+                if (ph >= 5) return false;
+            }
+        }
+        if (w >= args.total_work) return false;
         if (w >= args.tail_begin) {                 /* K slice of a tail tile (only with splits == batch == 1) */
             const long long j = w - args.tail_begin;
-            split = (int)(j % args.tail_splits);
-            bz = 0;
-            tile_coords((int)(args.tail_begin + j / args.tail_splits), args.tiles_m, args.tiles_n, args.group_n, mt, nt);
-            return;
+            o.split = (int)(j % args.tail_splits);
+            o.bz = 0;
+            tile_coords((int)(args.tail_begin + j / args.tail_splits), args.tiles_m, args.tiles_n, args.group_n, o.mt, o.nt);
+            o.it0 = o.split * args.tail_iters;
+            o.it1 = min(o.it0 + args.tail_iters, args.k_iters);
+            o.kind = 1; o.slot = (int)j;
+        } else {
+            const int tiles_mn = args.tiles_m * args.tiles_n;
+            long long q = w;
+            const int t = (int)(q % tiles_mn); q /= tiles_mn;
+            o.split = (int)(q % args.splits);
+            o.bz = (int)(q / args.splits);
+            tile_coords(t, args.tiles_m, args.tiles_n, args.group_n, o.mt, o.nt);
+            o.it0 = o.split * args.iters_per_split;
+            o.it1 = min(o.it0 + args.iters_per_split, args.k_iters);
+            o.kind = 0; o.slot = 0;
         }
-        const int tiles_mn = args.tiles_m * args.tiles_n;
-        const int t = (int)(w % tiles_mn); w /= tiles_mn;
-        split = (int)(w % args.splits);
-        bz = (int)(w / args.splits);
-        tile_coords(t, args.tiles_m, args.tiles_n, args.group_n, mt, nt);
-    };
-    auto k_range = [&](long long w, int split, int& it0, int& it1) {
-        const int per = w >= args.tail_begin ? args.tail_iters : args.iters_per_split;
-        it0 = split * per;
-        it1 = min(it0 + per, args.k_iters);
+        w += work_step;
+        return true;
     };
 
     if (warp == 0) {
@@ -439,10 +519,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             constexpr bool REMOTE_BAR = PAIR && !SPLIT;
             int stage = 0; uint32_t parity = 1u;                      /* empty barriers: first pass falls through */
             uint32_t sa = smem_base, eb = empty_bar(0), fb = full_bar(0);
-            bool alive = true;
-            for (long long w = work_begin; alive && w < args.total_work; w += work_step) {
-                int mt, nt, split, bz; decode(w, mt, nt, split, bz);
-                int it0, it1; k_range(w, split, it0, it1);
+            bool alive = true, traced = false;
+            long long w = work_begin; int phase_w = 0; Item item;
+            while (alive && next_item(w, phase_w, item)) {
+                const int mt = item.mt, nt = item.nt, bz = item.bz, it0 = item.it0, it1 = item.it1;
                 const int row0 = mt * TILE_M + (int)cta_rank * BLOCK_M;     /* this CTA's rows of A */
                 const int col0 = nt * ACC_N + (int)cta_rank * BN;           /* this CTA's columns of B */
                 const int r0 = it0 / args.k_blocks;
@@ -451,6 +531,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                 const int a_b = bz * args.a_batch_mul, b_b = bz * args.b_batch_mul;
                 for (int left = it1 - it0; left > 0; --left) {
                     if (!mbar_wait_warp(eb, parity, abort_flag, args.status, 1, args.wait_limit)) { alive = false; break; }
+                    if (args.trace && !traced && lane == 0) { trace_mark(args.trace, 2); }
+                    traced = true;
                     if (elect_one()) {
                         const uint32_t sb = sa + Cfg::A_BYTES;
                         uint32_t tb = fb;
@@ -499,18 +581,20 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             uint32_t wb = SPLIT ? ready_bar(0) : full_bar(0), eb = empty_bar(0);
             const uint32_t a_kstep = args.a_kstep, b_kstep = args.b_kstep, idesc = args.idesc;
             bool alive = true;
-            for (long long w = work_begin; alive && w < args.total_work; w += work_step, ++local_tile) {
-                int mt, nt, split, bz; decode(w, mt, nt, split, bz);
-                int it0, it1; k_range(w, split, it0, it1);
+            long long w = work_begin; int phase_w = 0; Item item;
+            for (; alive && next_item(w, phase_w, item); ++local_tile) {
+                const int it0 = item.it0, it1 = item.it1;
                 const uint32_t ab = local_tile & 1u;
                 const uint32_t acc_phase = (local_tile >> 1) & 1u;
                 if (!mbar_wait_warp(tempty_bar(ab), acc_phase ^ 1u, abort_flag, args.status, 2, args.wait_limit)) { alive = false; break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + ab * ACC_N;
                 uint32_t acc = 0u;                                  /* the first instruction of a tile overwrites */
+                if (args.trace && lane == 0) trace_mark(args.trace, 8 + 4 * (int)local_tile);
                 for (int left = it1 - it0; left > 0; --left) {
                     /* float32: the stage is usable once the split warps (of both CTAs of a pair) are done with it */
                     if (!mbar_wait_warp(wb, phase, abort_flag, args.status, 3, args.wait_limit)) { alive = false; break; }
+                    if (args.trace && lane == 0 && local_tile == 0 && left == it1 - it0) trace_mark(args.trace, 3);
                     tc_fence_after();
                     if (elect_one()) {
 #pragma unroll
@@ -538,6 +622,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                 }
                 if (alive && elect_one()) umma_commit<PAIR>(tfull_bar(ab));  /* accumulator complete */
                 __syncwarp();
+                if (args.trace && lane == 0) { trace_mark(args.trace, 9 + 4 * (int)local_tile); trace_mark(args.trace, 4); }
             }
         }
     } else if (SPLIT && warp >= 2 + EPI_WARPS) {
@@ -546,9 +631,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         const int st = (int)threadIdx.x - (2 + EPI_WARPS) * 32;
         int stage = 0; uint32_t phase = 0;
         bool alive = true;
-        for (long long w = work_begin; alive && w < args.total_work; w += work_step) {
-            int mt, nt, split, bz; decode(w, mt, nt, split, bz);
-            int it0, it1; k_range(w, split, it0, it1);
+        long long w = work_begin; int phase_w = 0; Item item;
+        while (alive && next_item(w, phase_w, item)) {
+            const int it0 = item.it0, it1 = item.it1;
             for (int it = it0; it < it1; ++it) {
                 if (!mbar_wait(full_bar(stage), phase, abort_flag, args.status, 5, args.wait_limit)) { alive = false; break; }
                 const uint32_t base = smem_base + stage * Cfg::STAGE_BYTES;
@@ -582,15 +667,71 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         uint32_t local_tile = 0;
         bool alive = true;
         T* cT = reinterpret_cast<T*>(args.c);
-        for (long long w = work_begin; alive && w < args.total_work; w += work_step, ++local_tile) {
-            int mt, nt, split, bz; decode(w, mt, nt, split, bz);
+        long long w = work_begin; int phase_w = 0; Item item;
+        for (; alive && next_item(w, phase_w, item); ++local_tile) {
+            const int mt = item.mt, nt = item.nt, split = item.split, bz = item.bz;
             const uint32_t ab = local_tile & 1u;
             const uint32_t acc_phase = (local_tile >> 1) & 1u;
+            if (args.trace && warp == 2 && lane == 0 && local_tile > 0) trace_mark(args.trace, 11 + 4 * (int)(local_tile - 1));
             if (!mbar_wait(tfull_bar(ab), acc_phase, abort_flag, args.status, 4, args.wait_limit, args.epi_sleep_ns)) { alive = false; break; }
             __syncwarp();
             tc_fence_after();
+            if (args.trace && warp == 2 && lane == 0) trace_mark(args.trace, 10 + 4 * (int)local_tile);
             const int row = mt * TILE_M + (int)cta_rank * BLOCK_M + quarter * 32 + lane;
             const bool row_ok = row < args.m;
+            /* How this warp treats the item.  0: output tile.  1: fp32 piece through map_p (K slice of a tail tile,
+             * reduced by a second kernel).  2: finish a cut tile with the neighbour's partial (balanced schedule).
+             * 3: leave an fp32 partial in bal_scratch (balanced: the shorter piece; fused tail: the first slice to get
+             * here).  4: fused tail, second slice to get here: finish with the first one's partial. */
+            int mode = item.kind;
+            int* tk = nullptr;
+            if (args.bal && item.kind == 1) mode = 3;
+            if (args.tail_fuse && item.kind == 1) {
+                tk = args.bal_flags + ((((long long)(item.slot >> 1) * 2 + (int)cta_rank) * EPI_WARPS) + (warp - 2)) * 2;
+                int ticket = 0;
+                if (lane == 0) ticket = atomicAdd(tk, 1);
+                ticket = __shfl_sync(0xffffffffu, ticket, 0);
+                mode = ticket == 0 ? 3 : 4;
+            }
+            const long long pslot = args.tail_fuse ? (item.slot >> 1) : item.slot;
+            if (mode == 3) {
+                /* fp32 sums to the slot, in the layout the finishing warp reads them in (same lane quarter, 32-column
+                 * chunk, lane: contiguous 512 bytes per warp access).  The fused tail uses the finishing warp's own
+                 * column assignment, so that the hand-over is warp to warp. */
+                float4* dst = reinterpret_cast<float4*>(args.bal_scratch) +
+                              ((pslot * 2 + (int)cta_rank) * 4 + quarter) * (ACC_N / 32) * 256 + lane;
+                const int row_warp = mt * TILE_M + (int)cta_rank * BLOCK_M + quarter * 32;
+                const int span = (args.tail_fuse && !SPLIT) ? 64 : 32;          /* columns per loop step */
+#pragma unroll 1
+                for (int c0 = half * span; c0 < ACC_N; c0 += 2 * span) {
+#pragma unroll 1
+                    for (int cc = c0; cc < c0 + span; cc += 32) {
+                        uint32_t v[32];
+                        __syncwarp();
+                        tmem_load_32(tmem_base + ab * ACC_N + cc + lane_field, v);
+                        if (nt * ACC_N + cc >= args.n || row_warp >= args.m) continue;      /* warp-uniform */
+                        float4* d4 = dst + (cc / 32) * 256;
+#pragma unroll
+                        for (int q = 0; q < 8; ++q)
+                            __stcg(d4 + q * 32, make_float4(__uint_as_float(v[4 * q]), __uint_as_float(v[4 * q + 1]),
+                                                            __uint_as_float(v[4 * q + 2]), __uint_as_float(v[4 * q + 3])));
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) {
+                    if (PAIR) mbar_arrive_cluster(cluster_addr(tempty_bar(ab), 0));
+                    else mbar_arrive(tempty_bar(ab));
+                    __threadfence();                      /* the warp's stores (ordered before by the warp barrier) are published */
+                    if (tk) {
+                        asm volatile("st.release.gpu.global.s32 [%0], 1;" ::"l"(tk + 1) : "memory");
+                    } else {
+                        int* f = args.bal_flags + ((long long)item.slot * 2 + (int)cta_rank) * 2;
+                        asm volatile("red.release.gpu.global.add.s32 [%0], 1;" ::"l"(f) : "memory");
+                    }
+                }
+                continue;
+            }
             if (args.tma_store) {
                 /* Each warp stages 32 rows x 128 bytes in the 128-byte swizzle the store's tensor map
                  * expects (16-byte chunk c of row r at position c ^ (r & 7)) and one lane hands the box to
@@ -600,11 +741,43 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                 const uint32_t buf = store_base + (uint32_t)(warp - 2) * Cfg::STORE_BUF_BYTES;
                 const uint32_t my_row = (uint32_t)lane * 128u;
                 const uint32_t sw = (uint32_t)lane & 7u;
-                const bool tail_item = w >= args.tail_begin;
+                const bool tail_item = mode == 1;
                 const bool partial_out = args.splits > 1 || tail_item || args.c_f32;
                 const bool wide = partial_out || SPLIT;                     /* rows of fp32: 32 columns per 128 bytes */
                 const int cols_per_box = wide ? 32 : 64;                    /* 128 bytes of fp32 or of 16-bit T */
                 const int zc = partial_out ? split * args.batch + bz : bz;
+                /* balanced schedule, finishing piece: the other piece of this tile was computed by the previous CTA
+                 * (pair) at the very start of its run; its rows of the partial tile are complete once its eight
+                 * epilogue warps have counted themselves in */
+                const float4* part = nullptr;
+                int* flag = nullptr;
+                if (mode == 2 || mode == 4) {
+                    /* balanced: all eight warps of the neighbour's CTA have counted in; fused tail: this warp's partner */
+                    const int* watch = mode == 2 ? args.bal_flags + ((long long)item.slot * 2 + (int)cta_rank) * 2 : tk + 1;
+                    const int need = mode == 2 ? EPI_WARPS : 1;
+                    if (mode == 2) flag = const_cast<int*>(watch);
+                    bool ok = true;
+                    if (lane == 0) {
+                        const long long t0 = clock64();
+                        int seen = 0;
+                        for (uint32_t i = 0;; ++i) {
+                            asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(watch) : "memory");
+                            if (seen >= need) break;
+                            __nanosleep(100);
+                            if ((i & 63u) == 63u && (*abort_flag || clock64() - t0 > args.wait_limit)) { ok = false; break; }
+                        }
+                        if (!ok) {
+                            *abort_flag = 1;
+                            volatile int* st = args.status;
+                            if (*st == 0) *st = 6;
+                            __threadfence_system();
+                        }
+                    }
+                    ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+                    if (!ok) { alive = false; break; }
+                    part = reinterpret_cast<const float4*>(args.bal_scratch) +
+                           ((pslot * 2 + (int)cta_rank) * 4 + quarter) * (ACC_N / 32) * 256 + lane;
+                }
 #pragma unroll 1
                 for (int c0 = half * cols_per_box; c0 < ACC_N; c0 += 2 * cols_per_box) {
                     const int col = nt * ACC_N + c0;
@@ -615,6 +788,33 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                     if (!wide) tmem_load_32_nowait(tmem_base + ab * ACC_N + c0 + 32 + lane_field, v2);
                     tmem_load_wait();
                     if (col >= args.n || row_warp >= args.m) continue;      /* warp-uniform */
+                    if (part) {                                             /* the other piece's sums for the same elements */
+                        if constexpr (!SPLIT) {
+                            const float4* p4 = part + (c0 / 32) * 256;
+#pragma unroll
+                            for (int q = 0; q < 8; ++q) {
+                                const float4 x = __ldcg(p4 + q * 32), y = __ldcg(p4 + 256 + q * 32);
+                                v[4 * q] = __float_as_uint(__uint_as_float(v[4 * q]) + x.x);
+                                v[4 * q + 1] = __float_as_uint(__uint_as_float(v[4 * q + 1]) + x.y);
+                                v[4 * q + 2] = __float_as_uint(__uint_as_float(v[4 * q + 2]) + x.z);
+                                v[4 * q + 3] = __float_as_uint(__uint_as_float(v[4 * q + 3]) + x.w);
+                                v2[4 * q] = __float_as_uint(__uint_as_float(v2[4 * q]) + y.x);
+                                v2[4 * q + 1] = __float_as_uint(__uint_as_float(v2[4 * q + 1]) + y.y);
+                                v2[4 * q + 2] = __float_as_uint(__uint_as_float(v2[4 * q + 2]) + y.z);
+                                v2[4 * q + 3] = __float_as_uint(__uint_as_float(v2[4 * q + 3]) + y.w);
+                            }
+                        } else {
+                            const float4* p4 = part + (c0 / 32) * 256;
+#pragma unroll
+                            for (int q = 0; q < 8; ++q) {
+                                const float4 x = __ldcg(p4 + q * 32);
+                                v[4 * q] = __float_as_uint(__uint_as_float(v[4 * q]) + x.x);
+                                v[4 * q + 1] = __float_as_uint(__uint_as_float(v[4 * q + 1]) + x.y);
+                                v[4 * q + 2] = __float_as_uint(__uint_as_float(v[4 * q + 2]) + x.z);
+                                v[4 * q + 3] = __float_as_uint(__uint_as_float(v[4 * q + 3]) + x.w);
+                            }
+                        }
+                    }
                     if (args.bias && !partial_out) {
                         add_bias_32<T>(v, reinterpret_cast<const T*>(args.bias), col, args.n);
                         if (!wide) add_bias_32<T>(v2, reinterpret_cast<const T*>(args.bias), col + 32, args.n);
@@ -643,8 +843,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   /* generic writes -> async proxy */
                     __syncwarp();
                     if (lane == 0) {
-                        if (tail_item)   /* compact scratch: [tail slice][row inside the tile][column inside the tile] */
-                            tma_store_3d(&map_p, buf, c0, (int)cta_rank * BLOCK_M + quarter * 32, (int)(w - args.tail_begin));
+                        if (tail_item)   /* compact scratch: [slot][row inside the tile][column inside the tile] */
+                            tma_store_3d(&map_p, buf, c0, (int)cta_rank * BLOCK_M + quarter * 32, item.slot);
                         else
                             tma_store_3d(&map_c, buf, col, row_warp, zc);
                     }
@@ -654,6 +854,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                 if (lane == 0) {
                     if (PAIR) mbar_arrive_cluster(cluster_addr(tempty_bar(ab), 0));
                     else mbar_arrive(tempty_bar(ab));
+                }
+                if (flag) {
+                    /* this warp has read its rows of the partial; the last of the eight readers clears both counts
+                     * for the next launch (no memset between launches, and a replayed CUDA graph stays correct) */
+                    __syncwarp();
+                    if (lane == 0) {
+                        __threadfence();
+                        if (atomicAdd(flag + 1, 1) == EPI_WARPS - 1) { flag[1] = 0; __threadfence(); atomicExch(flag, 0); }
+                    }
+                }
+                if (mode == 4) {                  /* both slices of this warp's part are done: ticket and flag back to zero */
+                    __syncwarp();
+                    if (lane == 0) { __threadfence(); atomicExch(tk + 1, 0); atomicExch(tk, 0); }
                 }
                 continue;
             }
@@ -742,7 +955,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     }
 
     if (warp >= 2 && lane == 0 && args.tma_store) tma_store_wait_all();   /* staged rows have left shared memory */
+    if (args.trace && warp == 2 && lane == 0) trace_mark(args.trace, 6);
 
+    if (threadIdx.x == 0) trace_mark(args.trace, 5);
     /* teardown: if a wait gave up, let copies that are still in flight land first */
     if (*abort_flag) {
         for (int i = 0; i < 2000; ++i) __nanosleep(1000);

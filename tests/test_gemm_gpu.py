@@ -429,3 +429,93 @@ def test_results_do_not_depend_on_scheduling(lib):
     first = run_ex(lib, "bfloat16", a, b)
     for _ in range(3):
         assert np.array_equal(run_ex(lib, "bfloat16", a, b), first)
+
+
+@pytest.mark.parametrize("dtype", ["bfloat16", "float16", "float32"])
+@pytest.mark.parametrize("plan", ["64,1,0", "128,1,0", "256,1,0", "64,1,1", "128,1,1"])
+def test_balanced_schedule_gives_the_same_product(lib, dtype, plan, monkeypatch):
+    """The balanced schedule deals tiles x K-blocks evenly over the CTAs (pairs): tiles are cut along K, the head
+    piece goes through an fp32 scratch tile and the neighbour finishes it in its epilogue.  Forced here on ragged
+    shapes with few SMs (max_sms), so that every CTA cuts tiles at both ends of its range, for every tile shape;
+    checked against float64 and for run-to-run determinism."""
+    monkeypatch.setenv("RPB_UMMA_PLAN", plan)
+    monkeypatch.setenv("RPB_BALANCED", "2")
+    rng = np.random.default_rng(3000 + 100 * CODE[dtype] + PLANS.index(plan))
+    lib.rpb_force_kernel(_lib.KERNEL_UMMA)
+    try:
+        for (m, k, n, sms) in [(1000, 1160, 1544, 6), (1300, 2056, 1100, 20), (2048, 1024, 2048, 14)]:
+            a = rand_operand(rng, (m, k), dtype, scale=1 / np.sqrt(k)); b = rand_operand(rng, (k, n), dtype)
+            bias = rand_operand(rng, (n,), dtype)
+            ref = f64(a, dtype) @ f64(b, dtype) + f64(bias, dtype)
+            ta, tb, tbias = dev(a, dtype), dev(b, dtype), dev(bias, dtype)
+            outs = []
+            for trial in range(2):
+                tc = dev(np.zeros((m, n), O.storage(CODE[dtype])), dtype)
+                g = rpb.RpbGemm(); lib.rpb_gemm_packed(C.byref(g), m, k, n)
+                g.max_sms = sms; g.bias = tbias.data_ptr
+                assert lib.rp_matmul_ex(C.c_void_p(tc.data_ptr), C.c_void_p(ta.data_ptr), C.c_void_p(tb.data_ptr), C.byref(g),
+                                        CODE[dtype], 0, None) == 0
+                assert lib.rpb_last_kernel() == _lib.KERNEL_UMMA
+                outs.append(tc.to_numpy())
+            assert np.array_equal(outs[0], outs[1])
+            got = f64(outs[0], dtype)
+            if dtype == "float32":      # the path's float32 bound: max |err| / (sqrt(K) rms)
+                err = np.abs(got - ref).max() / (np.sqrt(k) * np.sqrt(np.mean(ref * ref)))
+                assert err <= 1e-5, (m, k, n, sms, err)
+            else:
+                err = np.linalg.norm(got - ref) / np.linalg.norm(ref)
+                assert err <= {"bfloat16": 4e-3, "float16": 6e-4}[dtype], (m, k, n, sms, err)
+        # transposed operands (the backward GEMMs' layouts) on the balanced path
+        m, k, n = 1536, 1280, 1024
+        at = rand_operand(rng, (k, m), dtype, scale=1 / np.sqrt(k)); bt = rand_operand(rng, (n, k), dtype)
+        ref = f64(at, dtype).T @ f64(bt, dtype).T
+        tc = dev(np.zeros((m, n), O.storage(CODE[dtype])), dtype); ta, tb = dev(at, dtype), dev(bt, dtype)
+        g = rpb.RpbGemm(); lib.rpb_gemm_packed(C.byref(g), m, k, n)
+        g.a_row, g.a_col, g.b_row, g.b_col, g.max_sms = 1, m, 1, k, 10
+        assert lib.rp_matmul_ex(C.c_void_p(tc.data_ptr), C.c_void_p(ta.data_ptr), C.c_void_p(tb.data_ptr), C.byref(g), CODE[dtype], 0, None) == 0
+        got = f64(tc.to_numpy(), dtype)
+        assert np.linalg.norm(got - ref) / np.linalg.norm(ref) <= {"bfloat16": 4e-3, "float16": 6e-4, "float32": 2e-5}[dtype]
+    finally:
+        lib.rpb_force_kernel(0)
+    assert lib.rpb_device_status(0) == 0
+
+
+@pytest.mark.parametrize("dtype", ["bfloat16", "float16", "float32"])
+def test_two_slice_tail_is_finished_inside_the_kernel(lib, dtype):
+    """A last wave that fills between a quarter and a half of the CTA pairs: its tiles are cut into TWO K slices that
+    run side by side, and per epilogue warp the slice that arrives second adds the first one's fp32 sums and writes
+    C (no reduction launch).  Ragged M, N and K, with a bias; float64 reference; identical bits on every run although
+    the arrival order is not fixed."""
+    rng = np.random.default_rng(91)
+    m, k, n = 2000, 6200, 3300                       # 8 x 13 = 104 tiles of 256 x 256 on 74 pairs: 30 tail tiles
+    a = rand_operand(rng, (m, k), dtype, scale=1 / np.sqrt(k)); b = rand_operand(rng, (k, n), dtype)
+    bias = rand_operand(rng, (n,), dtype)
+    pad = (-n) % 8
+    bp = np.zeros((k, n + pad), b.dtype); bp[:, :n] = b          # row stride a multiple of 16 bytes
+    ref = f64(a, dtype) @ f64(b, dtype) + f64(bias, dtype)
+    ap = np.zeros((m, k + (-k) % 8), a.dtype); ap[:, :k] = a
+    ta, tb, tbias = dev(ap, dtype), dev(bp, dtype), dev(bias, dtype)
+    if dtype == "float32":
+        lib.rpb_force_kernel(_lib.KERNEL_UMMA)
+    try:
+        outs = []
+        for trial in range(3):
+            tc = dev(np.zeros((m, n + pad), O.storage(CODE[dtype])), dtype)
+            g = rpb.RpbGemm(); lib.rpb_gemm_packed(C.byref(g), m, k, n)
+            g.a_row = ap.shape[1]; g.b_row = n + pad; g.c_row = n + pad; g.bias = tbias.data_ptr
+            before = lib.rpb_launch_count()
+            assert lib.rp_matmul_ex(C.c_void_p(tc.data_ptr), C.c_void_p(ta.data_ptr), C.c_void_p(tb.data_ptr), C.byref(g),
+                                    CODE[dtype], 0, None) == 0
+            assert lib.rpb_last_kernel() == _lib.KERNEL_UMMA
+            if dtype != "float32":                     # the float32 planner may choose another tile shape
+                assert lib.rpb_launch_count() - before == 1, "the tail was not finished inside the GEMM kernel"
+            outs.append(tc.to_numpy()[:, :n])
+        assert np.array_equal(outs[0], outs[1]) and np.array_equal(outs[0], outs[2])
+        got = f64(outs[0], dtype)
+        if dtype == "float32":
+            assert np.abs(got - ref).max() / (np.sqrt(k) * np.sqrt(np.mean(ref * ref))) <= 1e-5
+        else:
+            assert np.linalg.norm(got - ref) / np.linalg.norm(ref) <= {"bfloat16": 4e-3, "float16": 6e-4}[dtype]
+    finally:
+        lib.rpb_force_kernel(0)
+    assert lib.rpb_device_status(0) == 0
