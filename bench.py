@@ -85,7 +85,7 @@ def parse():
 # streamed once per column group, B is re-read once per row block), so a launch of `rows` rows is the line
 # through the two captures.  (rows, bytes) pairs; None until both captures exist.
 NCU_TRAFFIC_POINTS = {
-    "rowsharded_65536x8192x8192": ((8192, 1.2109e9), None),
+    "rowsharded_65536x8192x8192": ((8192, 1.2061e9), (16384, 2.2903e9)),
 }
 
 

@@ -39,7 +39,11 @@ void rpb_node_stream(void* stream, int synchronise) {
 /* end of an entry point: wait (unless told not to) and report a kernel that gave up */
 static int node_finish(int device_id) {
     if (!t_sync) return 0;
-    if (cudaStreamSynchronize(t_stream) != cudaSuccess) return -1;
+    cudaError_t e = cudaStreamSynchronize(t_stream);
+    if (e != cudaSuccess) {
+        fprintf(stderr, "recpulse_b200: synchronising after a node failed: %s\n", cudaGetErrorString(e));
+        return -1;
+    }
     return rpb_take_status(device_id) ? -1 : 0;
 }
 
@@ -414,7 +418,11 @@ static Tensor* matmul_node(Tensor* a, Tensor* b, Tensor* bias) {
     int rc = product_into(out, a, b, bias, 0, 0, nd, oshape);
     /* callers assume the result is complete on return (every RecPulse device op synchronises) */
     if (rc == 0) rc = node_finish(a->device_id);
-    if (rc != 0) { rpb_tensor_release(out); return NULL; }
+    if (rc != 0) {
+        fprintf(stderr, "recpulse_b200: matmul node: the product could not be computed\n");
+        rpb_tensor_release(out);
+        return NULL;
+    }
 
     if (wants_grad(a) || wants_grad(b) || wants_grad(bias)) {
         Tensor* in[3] = {a, b, bias};
