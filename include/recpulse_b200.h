@@ -220,8 +220,9 @@ typedef struct {
                                     /* [n/2, 3n/4) go through tanh and the others through 1 / (1 + exp(-x))    */
                                     /* before the one rounding; n must be a multiple of 4                      */
     int c_float32;                  /* 1: float16 / bfloat16 operands, but C receives the UNROUNDED float32 sums */
-                                    /* (packed [batch][m][n], c_row == n; no bias, accumulation or epilogue):   */
-                                    /* partial gradients that are summed across GPUs before their one rounding  */
+                                    /* (packed [batch][m][n], c_row == n; no bias or epilogue; `accumulate`      */
+                                    /* keeps a float32 running sum): partial gradients that are summed over row  */
+                                    /* chunks or across GPUs before their one rounding                          */
 } RpbGemm;
 #define RPB_EPILOGUE_LSTM_GATES 1
 

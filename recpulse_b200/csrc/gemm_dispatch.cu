@@ -681,6 +681,7 @@ int launch_umma(const RpbProblem& p, void* C, const void* A, const void* B, Devi
     a.iters_per_split = (a.k_iters + splits - 1) / splits;
     a.splits = (a.k_iters + a.iters_per_split - 1) / a.iters_per_split;
     a.total_work = tiles * a.splits;
+    if (a.total_work + 4 * tiles > 0x7fffffffLL || (long long)a.tiles_m * a.tiles_n > 0x7fffffffLL) return 1;   /* the kernel decodes work items in 32 bits */
     a.group_n = raster_group(pair ? d->sm_count / 2 : d->sm_count, tile_m, tile_n, a.tiles_n);
     if (const char* e = getenv("RPB_GROUP_N")) {            /* experiments: n-tiles per rasterisation group */
         const int v = atoi(e);
@@ -727,7 +728,8 @@ int launch_umma(const RpbProblem& p, void* C, const void* A, const void* B, Devi
     if (a.c_f32) {
         /* unrounded fp32 output of 16-bit operands: written like a K slice, straight into the caller's buffer */
         a.partial = reinterpret_cast<float*>(C);
-        if (p.n % 4 == 0 && (reinterpret_cast<uintptr_t>(C) & 15u) == 0 &&
+        /* "C += AB" in float32 reads C back: the register epilogue */
+        if (!p.accumulate && p.n % 4 == 0 && (reinterpret_cast<uintptr_t>(C) & 15u) == 0 &&
             encode_store_map(&mc, C, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, p.n, p.m, p.batch, p.n, (long long)p.m * p.n, 32) == 0)
             a.tma_store = 1;
     } else if (a.splits > 1) {
@@ -846,7 +848,7 @@ int launch_umma(const RpbProblem& p, void* C, const void* A, const void* B, Devi
     }
     if (a.splits > 1 && p.c_f32) {
         rpb_simt::launch_splitk_reduce<float, float>(a.partial, reinterpret_cast<float*>(C), a.splits, p.batch, p.m, p.n, p.n,
-                                                     (long long)p.m * p.n, 0, nullptr, d->sm_count, stream);
+                                                     (long long)p.m * p.n, p.accumulate, nullptr, d->sm_count, stream);
         g_launches++;
         RPB_CUDA(cudaGetLastError());
         if (release_scratch(d, stream)) return -1;
@@ -1026,9 +1028,9 @@ int run_gemm_planned(const RpbProblem& in, void* C, const void* A, const void* B
     const bool half_type = p.dtype == DTYPE_FLOAT16 || p.dtype == DTYPE_BFLOAT16;
     if (p.c_f32) {
         /* unrounded float32 output: a capability of the tcgen05 kernel only */
-        if (!half_type || p.accumulate || p.bias || p.act || p.c_row != p.n || (p.batch > 1 && p.c_batch != (long long)p.m * p.n)) {
-            fprintf(stderr, "recpulse_b200: a float32 output needs float16 / bfloat16 operands, a packed C and no bias, "
-                            "accumulation or epilogue\n");
+        if (!half_type || p.bias || p.act || p.c_row != p.n || (p.batch > 1 && p.c_batch != (long long)p.m * p.n)) {
+            fprintf(stderr, "recpulse_b200: a float32 output needs float16 / bfloat16 operands, a packed C and no bias "
+                            "or epilogue\n");
             return -1;
         }
         int rc = p.dtype == DTYPE_BFLOAT16 ? launch_umma<__nv_bfloat16>(p, C, A, B, d, stream)

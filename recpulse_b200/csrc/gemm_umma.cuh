@@ -489,20 +489,25 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             }
         }
         if (w >= args.total_work) return false;
-        if (w >= args.tail_begin) {                 /* K slice of a tail tile (only with splits == batch == 1) */
-            const long long j = w - args.tail_begin;
-            o.split = (int)(j % args.tail_splits);
+        /* 32-bit arithmetic: the host keeps tiles x slices below 2^31, and 64-bit divisions cost hundreds of clocks
+         * in code that sits between one tile's last MMA and the next tile's first */
+        const uint32_t wi = (uint32_t)w, tb32 = (uint32_t)args.tail_begin;
+        if (wi >= tb32) {                           /* K slice of a tail tile (only with splits == batch == 1) */
+            const uint32_t j = wi - tb32;
+            const uint32_t tile = j / (uint32_t)args.tail_splits;
+            o.split = (int)(j - tile * (uint32_t)args.tail_splits);
             o.bz = 0;
-            tile_coords((int)(args.tail_begin + j / args.tail_splits), args.tiles_m, args.tiles_n, args.group_n, o.mt, o.nt);
+            tile_coords((int)(tb32 + tile), args.tiles_m, args.tiles_n, args.group_n, o.mt, o.nt);
             o.it0 = o.split * args.tail_iters;
             o.it1 = min(o.it0 + args.tail_iters, args.k_iters);
             o.kind = 1; o.slot = (int)j;
         } else {
-            const int tiles_mn = args.tiles_m * args.tiles_n;
-            long long q = w;
-            const int t = (int)(q % tiles_mn); q /= tiles_mn;
-            o.split = (int)(q % args.splits);
-            o.bz = (int)(q / args.splits);
+            const uint32_t tiles_mn = (uint32_t)(args.tiles_m * args.tiles_n);
+            uint32_t q = wi / tiles_mn;
+            const int t = (int)(wi - q * tiles_mn);
+            const uint32_t bz = q / (uint32_t)args.splits;
+            o.split = (int)(q - bz * (uint32_t)args.splits);
+            o.bz = (int)bz;
             tile_coords(t, args.tiles_m, args.tiles_n, args.group_n, o.mt, o.nt);
             o.it0 = o.split * args.iters_per_split;
             o.it1 = min(o.it0 + args.iters_per_split, args.k_iters);
@@ -880,12 +885,20 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                     /* nothing to store for this lane */
                 } else if (args.splits > 1 || args.c_f32) {
                     float* dst = args.partial + (((long long)split * args.batch + bz) * args.m + row) * (long long)args.n + col;
+                    const bool add = args.c_f32 && args.accumulate;      /* float32 output that keeps a running sum */
                     if (col + 32 <= args.n && ((reinterpret_cast<uintptr_t>(dst) & 15u) == 0)) {
 #pragma unroll
-                        for (int j = 0; j < 32; j += 4)
-                            *reinterpret_cast<uint4*>(dst + j) = make_uint4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                        for (int j = 0; j < 32; j += 4) {
+                            float4 f = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]), __uint_as_float(v[j + 2]),
+                                                   __uint_as_float(v[j + 3]));
+                            if (add) {
+                                const float4 o = *reinterpret_cast<const float4*>(dst + j);
+                                f.x += o.x; f.y += o.y; f.z += o.z; f.w += o.w;
+                            }
+                            *reinterpret_cast<float4*>(dst + j) = f;
+                        }
                     } else {
-                        for (int j = 0; j < 32 && col + j < args.n; ++j) dst[j] = __uint_as_float(v[j]);
+                        for (int j = 0; j < 32 && col + j < args.n; ++j) dst[j] = __uint_as_float(v[j]) + (add ? dst[j] : 0.f);
                     }
                 } else {
                     T* dst = cT + bz * args.c_batch + (long long)row * args.c_row + col;

@@ -50,12 +50,20 @@ def test_float32_output_is_the_unrounded_sum(lib, dtype, shape, monkeypatch):
         assert np.isfinite(got).all()
         # fp32 accumulation of exact 16-bit products: far inside one 16-bit rounding step
         assert np.abs(got - ref).max() <= 2e-6 * np.sqrt(k) * np.sqrt(np.mean(ref * ref)) + 1e-30, (plan, shape)
+        # "C += AB" keeps a float32 running sum (gradients accumulated over row chunks before their one rounding)
+        g.accumulate = 1
+        assert lib.rp_matmul_ex(C.c_void_p(out.data_ptr), C.c_void_p(ta.data_ptr), C.c_void_p(tb.data_ptr), C.byref(g),
+                                CODE[dtype], 0, None) == 0
+        twice = out.to_numpy().astype(np.float64)
+        assert np.abs(twice - 2 * ref).max() <= 4e-6 * np.sqrt(k) * np.sqrt(np.mean(ref * ref)) + 1e-30, (plan, shape)
     monkeypatch.delenv("RPB_UMMA_PLAN", raising=False)
     # what it cannot do is refused, not approximated
-    g.accumulate = 1
+    g.accumulate = 0
+    tbias = dev(rand_operand(rng, (n,), dtype), dtype)
+    g.bias = tbias.data_ptr
     assert lib.rp_matmul_ex(C.c_void_p(out.data_ptr), C.c_void_p(ta.data_ptr), C.c_void_p(tb.data_ptr), C.byref(g),
                             CODE[dtype], 0, None) == -1
-    g.accumulate = 0
+    g.bias = None
     assert lib.rp_matmul_ex(C.c_void_p(out.data_ptr), C.c_void_p(ta.data_ptr), C.c_void_p(tb.data_ptr), C.byref(g),
                             CODE["float32"], 0, None) == -1
 
