@@ -110,3 +110,31 @@ def test_tile_plan_model_on_the_host():
     assert plan(65536, 2048, 512, dtype=0)[2] == 1       # fp32 (3xTF32) large output: pair tiles
     assert lib.rpb_umma_plan(0, 8, 8, 1, 1, 3, 148, None, None, None) == -1
     assert lib.rpb_umma_plan(8, 8, 8, 1, 1, 1, 148, None, None, None) == -1      # float64 has no tcgen05 plan
+
+
+def test_new_entry_points_refuse_bad_arguments_without_gpu():
+    """GRU / conv2d passes, the stream-ordered node switch and the diagnostics: argument errors need no GPU."""
+    lib = rpb.load()
+    buf = np.zeros(64, np.float32).ctypes.data_as(C.c_void_p)
+    # GRU passes: host "device", hidden <= 0, row stride shorter than a row
+    assert lib.rp_gru_gates_ex(buf, buf, buf, buf, 4, 4, 4, 0, -1, None) == -1
+    assert lib.rp_gru_gates_ex(buf, buf, buf, buf, 4, 0, 4, 0, 0, None) == -1
+    assert lib.rp_gru_gates_ex(buf, buf, buf, buf, 4, 4, 3, 0, 0, None) == -1
+    assert lib.rp_gru_gates_grad_ex(buf, buf, None, 0, None, buf, buf, buf, 4, 4, 4, 0, 0, None) == -1
+    # conv2d geometry (ops/ops.c:4739-4740): kernel larger than the padded image, zero stride
+    cv = _lib.RpbConv2d(2, 3, 7, 6, 4, 3, 3, 1, 1, 1, 1, 1, 1)
+    oh, ow = C.c_int(), C.c_int()
+    assert lib.rp_conv2d_out_shape(C.byref(cv), C.byref(oh), C.byref(ow)) == 0 and (oh.value, ow.value) == (7, 6)
+    assert lib.rp_conv2d_col_elems(C.byref(cv)) == 2 * 27 * 42
+    cv2 = _lib.RpbConv2d(3, 2, 9, 8, 5, 2, 3, 2, 1, 0, 1, 1, 2)
+    assert lib.rp_conv2d_out_shape(C.byref(cv2), C.byref(oh), C.byref(ow)) == 0 and (oh.value, ow.value) == (4, 6)
+    assert lib.rp_conv2d_col_elems(C.byref(_lib.RpbConv2d(1, 1, 2, 2, 1, 5, 5, 1, 1, 0, 0, 1, 1))) == -1
+    assert lib.rp_conv2d_col_elems(C.byref(_lib.RpbConv2d(1, 1, 8, 8, 1, 3, 3, 0, 1, 0, 0, 1, 1))) == -1
+    assert lib.rp_conv2d_forward_ex(buf, buf, buf, None, C.byref(cv), 0, 0, None) == -1
+    assert lib.rp_conv2d_backward_ex(None, 0, None, 0, buf, buf, buf, buf, C.byref(cv), 0, 0, None) == -1
+    # node switch and wait limit are plain host state
+    lib.rpb_node_stream(None, 0); lib.rpb_node_stream(None, 1)
+    lib.rpb_set_wait_limit_ms(250); lib.rpb_set_wait_limit_ms(0)
+    assert lib.rpb_trace_read((C.c_ulonglong * 4)(), 4) == -1          # tracing is off
+    assert lib.rpb_selftest_bounded_wait(0, 0) == -1
+    assert lib.op_gru_cell(None, None, None, None, None, None) is None or not lib.op_gru_cell(None, None, None, None, None, None)
