@@ -178,7 +178,7 @@ __device__ __forceinline__ bool elect_one() {
     asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
     return pred != 0;
 }
-/* all lanes of a converged warp wait; the verdict is uniform */
+/* all lanes of a converged warp wait; the outcome is uniform */
 __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                                int* status, int code, long long limit) {
     const bool ok = mbar_wait(bar, parity, abort_flag, status, code, limit);
