@@ -371,7 +371,9 @@ enum {                              /* values of rpb_last_kernel()              
 /* Which kernel family the last GEMM issued by the calling thread used. */
 int rpb_last_kernel(void);
 /* The tile plan the tcgen05 kernel would use for an m x n output over k (per summed problem; `reduce` of them)
- * on `sms` SMs: rows of B per CTA (64 / 128 / 256), K slices (1 = none) and whether two CTAs share a tile.
+ * on `sms` SMs: rows of B per CTA (64 / 128 / 256), K slices (1 = none) and whether two CTAs share a tile
+ * (*cta_pair: 0 one CTA per 128-row tile, 1 a pair per 256 x 2*rows_of_b tile, 2 a pair per double-width tile of
+ * 256 x 512 with two accumulators).
  * Pure host arithmetic (a cost model in microseconds per K block fitted to measurements): needs no GPU.
  * dtype: DTYPE_FLOAT32 plans the 3xTF32 kernel, the 16-bit types the f16 / bf16 one.  0 / -1. */
 int rpb_umma_plan(int m, int n, int k, int reduce, int batch, DType dtype, int sms, int* rows_of_b, int* k_slices,

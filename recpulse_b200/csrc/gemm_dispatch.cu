@@ -576,11 +576,11 @@ int raster_group(int in_flight, int tile_m, int tile_n, int tiles_n) {
     return g < 1 ? 1 : g;
 }
 
-template <typename T, int BN, bool A_MN, bool B_MN, bool PAIR>
+template <typename T, int BN, bool A_MN, bool B_MN, bool PAIR, int NH = 1>
 int launch_umma_inst(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, const CUtensorMap& mp,
                      const rpb_umma::Args& args, int grid, cudaStream_t stream) {
-    using Cfg = rpb_umma::Config<BN, rpb_umma::Elem<T>::SPLIT>;
-    auto kern = rpb_umma::gemm_kernel<T, BN, A_MN, B_MN, PAIR>;
+    using Cfg = rpb_umma::Config<BN, rpb_umma::Elem<T>::SPLIT, NH>;
+    auto kern = rpb_umma::gemm_kernel<T, BN, A_MN, B_MN, PAIR, NH>;
     static std::atomic<bool> attr_done[MAX_DEVICES];
     RPB_CUDA(smem_attr_once(kern, Cfg::SMEM_BYTES, attr_done));
     RPB_CUDA(rpb_launch(kern, dim3((unsigned)grid), dim3(rpb_umma::Elem<T>::THREADS), Cfg::SMEM_BYTES, stream, PAIR ? 2 : 1,
@@ -590,13 +590,13 @@ int launch_umma_inst(const CUtensorMap& ma, const CUtensorMap& mb, const CUtenso
     return 0;
 }
 
-template <typename T, int BN, bool PAIR = false>
+template <typename T, int BN, bool PAIR = false, int NH = 1>
 int launch_umma_bn(bool a_mn, bool b_mn, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc,
                    const CUtensorMap& mp, const rpb_umma::Args& args, int grid, cudaStream_t stream) {
-    if (!a_mn && !b_mn) return launch_umma_inst<T, BN, false, false, PAIR>(ma, mb, mc, mp, args, grid, stream);
-    if (!a_mn && b_mn) return launch_umma_inst<T, BN, false, true, PAIR>(ma, mb, mc, mp, args, grid, stream);
-    if (a_mn && !b_mn) return launch_umma_inst<T, BN, true, false, PAIR>(ma, mb, mc, mp, args, grid, stream);
-    return launch_umma_inst<T, BN, true, true, PAIR>(ma, mb, mc, mp, args, grid, stream);
+    if (!a_mn && !b_mn) return launch_umma_inst<T, BN, false, false, PAIR, NH>(ma, mb, mc, mp, args, grid, stream);
+    if (!a_mn && b_mn) return launch_umma_inst<T, BN, false, true, PAIR, NH>(ma, mb, mc, mp, args, grid, stream);
+    if (a_mn && !b_mn) return launch_umma_inst<T, BN, true, false, PAIR, NH>(ma, mb, mc, mp, args, grid, stream);
+    return launch_umma_inst<T, BN, true, true, PAIR, NH>(ma, mb, mc, mp, args, grid, stream);
 }
 
 /* Tile shape and K slices, chosen by a small cost model in microseconds fitted to measurements on B200
@@ -607,15 +607,16 @@ int launch_umma_bn(bool a_mn, bool b_mn, const CUtensorMap& ma, const CUtensorMa
  * without work.  A CTA pair multiplies a 256 x 2BN tile with half the B traffic per SM and draws less power,
  * so it wins whenever it keeps about as many SMs busy.  Slicing K costs a second launch plus a round trip of
  * fp32 partial sums. */
-struct TilePlan { int bn, splits, pair; };
+struct TilePlan { int bn, splits, pair, wide; };   /* wide: the pair tile is two instructions wide (256 x 512) */
 TilePlan plan_tiles(int m, int n, int batch, int k_iters, int sms, bool f32) {
     static int pair_env = -1;
     if (pair_env < 0) { const char* e = getenv("RPB_UMMA_PAIR"); pair_env = e ? (atoi(e) ? 2 : 1) : 0; }
     if (const char* e = getenv("RPB_UMMA_PLAN")) {                  /* "BN,splits,pair": pins the plan (experiments) */
         int b = 0, sp = 0, pr = 0;
-        if (sscanf(e, "%d,%d,%d", &b, &sp, &pr) >= 2 && (b == 64 || b == 128 || (b == 256 && !pr)) && sp >= 1) {
+        if (sscanf(e, "%d,%d,%d", &b, &sp, &pr) >= 2 && (b == 64 || b == 128 || (b == 256 && !pr)) && sp >= 1 &&
+            (pr != 2 || (b == 128 && !f32 && m >= 256 && n >= 512))) {           /* pair = 2: the double-width tile */
             if (sp > k_iters) sp = k_iters;
-            return TilePlan{b, sp > 128 ? 128 : sp, pr ? 1 : 0};
+            return TilePlan{b, sp > 128 ? 128 : sp, pr ? 1 : 0, pr == 2 ? 1 : 0};
         }
     }
     static const int cand_splits[] = {1, 2, 3, 4, 6, 8, 12, 16, 24, 32, 48, 64, 96, 128};
@@ -623,7 +624,7 @@ TilePlan plan_tiles(int m, int n, int batch, int k_iters, int sms, bool f32) {
     static const double step16[5] = {0.26, 0.28, 0.41, 0.25, 0.38};
     static const double step32[5] = {0.70, 0.86, 1.50, 1.12, 1.33};
     const double* step = f32 ? step32 : step16;
-    TilePlan best = {n <= 64 ? 64 : (n <= 128 ? 128 : 256), 1, 0};
+    TilePlan best = {n <= 64 ? 64 : (n <= 128 ? 128 : 256), 1, 0, 0};
     double best_t = 1e30;
     for (int c = 0; c < 5; ++c) {
         const int pair = c >= 3;
@@ -640,12 +641,31 @@ TilePlan plan_tiles(int m, int n, int batch, int k_iters, int sms, bool f32) {
             const long long waves = (tiles * sp + units - 1) / units;
             double t = (double)waves * (ips * step[c] + (pair ? 0.8 : 0.5));
             if (sp > 1) t += 3.5 + (double)sp * m * n * batch * 8.0 / 3.0e6;
-            if (t < best_t) { best_t = t; best.bn = bn; best.splits = sp; best.pair = pair; }
+            if (t < best_t) { best_t = t; best.bn = bn; best.splits = sp; best.pair = pair; best.wide = 0; }
         }
     }
+    /* The double-width pair tile (256 x 512, two accumulators sharing the A tile) fetches a quarter fewer bytes per
+     * FLOP than the 256 x 256 one.  Measured on 16-bit 8192-wide problems: 1.5-4% less time at the burst clock and
+     * 4-8% more throughput under the power cap, where bytes moved are watts; but its tiles are twice as large, its
+     * epilogue is only partly hidden and its last wave is not cut along K.  It replaces the 256 x 256 plan when the
+     * model says so, with the 256 x 256 plan credited for its K-sliced last wave. */
+    static int wide_env = -1;
+    if (wide_env < 0) { const char* e = getenv("RPB_UMMA_WIDE"); wide_env = e ? (atoi(e) ? 2 : 1) : 0; }
+    if (!f32 && wide_env != 1 && best.pair && best.bn == 128 && best.splits == 1 && n >= 512 && m >= 256) {
+        const int units = sms / 2;
+        const long long tiles_d = (long long)((m + 255) / 256) * ((n + 255) / 256) * batch;
+        const long long tiles_w = (long long)((m + 255) / 256) * ((n + 511) / 512) * batch;
+        double waves_d = (double)((tiles_d + units - 1) / units);
+        const long long rem = tiles_d % units;
+        if (batch == 1 && tiles_d > units && rem > 0 && rem * 2 <= units && k_iters >= 32) waves_d -= 0.5;
+        const double waves_w = (double)((tiles_w + units - 1) / units);
+        const double t_d = waves_d * (k_iters * step16[4] + 0.8);
+        const double t_w = waves_w * (k_iters * 0.72 + 3.0);
+        if (wide_env == 2 ? tiles_w >= 1 : t_w < t_d) { best.wide = 1; best_t = t_w; }
+    }
     if (getenv("RPB_UMMA_PLAN_LOG"))
-        fprintf(stderr, "rpb plan %dx%dx(%d blocks) batch %d: %s 128x%d, %d slices, model %.1f us\n", m, n, k_iters, batch,
-                best.pair ? "pair" : "one-CTA", best.bn, best.splits, best_t);
+        fprintf(stderr, "rpb plan %dx%dx(%d blocks) batch %d: %s 128x%d%s, %d slices, model %.1f us\n", m, n, k_iters, batch,
+                best.pair ? "pair" : "one-CTA", best.bn, best.wide ? " double-width" : "", best.splits, best_t);
     return best;
 }
 
@@ -668,7 +688,8 @@ int launch_umma(const RpbProblem& p, void* C, const void* A, const void* B, Devi
     const bool pair = tp.pair != 0;
     const int BN = tp.bn;
     const int tile_m = pair ? 2 * rpb_umma::BLOCK_M : rpb_umma::BLOCK_M;
-    const int tile_n = pair ? 2 * BN : BN;
+    const int inst_n = pair ? 2 * BN : BN;                          /* columns per tcgen05.mma and per accumulator */
+    const int tile_n = tp.wide ? 2 * inst_n : inst_n;
     rpb_umma::Args a;
     memset(&a, 0, sizeof(a));
     a.m = p.m; a.n = p.n; a.k = p.k; a.batch = p.batch; a.reduce = p.reduce;
@@ -701,7 +722,7 @@ int launch_umma(const RpbProblem& p, void* C, const void* A, const void* B, Devi
     const bool bf16 = p.dtype == DTYPE_BFLOAT16;
     const uint32_t fmt = F32 ? 2u : (bf16 ? 1u : 0u);             /* operand format: F16 = 0, BF16 = 1, TF32 = 2 */
     a.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((pa.mn_major ? 1u : 0u) << 15) | ((pb.mn_major ? 1u : 0u) << 16) |
-              ((uint32_t)(tile_n >> 3) << 17) | ((uint32_t)(tile_m >> 4) << 24);
+              ((uint32_t)(inst_n >> 3) << 17) | ((uint32_t)(tile_m >> 4) << 24);
     a.a_desc_base = smem_desc_base(pa.mn_major, ES);
     a.b_desc_base = smem_desc_base(pb.mn_major, ES);
     /* advance per instruction (32 bytes of K): K-major 32 bytes inside the swizzle row; MN-major the K rows it
@@ -713,6 +734,10 @@ int launch_umma(const RpbProblem& p, void* C, const void* A, const void* B, Devi
     a.wait_limit = wait_limit_cycles();
     a.epi_sleep_ns = epilogue_sleep_ns();
     a.trace = g_trace_buffer;
+    /* double-width tiles: the second accumulator trails the first by this many K blocks at both ends of a tile
+     * (at most stages - 1 = 3; measured on the row-sharded workload under the power cap: 0 -> 3 blocks = +1%) */
+    a.wide_skew = 3;
+    if (const char* e = getenv("RPB_WIDE_SKEW")) { const int v = atoi(e); a.wide_skew = v < 0 ? 0 : (v > 3 ? 3 : v); }
 
     CUtensorMap ma, mb;
     const CUtensorMapDataType dt = F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
@@ -742,6 +767,10 @@ int launch_umma(const RpbProblem& p, void* C, const void* A, const void* B, Devi
         if (encode_store_map(&mc, C, dt, ES, p.n, p.m, p.batch, p.c_row, p.c_batch, 128 / ES) == 0) a.tma_store = 1;
     }
 
+    {
+        const char* e = getenv("RPB_EPI_PIPE");
+        a.epi_pipe = e ? (atoi(e) ? 1 : 0) : 1;
+    }
     /* the gate non-linearity lives in the register epilogue (it follows "C += AB" in its only user) */
     if (p.act && a.splits == 1) a.tma_store = 0;
     a.act = a.splits == 1 ? p.act : 0;
@@ -758,7 +787,7 @@ int launch_umma(const RpbProblem& p, void* C, const void* A, const void* B, Devi
         const char* be = getenv("RPB_BALANCED");
         const int env = be ? atoi(be) : 0;
         const long long units = pair ? sms / 2 : sms;
-        if (env && a.splits == 1 && p.batch == 1 && !p.c_f32 && a.tma_store == 1 && units >= 2 &&
+        if (env && !tp.wide && a.splits == 1 && p.batch == 1 && !p.c_f32 && a.tma_store == 1 && units >= 2 &&
             units <= BAL_MAX_UNITS && tiles > units && a.k_iters >= 16) {
             const long long waves = (tiles + units - 1) / units;
             const double idle = (double)(waves * units) / (double)tiles - 1.0;
@@ -791,7 +820,7 @@ int launch_umma(const RpbProblem& p, void* C, const void* A, const void* B, Devi
         const long long rem = units > 0 ? tiles % units : 0;
         const char* fe = getenv("RPB_TAIL_FUSE");
         const bool may_fuse = !(fe && atoi(fe) == 0) && rem * 64 <= 4 * BAL_MAX_UNITS;
-        if (env && !a.bal && a.splits == 1 && !p.c_f32 && p.batch == 1 && a.tma_store == 1 && tiles > units && rem > 0 && rem * 2 <= units) {
+        if (env && !tp.wide && !a.bal && a.splits == 1 && !p.c_f32 && p.batch == 1 && a.tma_store == 1 && tiles > units && rem > 0 && rem * 2 <= units) {
             long long ts = units / rem;
             if (ts > 4) ts = 4;
             if (ts > a.k_iters / 8) ts = a.k_iters / 8;
@@ -829,7 +858,11 @@ int launch_umma(const RpbProblem& p, void* C, const void* A, const void* B, Devi
     int rc;
     if (pair) {
         const long long clusters = a.total_work < sms / 2 ? a.total_work : sms / 2;
-        if (BN == 64) rc = launch_umma_bn<T, 64, true>(pa.mn_major, pb.mn_major, ma, mb, mc, mp, a, (int)clusters * 2, stream);
+        if (tp.wide) {
+            if constexpr (!F32) rc = launch_umma_bn<T, 128, true, 2>(pa.mn_major, pb.mn_major, ma, mb, mc, mp, a, (int)clusters * 2, stream);
+            else rc = -1;
+        }
+        else if (BN == 64) rc = launch_umma_bn<T, 64, true>(pa.mn_major, pb.mn_major, ma, mb, mc, mp, a, (int)clusters * 2, stream);
         else rc = launch_umma_bn<T, 128, true>(pa.mn_major, pb.mn_major, ma, mb, mc, mp, a, (int)clusters * 2, stream);
     }
     else if (BN == 64) rc = launch_umma_bn<T, 64>(pa.mn_major, pb.mn_major, ma, mb, mc, mp, a, grid, stream);
@@ -1340,7 +1373,7 @@ int rpb_umma_plan(int m, int n, int k, int reduce, int batch, DType dtype, int s
     const TilePlan tp = plan_tiles(m, n, batch, (int)k_iters, sms, es == 4);
     if (rows_of_b) *rows_of_b = tp.bn;
     if (k_slices) *k_slices = tp.splits;
-    if (cta_pair) *cta_pair = tp.pair;
+    if (cta_pair) *cta_pair = tp.wide ? 2 : tp.pair;
     return 0;
 }
 int rpb_last_kernel(void) { return t_last_kernel; }

@@ -10,6 +10,10 @@
  *                 and take alternate column chunks.
  *   warps 10..13  float32 only: split each delivered tile into hi and lo TF32 parts in shared memory
  * Two accumulators in tensor memory let the epilogue of tile i overlap the main loop of tile i+1.
+ * Large 16-bit problems take a double-width pair tile instead (256 x 512: the two accumulators belong to one
+ * tile and share its A operand, a quarter fewer bytes fetched per FLOP); there the second accumulator trails
+ * the first by a few K blocks at both ends of a tile and the epilogue hands each accumulator back as soon as
+ * it is in registers, which hides the epilogue without a spare buffer.
  *
  * Operands are read where they lie: each one may be K-major (reduction index
  * contiguous) or MN-major (output index contiguous); the TMA descriptor is built from
@@ -52,11 +56,16 @@ template <typename T> struct Elem {
 constexpr long long WAIT_LIMIT_CYCLES = 4000000000ll;   /* default bound of one wait: about 2 s of SM clock */
 constexpr int SMEM_LIMIT = 227 * 1024;
 constexpr int TRACE_SLOTS = 64;        /* 0 entry, 1 set-up done, 2 first TMA issued, 3 first stage landed, 4 last MMA committed,
-                                        * 5 kernel end; 8 + 4 i .. : item i  MMA start / MMA committed / epilogue start / epilogue end */
+                                        * 5 kernel end; 8 + 4 i .. : item i  MMA start / MMA committed / epilogue start / epilogue end
+                                        * (items 0..6); double-width tiles also 36 + i: second accumulator complete, 50 + i: the MMA
+                                        * warp has the first accumulator back (items 0..13; overlapping the slots of items 7 and up) */
 
-template <int BN, bool SPLIT = false> struct Config {
+/* NH: accumulators per tile.  2 = the double-width pair tile 256 x 4BN, whose two instruction-wide halves share the
+ * A tile: a stage then holds one A tile and two B sub-tiles of BN rows. */
+template <int BN, bool SPLIT = false, int NH = 1> struct Config {
     static constexpr int A_BYTES = BLOCK_M * 128;
-    static constexpr int B_BYTES = BN * 128;
+    static constexpr int B_SUB_BYTES = BN * 128;
+    static constexpr int B_BYTES = NH * B_SUB_BYTES;
     static constexpr int LOAD_BYTES = A_BYTES + B_BYTES;                 /* what TMA delivers per stage */
     static constexpr int STAGE_BYTES = SPLIT ? 2 * LOAD_BYTES : LOAD_BYTES;   /* [A | B | A_lo | B_lo]   */
     /* epilogue staging for TMA stores: one buffer of 32 rows x 128 bytes per epilogue warp */
@@ -117,6 +126,8 @@ struct Args {
     int* bal_flags;             /* [slots][2 ranks][ready, done] */
     long long wait_limit;  /* bound of every mbarrier wait, in SM clock cycles */
     uint32_t epi_sleep_ns; /* back-off between polls of the epilogue warps' wait for a finished accumulator (0 = spin) */
+    int epi_pipe;          /* 1: the 16-bit TMA-store epilogue runs software-pipelined (RPB_EPI_PIPE=0 for the plain loop) */
+    int wide_skew;         /* double-width tiles: K blocks by which the second accumulator trails the first at a tile's ends */
     int c_f32;             /* 1: the output is packed float32 [batch][m][n] (unrounded sums of 16-bit operands); the
                             * epilogue then writes it like a K slice: `partial` = the output when splits == 1 */
 };
@@ -368,7 +379,13 @@ __device__ __forceinline__ void trace_mark(unsigned long long* trace, int slot) 
  *               CTAs' shared memory, and each CTA's tensor memory receives its own 128 rows of the
  *               accumulator.  Each operand byte is fetched from L2 by one SM only (no multicast), so
  *               L2 traffic per FLOP drops by a third against PAIR = false at the same MMA shape per SM. */
-template <typename T, int BN, bool A_MN, bool B_MN, bool PAIR>
+/* NH = 2 (pairs of 16-bit types only): the tile is two instructions wide, 256 x 4BN.  Every K block is multiplied into
+ *               two accumulators that share the A tile, which takes another quarter off the bytes fetched per
+ *               FLOP (and off the power they cost).  The two accumulators fill tensor memory, so there is no second
+ *               buffer: instead the second accumulator runs SKEW K blocks behind the first at both ends of a
+ *               tile, so that the epilogue drains the first one while the second is still being multiplied, and the
+ *               next tile starts on the first accumulator while the second one is being drained. */
+template <typename T, int BN, bool A_MN, bool B_MN, bool PAIR, int NH = 1>
 __global__ void __launch_bounds__(Elem<T>::THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
             const __grid_constant__ CUtensorMap map_c, const __grid_constant__ CUtensorMap map_p, const Args args)
@@ -376,10 +393,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     using E = Elem<T>;
     constexpr bool SPLIT = E::SPLIT;
     constexpr int BLOCK_K = E::BLOCK_K, UMMA_K = E::UMMA_K, CHUNK = E::CHUNK;
-    using Cfg = Config<BN, SPLIT>;
+    using Cfg = Config<BN, SPLIT, NH>;
+    static_assert(NH == 1 || (NH == 2 && PAIR && !SPLIT && BN == 128), "double-width tiles: 16-bit pairs of 256 x 512");
     constexpr int ACC_N = PAIR ? 2 * BN : BN;              /* accumulator columns = instruction N */
+    constexpr int TILE_N = NH * ACC_N;                     /* columns of C per tile */
     constexpr int TILE_M = PAIR ? 2 * BLOCK_M : BLOCK_M;
-    constexpr uint32_t TMEM_COLS = 2 * ACC_N;
+    constexpr uint32_t TMEM_COLS = 2 * ACC_N;              /* NH = 1: two buffers; NH = 2: the tile's two accumulators */
     static_assert(TMEM_COLS <= 512 && (TMEM_COLS & (TMEM_COLS - 1)) == 0 && TMEM_COLS >= 32, "tensor memory columns");
     extern __shared__ uint8_t smem_raw[];
     /* the swizzle pattern and the descriptors' base_offset = 0 need 1024-byte aligned tiles */
@@ -529,7 +548,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             while (alive && next_item(w, phase_w, item)) {
                 const int mt = item.mt, nt = item.nt, bz = item.bz, it0 = item.it0, it1 = item.it1;
                 const int row0 = mt * TILE_M + (int)cta_rank * BLOCK_M;     /* this CTA's rows of A */
-                const int col0 = nt * ACC_N + (int)cta_rank * BN;           /* this CTA's columns of B */
+                const int col0 = nt * TILE_N + (int)cta_rank * BN;          /* this CTA's columns of B (first accumulator) */
                 const int r0 = it0 / args.k_blocks;
                 int kb = it0 - r0 * args.k_blocks, k0 = kb * BLOCK_K;
                 int a_r = r0 * args.a_reduce_mul, b_r = r0 * args.b_reduce_mul;
@@ -556,12 +575,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                             for (int c = 0; c < BLOCK_M / CHUNK; ++c)
                                 tma_load_4d<REMOTE_BAR>(sa + c * (BLOCK_K * 128), &map_a, tb, row0 + c * CHUNK, k0, a_r, a_b);
                         }
-                        if (!B_MN) {
-                            tma_load_4d<REMOTE_BAR>(sb, &map_b, tb, k0, col0, b_r, b_b);
-                        } else {
 #pragma unroll
-                            for (int c = 0; c < BN / CHUNK; ++c)
-                                tma_load_4d<REMOTE_BAR>(sb + c * (BLOCK_K * 128), &map_b, tb, col0 + c * CHUNK, k0, b_r, b_b);
+                        for (int h = 0; h < NH; ++h) {
+                            const uint32_t sbh = sb + h * Cfg::B_SUB_BYTES;
+                            const int colh = col0 + h * ACC_N;
+                            if (!B_MN) {
+                                tma_load_4d<REMOTE_BAR>(sbh, &map_b, tb, k0, colh, b_r, b_b);
+                            } else {
+#pragma unroll
+                                for (int c = 0; c < BN / CHUNK; ++c)
+                                    tma_load_4d<REMOTE_BAR>(sbh + c * (BLOCK_K * 128), &map_b, tb, colh + c * CHUNK, k0, b_r, b_b);
+                            }
                         }
                     }
                     __syncwarp();
@@ -589,6 +613,79 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             long long w = work_begin; int phase_w = 0; Item item;
             for (; alive && next_item(w, phase_w, item); ++local_tile) {
                 const int it0 = item.it0, it1 = item.it1;
+                if constexpr (NH == 2) {
+                    /* Two accumulators per tile (tensor-memory columns [0, ACC_N) and [ACC_N, 2 ACC_N)), one A tile and two
+                     * B sub-tiles per stage.  The second accumulator runs `head` K blocks behind the first at the start of a
+                     * tile and `tail` blocks behind at its end (the stages concerned stay in shared memory meanwhile), so the
+                     * first accumulator is handed to the epilogue early and taken back early.  In between, every stage is
+                     * multiplied into both accumulators and freed. */
+                    static_assert(NH == 1 || Cfg::STAGES >= 4, "the lead of the first accumulator holds up to three stages");
+                    const int SKEW = args.wide_skew;
+                    constexpr uint32_t BH = (uint32_t)(Cfg::B_SUB_BYTES >> 4);
+                    const uint32_t acc_phase = local_tile & 1u;
+                    const int iters = it1 - it0;
+                    const int head = iters < SKEW ? iters : SKEW;
+                    const int tail = iters >= 2 * SKEW ? SKEW : 0;
+                    uint32_t acc[2] = {0u, 0u};
+                    /* `count` K blocks from the ring position: multiply into the accumulators of `hmask`, after waiting
+                     * for the data (wait) and/or freeing the stage afterwards (free_stage) */
+                    auto run = [&](int count, int hmask, bool wait, bool free_stage) -> bool {
+                        for (int j = 0; j < count; ++j) {
+                            if (wait && !mbar_wait_warp(wb, phase, abort_flag, args.status, 3, args.wait_limit)) return false;
+                            tc_fence_after();
+                            if (elect_one()) {
+#pragma unroll
+                                for (int h = 0; h < 2; ++h) {
+                                    if (!(hmask & (1 << h))) continue;
+                                    uint32_t ac = acc[h];
+#pragma unroll
+                                    for (int kk = 0; kk < BLOCK_K / UMMA_K; ++kk) {
+                                        umma_f16<PAIR>(tmem_base + h * ACC_N, a_lo + kk * a_kstep, a_hi, b_lo + h * BH + kk * b_kstep, b_hi,
+                                                       idesc, ac);
+                                        ac = 1u;
+                                    }
+                                }
+                                if (free_stage) umma_commit<PAIR>(eb);
+                            }
+                            __syncwarp();
+                            if (hmask & 1) acc[0] = 1u;
+                            if (hmask & 2) acc[1] = 1u;
+                            a_lo += Cfg::STAGE_BYTES >> 4; b_lo += Cfg::STAGE_BYTES >> 4; wb += 8u; eb += 8u;
+                            if (++stage == Cfg::STAGES) { stage = 0; phase ^= 1u; a_lo = a_lo0; b_lo = b_lo0; wb = full_bar(0); eb = empty_bar(0); }
+                        }
+                        return true;
+                    };
+                    if (args.trace && lane == 0) trace_mark(args.trace, 8 + 4 * (int)local_tile);
+                    bool ok = mbar_wait_warp(tempty_bar(0), acc_phase ^ 1u, abort_flag, args.status, 2, args.wait_limit);
+                    if (args.trace && lane == 0 && local_tile < 6) trace_mark(args.trace, 50 + (int)local_tile);   /* first accumulator taken back */
+                    int s_stage = stage; uint32_t s_phase = phase, s_a = a_lo, s_b = b_lo, s_wb = wb, s_eb = eb;
+                    ok = ok && run(head, 1, true, false);
+                    ok = ok && mbar_wait_warp(tempty_bar(1), acc_phase ^ 1u, abort_flag, args.status, 2, args.wait_limit);
+                    if (ok) {
+                        stage = s_stage; phase = s_phase; a_lo = s_a; b_lo = s_b; wb = s_wb; eb = s_eb;
+                        run(head, 2, false, true);
+                        if (args.trace && lane == 0 && local_tile == 0) trace_mark(args.trace, 3);
+                        ok = run(iters - head - tail, 3, true, true);
+                    }
+                    if (ok && tail) {
+                        s_stage = stage; s_phase = phase; s_a = a_lo; s_b = b_lo; s_wb = wb; s_eb = eb;
+                        ok = run(tail, 1, true, false);
+                        if (ok) {
+                            if (elect_one()) umma_commit<PAIR>(tfull_bar(0));       /* first accumulator complete */
+                            __syncwarp();
+                            stage = s_stage; phase = s_phase; a_lo = s_a; b_lo = s_b; wb = s_wb; eb = s_eb;
+                            run(tail, 2, false, true);
+                            if (elect_one()) umma_commit<PAIR>(tfull_bar(1));
+                            __syncwarp();
+                        }
+                    } else if (ok) {
+                        if (elect_one()) { umma_commit<PAIR>(tfull_bar(0)); umma_commit<PAIR>(tfull_bar(1)); }
+                        __syncwarp();
+                    }
+                    if (!ok) { alive = false; break; }
+                    if (args.trace && lane == 0) { trace_mark(args.trace, 9 + 4 * (int)local_tile); trace_mark(args.trace, 4); }
+                    continue;
+                }
                 const uint32_t ab = local_tile & 1u;
                 const uint32_t acc_phase = (local_tile >> 1) & 1u;
                 if (!mbar_wait_warp(tempty_bar(ab), acc_phase ^ 1u, abort_flag, args.status, 2, args.wait_limit)) { alive = false; break; }
@@ -675,13 +772,22 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         long long w = work_begin; int phase_w = 0; Item item;
         for (; alive && next_item(w, phase_w, item); ++local_tile) {
             const int mt = item.mt, nt = item.nt, split = item.split, bz = item.bz;
-            const uint32_t ab = local_tile & 1u;
-            const uint32_t acc_phase = (local_tile >> 1) & 1u;
             if (args.trace && warp == 2 && lane == 0 && local_tile > 0) trace_mark(args.trace, 11 + 4 * (int)(local_tile - 1));
+            /* NH = 1: one pass over the tile's accumulator (two buffers, taken in turn).  NH = 2: the tile's two
+             * accumulators one after the other.  The two warps of a lane quarter take alternate column chunks.
+             * `continue` below means "this accumulator is done". */
+#pragma unroll 1
+            for (int h = 0; h < NH && alive; ++h) {
+            const uint32_t ab = NH == 2 ? (uint32_t)h : (local_tile & 1u);
+            const uint32_t acc_phase = NH == 2 ? (local_tile & 1u) : ((local_tile >> 1) & 1u);
+            const int ncol0 = nt * TILE_N + h * ACC_N;              /* first column of C behind this accumulator */
             if (!mbar_wait(tfull_bar(ab), acc_phase, abort_flag, args.status, 4, args.wait_limit, args.epi_sleep_ns)) { alive = false; break; }
             __syncwarp();
             tc_fence_after();
-            if (args.trace && warp == 2 && lane == 0) trace_mark(args.trace, 10 + 4 * (int)local_tile);
+            if (args.trace && warp == 2 && lane == 0) {
+                if (h == 0) trace_mark(args.trace, 10 + 4 * (int)local_tile);
+                else if (local_tile < 6) trace_mark(args.trace, 36 + (int)local_tile);     /* second accumulator complete */
+            }
             const int row = mt * TILE_M + (int)cta_rank * BLOCK_M + quarter * 32 + lane;
             const bool row_ok = row < args.m;
             /* How this warp treats the item.  0: output tile.  1: fp32 piece through map_p (K slice of a tail tile,
@@ -714,7 +820,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                         uint32_t v[32];
                         __syncwarp();
                         tmem_load_32(tmem_base + ab * ACC_N + cc + lane_field, v);
-                        if (nt * ACC_N + cc >= args.n || row_warp >= args.m) continue;      /* warp-uniform */
+                        if (ncol0 + cc >= args.n || row_warp >= args.m) continue;      /* warp-uniform */
                         float4* d4 = dst + (cc / 32) * 256;
 #pragma unroll
                         for (int q = 0; q < 8; ++q)
@@ -783,9 +889,77 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                     part = reinterpret_cast<const float4*>(args.bal_scratch) +
                            ((pslot * 2 + (int)cta_rank) * 4 + quarter) * (ACC_N / 32) * 256 + lane;
                 }
+                if constexpr (!SPLIT) {
+                    if (!wide && !part && args.epi_pipe) {
+                        /* 16-bit rows of C, the common case.  Measured in SM clocks per 64-column chunk of a warp: the
+                         * tcgen05.ld pair ~45, rounding and packing ~200, and the hand-over to the TMA engine (wait for the
+                         * previous store to have read the buffer, st.shared, proxy fence, issue) 500-900.  So the warp first
+                         * pulls BOTH of its chunks of the accumulator into registers (the first one packed to 16 bits), gives
+                         * the accumulator back to the MMA warp -- a few hundred clocks after it was completed -- and only
+                         * then stages and stores. */
+                        const bool rows_in = row_warp < args.m;             /* warp-uniform */
+                        const int ca = half * 64, cb = ca + 128;            /* this warp's chunks of the accumulator */
+                        const bool two = cb < ACC_N;
+                        uint32_t v[32], v2[32], pk[32];
+                        if (ca < ACC_N) {
+                            __syncwarp();
+                            tmem_load_32_nowait(tmem_base + ab * ACC_N + ca + lane_field, v);
+                            tmem_load_32_nowait(tmem_base + ab * ACC_N + ca + 32 + lane_field, v2);
+                            tmem_load_wait();
+                            if (args.bias) {
+                                add_bias_32<T>(v, reinterpret_cast<const T*>(args.bias), ncol0 + ca, args.n);
+                                add_bias_32<T>(v2, reinterpret_cast<const T*>(args.bias), ncol0 + ca + 32, args.n);
+                            }
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) {
+                                pk[i] = pack2<T>(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
+                                pk[16 + i] = pack2<T>(__uint_as_float(v2[2 * i]), __uint_as_float(v2[2 * i + 1]));
+                            }
+                            if (two) {
+                                __syncwarp();
+                                tmem_load_32_nowait(tmem_base + ab * ACC_N + cb + lane_field, v);
+                                tmem_load_32_nowait(tmem_base + ab * ACC_N + cb + 32 + lane_field, v2);
+                                tmem_load_wait();
+                            }
+                        }
+                        tc_fence_before();                                  /* every lane's reads are complete */
+                        __syncwarp();
+                        if (lane == 0) {
+                            if (PAIR) mbar_arrive_cluster(cluster_addr(tempty_bar(ab), 0));
+                            else mbar_arrive(tempty_bar(ab));
+                        }
+                        /* one chunk: registers -> staging buffer (128-byte swizzle) -> TMA store */
+                        auto put = [&](int c0) {
+                            if (ncol0 + c0 < args.n && rows_in) {
+                                if (lane == 0) tma_store_wait_read<0>();    /* the previous store has read `buf` */
+                                __syncwarp();
+#pragma unroll
+                                for (uint32_t c = 0; c < 8; ++c)
+                                    st_shared_v4(buf + my_row + ((c ^ sw) << 4), pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+                                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                                __syncwarp();
+                                if (lane == 0) tma_store_3d(&map_c, buf, ncol0 + c0, row_warp, zc);
+                            }
+                        };
+                        if (ca < ACC_N) put(ca);
+                        if (ca < ACC_N && two) {
+                            if (args.bias) {
+                                add_bias_32<T>(v, reinterpret_cast<const T*>(args.bias), ncol0 + cb, args.n);
+                                add_bias_32<T>(v2, reinterpret_cast<const T*>(args.bias), ncol0 + cb + 32, args.n);
+                            }
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) {
+                                pk[i] = pack2<T>(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
+                                pk[16 + i] = pack2<T>(__uint_as_float(v2[2 * i]), __uint_as_float(v2[2 * i + 1]));
+                            }
+                            put(cb);
+                        }
+                        continue;
+                    }
+                }
 #pragma unroll 1
                 for (int c0 = half * cols_per_box; c0 < ACC_N; c0 += 2 * cols_per_box) {
-                    const int col = nt * ACC_N + c0;
+                    const int col = ncol0 + c0;
                     uint32_t v[32], v2[32];
                     __syncwarp();
                     /* the accumulator reads of this chunk overlap the TMA engine draining the previous one */
@@ -880,7 +1054,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                 uint32_t v[32];
                 __syncwarp();                 /* tcgen05.ld is warp-collective */
                 tmem_load_32(tmem_base + ab * ACC_N + c0 + lane_field, v);
-                const int col = nt * ACC_N + c0;
+                const int col = ncol0 + c0;
                 if (!row_ok || col >= args.n) {
                     /* nothing to store for this lane */
                 } else if (args.splits > 1 || args.c_f32) {
@@ -963,6 +1137,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             if (lane == 0) {
                 if (PAIR) mbar_arrive_cluster(cluster_addr(tempty_bar(ab), 0));   /* the leader owns the accumulator hand-off */
                 else mbar_arrive(tempty_bar(ab));
+            }
             }
         }
     }

@@ -97,9 +97,12 @@ def test_tile_plan_model_on_the_host():
         assert lib.rpb_umma_plan(m, n, k, reduce, batch, dtype, sms, C.byref(bn), C.byref(sl), C.byref(pr)) == 0
         return bn.value, sl.value, pr.value
 
-    assert plan(65536, 8192, 8192) == (128, 1, 1)        # the row-sharded workload: 256 x 256 pair tiles, no K slices
-    assert plan(8192, 8192, 65536) == (128, 1, 1)        # its dB
-    assert plan(8192, 8192, 8192, sms=132) == (128, 1, 1)    # with SMs left to a collective
+    assert plan(65536, 8192, 8192) == (128, 1, 2)        # the row-sharded workload: double-width pair tiles, no K slices
+    assert plan(8192, 8192, 65536) == (128, 1, 2)        # its dB
+    assert plan(8192, 8192, 8192, sms=132) == (128, 1, 2)    # with SMs left to a collective
+    assert plan(4096, 4096, 4096) == (128, 1, 1)         # 3.46 waves of 256 x 256 tiles, the last one cut along K: stays
+    assert plan(2048, 2048, 4096) == (128, 1, 1)         # one wave: halving the tile count would idle half the SMs
+    assert plan(65536, 2048, 512, dtype=0)[2] == 1       # float32 never takes the double-width tile
     bn, sl, pr = plan(1024, 1024, 1024)                  # few tiles, short K: narrow one-CTA tiles, un-split
     assert (sl, pr) == (1, 0) and bn in (64, 128)
     assert plan(4096, 4096, 64) == (256, 1, 0)           # K of one block: the pair's hand-offs do not pay

@@ -289,6 +289,45 @@ def test_every_tile_plan_gives_the_same_product(lib, dtype, plan, monkeypatch):
         lib.rpb_force_kernel(0)
 
 
+@pytest.mark.parametrize("dtype", ["bfloat16", "float16"])
+@pytest.mark.parametrize("plan", ["128,1,2", "128,3,2"])
+def test_double_width_pair_tile(lib, dtype, plan, monkeypatch):
+    """The 256 x 512 pair tile (two accumulators sharing the A tile; RPB_UMMA_PLAN's third field = 2), which the
+    planner takes for large 16-bit problems.  K of one, three and many blocks (shorter than, between and beyond the
+    lead of the first accumulator), ragged M/N/K with a last tile whose second accumulator is almost empty, every
+    operand orientation, batches, bias, C += AB, float32 output; and the same bits as the 256 x 256 tile."""
+    rng = np.random.default_rng(4100 + CODE[dtype] + len(plan) + int(plan[4]))
+    split = int(plan.split(",")[1]) > 1
+    kinds = (_lib.KERNEL_UMMA_SPLITK,) if split else (_lib.KERNEL_UMMA,)
+    shapes = [(256, 64, 512), (768, 192, 1536), (520, 1160, 776), (1024, 4096, 1024)]
+    for (m, k, n) in shapes:
+        a = rand_operand(rng, (1, 1, m, k), dtype); b = rand_operand(rng, (1, 1, k, n), dtype, scale=1 / np.sqrt(k))
+        outs = {}
+        for pl in (plan, "128,%s,1" % plan.split(",")[1]):
+            monkeypatch.setenv("RPB_UMMA_PLAN", pl)
+            outs[pl] = [run_ex(lib, dtype, a, b, ta=ta, tb=tb, expect=kinds if k >= 256 or not split else None, oracle=(m <= 768))
+                        for ta, tb in ((False, False), (True, False), (False, True), (True, True))]
+        for x, y in zip(*outs.values()):
+            assert np.array_equal(x, y), (m, k, n)
+    monkeypatch.setenv("RPB_UMMA_PLAN", plan)
+    m, k, n = 520, 1160, 776
+    a = rand_operand(rng, (3, 1, m, k), dtype); b = rand_operand(rng, (1, 1, k, n), dtype, scale=1 / np.sqrt(k))
+    run_ex(lib, dtype, a, b, expect=kinds, oracle=False)                                              # batched A, shared B
+    run_ex(lib, dtype, a[:1], b, tb=True, expect=kinds, oracle=False, bias=rand_operand(rng, (n,), dtype))
+    run_ex(lib, dtype, a[:1], b, c_init=rand_operand(rng, (1, m, n), dtype), expect=UMMA, oracle=False)   # register epilogue
+    # float32 output of the unrounded sums
+    ta_, tb_ = dev(a[0, 0], dtype), dev(b[0, 0], dtype)
+    out = dev(np.full((m, n), np.nan, np.float32), "float32")
+    g = rpb.RpbGemm(); lib.rpb_gemm_packed(C.byref(g), m, k, n); g.c_float32 = 1
+    assert lib.rp_matmul_ex(C.c_void_p(out.data_ptr), C.c_void_p(ta_.data_ptr), C.c_void_p(tb_.data_ptr), C.byref(g),
+                            CODE[dtype], 0, None) == 0
+    ref = f64(a[0, 0], dtype) @ f64(b[0, 0], dtype)
+    got = out.to_numpy().astype(np.float64)
+    assert np.isfinite(got).all()
+    assert np.abs(got - ref).max() <= 2e-6 * np.sqrt(k) * np.sqrt(np.mean(ref * ref))
+    assert lib.rpb_device_status(0) == 0
+
+
 @pytest.mark.parametrize("dtype", ["float32", "float64", "float16", "bfloat16"])
 def test_gate_epilogue_in_every_kernel_family(lib, dtype):
     """RpbGemm.epilogue = LSTM gates: applied inside the tcgen05 kernel's register epilogue when that writes C directly,
