@@ -83,9 +83,10 @@ def parse():
 # DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) of ONE forward launch of the tcgen05 GEMM at
 # K = N = 8192, from ncu captures at two row counts: the figure grows linearly with the rows (A and C are
 # streamed once per column group, B is re-read once per row block), so a launch of `rows` rows is the line
-# through the two captures.  (rows, bytes) pairs; None until both captures exist.
+# through the two captures.  (rows, bytes) pairs; None until both captures exist.  Captured with the 256 x 512
+# pair tile the planner takes for this workload (the 256 x 256 tile read 1.2061e9 / 2.2903e9 bytes).
 NCU_TRAFFIC_POINTS = {
-    "rowsharded_65536x8192x8192": ((8192, 1.2061e9), (16384, 2.2903e9)),
+    "rowsharded_65536x8192x8192": ((8192, 0.9560e9), (16384, 1.9076e9)),
 }
 
 
