@@ -25,6 +25,7 @@ namespace {
 
 constexpr int MAX_DEVICES = 64;
 constexpr int BAL_MAX_UNITS = 1024;       /* CTAs (pairs) a balanced launch may use: far above any SM count */
+constexpr int SYNC_CTRS = 8;              /* launches that overlap on the device (other streams) do not share a rendezvous counter */
 
 struct DeviceState {
     std::atomic<bool> ready{false};
@@ -40,6 +41,12 @@ struct DeviceState {
     int* bal_flags = nullptr;             /* hand-off counters of the balanced schedule: [slot][rank][ready, done], all
                                            * zero between launches (the kernel clears what it used) */
     std::atomic<bool> bal_dirty{false};   /* a kernel gave up part-way: clear the counters before the next use */
+    int* sync_ctrs = nullptr;             /* rendezvous of a launch's CTAs: SYNC_CTRS counters (one per launch, taken in turn), 128 bytes apart */
+    std::atomic<unsigned int> sync_serial{0};
+    std::mutex sync_mu;                   /* guards the three fields below */
+    cudaEvent_t sync_event = nullptr;     /* recorded behind the last launch that took the rendezvous */
+    cudaStream_t sync_stream = nullptr;
+    bool sync_recorded = false;
     std::mutex mu;                        /* guards the scratch fields: per device, because growing the scratch waits
                                            * for this device, whose work may in turn wait for another thread's GPU */
 };
@@ -159,6 +166,8 @@ int device_state(int device_id, DeviceState** out) {
             d.status = g_status_words + device_id;
             RPB_CUDA(cudaMalloc(&d.bal_flags, sizeof(int) * 4 * BAL_MAX_UNITS));
             RPB_CUDA(cudaMemset(d.bal_flags, 0, sizeof(int) * 4 * BAL_MAX_UNITS));
+            RPB_CUDA(cudaMalloc(&d.sync_ctrs, SYNC_CTRS * 128));
+            RPB_CUDA(cudaMemset(d.sync_ctrs, 0, SYNC_CTRS * 128));
             RPB_CUDA(cudaEventCreateWithFlags(&d.scratch_free, cudaEventDisableTiming));
             {   /* temporaries for packed operands come from the stream-ordered pool: let it keep freed blocks */
                 const char* e = getenv("RPB_POOL");
@@ -853,6 +862,51 @@ int launch_umma(const RpbProblem& p, void* C, const void* A, const void* B, Devi
             }
         }
     }
+    /* Rendezvous of the CTAs (pairs) at tile starts and every 32 K blocks, for launches of several waves of whole tiles
+     * in round-robin order (Args.sync_ctr): without it the units drift apart by 2-3% per tile and every unit fetches
+     * its operand panels from L2 by itself; in step, the L2 request coalescer serves units that share a panel with one
+     * lookup (measured on 32768 x 8192 x 8192 bf16: sectors delivered per sector read 1.11 -> 1.2, DRAM reads -17%,
+     * 3-5% less time at the burst clock, 2-4% more throughput under the power cap).  RPB_TILE_SYNC=0 switches it off,
+     * 1 = tile starts only, n > 1 = every n K blocks.
+     * The units wait for one another, so all CTAs of the launch must be resident: a persistent grid of at most one CTA
+     * per SM is, unless another kernel holds SMs for as long as this one runs.  Two such launches that share the SMs
+     * could each wait for CTAs the other one keeps from starting, so a launch only takes the rendezvous when the
+     * previous one that did has finished or sits earlier in the same stream, and never inside a stream capture (a
+     * replayed graph may run beside anything).  The wait itself is bounded like every other and reports through the
+     * status word.  The counter is one of SYNC_CTRS, zeroed in stream order before the launch. */
+    bool sync_launch = false;
+    std::unique_lock<std::mutex> sync_lock(d->sync_mu, std::defer_lock);
+    {
+        const char* e = getenv("RPB_TILE_SYNC");
+        const int env = e ? atoi(e) : 32;
+        const long long units = pair ? sms / 2 : sms;
+        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+        if (env > 0 && !a.bal && a.tail_splits == 1 && a.splits == 1 && p.batch == 1 && tiles >= 3 * units) {
+            if (cudaStreamIsCapturing(stream, &cap) != cudaSuccess) { cudaGetLastError(); cap = cudaStreamCaptureStatusActive; }
+            if (cap == cudaStreamCaptureStatusNone) {
+                sync_lock.lock();
+                bool free_now = !d->sync_recorded || d->sync_stream == stream;
+                if (!free_now) {
+                    const cudaError_t q = cudaEventQuery(d->sync_event);
+                    if (q == cudaSuccess) free_now = true;
+                    else cudaGetLastError();                        /* cudaErrorNotReady is not an error here */
+                }
+                if (free_now && !d->sync_event && cudaEventCreateWithFlags(&d->sync_event, cudaEventDisableTiming) != cudaSuccess) {
+                    cudaGetLastError();
+                    free_now = false;
+                }
+                if (free_now) {
+                    int* ctr = d->sync_ctrs + (size_t)(d->sync_serial.fetch_add(1) % SYNC_CTRS) * 32;
+                    RPB_CUDA(cudaMemsetAsync(ctr, 0, sizeof(int), stream));
+                    a.sync_ctr = ctr;
+                    a.sync_every = env > 1 ? env : 0;
+                    sync_launch = true;
+                } else {
+                    sync_lock.unlock();
+                }
+            }
+        }
+    }
     if (a.act) t_act_fused = true;
     int grid = (int)(a.total_work < sms ? a.total_work : sms);
     int rc;
@@ -868,6 +922,11 @@ int launch_umma(const RpbProblem& p, void* C, const void* A, const void* B, Devi
     else if (BN == 64) rc = launch_umma_bn<T, 64>(pa.mn_major, pb.mn_major, ma, mb, mc, mp, a, grid, stream);
     else if (BN == 128) rc = launch_umma_bn<T, 128>(pa.mn_major, pb.mn_major, ma, mb, mc, mp, a, grid, stream);
     else rc = launch_umma_bn<T, 256>(pa.mn_major, pb.mn_major, ma, mb, mc, mp, a, grid, stream);
+    if (sync_launch) {
+        if (!rc && cudaEventRecord(d->sync_event, stream) == cudaSuccess) { d->sync_stream = stream; d->sync_recorded = true; }
+        else cudaGetLastError();
+        sync_lock.unlock();
+    }
     if (rc) return -1;
     if ((a.bal || a.tail_fuse) && release_scratch(d, stream)) return -1;
     if (a.tail_splits > 1 && !a.tail_fuse) {

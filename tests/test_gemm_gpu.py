@@ -328,6 +328,47 @@ def test_double_width_pair_tile(lib, dtype, plan, monkeypatch):
     assert lib.rpb_device_status(0) == 0
 
 
+@pytest.mark.parametrize("plan", ["64,1,0", "128,1,1", "128,1,2"])
+def test_rendezvous_of_the_ctas_changes_no_bit_and_never_crosses_streams(lib, plan, monkeypatch):
+    """Launches of several waves of whole tiles keep their CTAs (pairs) in step with a counter they all wait on at
+    tile starts and every few K blocks.  The product must be the same bits with and without it; and two such
+    launches on two streams at once must both finish (the second one runs without the rendezvous, because CTAs of
+    two kernels that each wait for all of their own could keep one another from starting)."""
+    import torch
+    dtype = "bfloat16"
+    monkeypatch.setenv("RPB_UMMA_PLAN", plan)
+    rng = np.random.default_rng(6100 + len(plan) + int(plan[0]))
+    m, k, n = 4104, 328, 4232                       # 14+ waves of any tile shape, ragged edges, 6 K blocks
+    a = rand_operand(rng, (m, k), dtype); b = rand_operand(rng, (k, n), dtype, scale=1 / np.sqrt(k))
+    ta, tb = dev(a, dtype), dev(b, dtype)
+    g = rpb.RpbGemm(); lib.rpb_gemm_packed(C.byref(g), m, k, n)
+
+    def run(tc, stream=None):
+        assert lib.rp_matmul_ex(C.c_void_p(tc.data_ptr), C.c_void_p(ta.data_ptr), C.c_void_p(tb.data_ptr), C.byref(g),
+                                CODE[dtype], 0, C.c_void_p(stream) if stream else None) == 0
+    blank = lambda: dev(np.zeros((m, n), np.uint16), dtype)
+    outs = {}
+    for setting in ("0", "1", "2", "32"):           # off, tile starts only, every 2 K blocks, the default
+        monkeypatch.setenv("RPB_TILE_SYNC", setting)
+        tc = blank(); run(tc)
+        outs[setting] = tc.to_numpy()
+        assert lib.rpb_device_status(0) == 0
+    for setting in ("1", "2", "32"):
+        assert np.array_equal(outs[setting], outs["0"]), setting
+    ref = f64(a, dtype) @ f64(b, dtype)
+    check_close(outs["0"], O.narrow(ref.astype(np.float32), CODE[dtype]), dtype, k, f"plan {plan}")
+    # two streams at once, several rounds
+    monkeypatch.setenv("RPB_TILE_SYNC", "2")
+    s1, s2 = torch.cuda.Stream(), torch.cuda.Stream()
+    c1, c2 = blank(), blank()
+    torch.cuda.synchronize()
+    for _ in range(4):
+        run(c1, s1.cuda_stream); run(c2, s2.cuda_stream)
+    torch.cuda.synchronize()
+    assert lib.rpb_device_status(0) == 0
+    assert np.array_equal(c1.to_numpy(), outs["0"]) and np.array_equal(c2.to_numpy(), outs["0"])
+
+
 @pytest.mark.parametrize("dtype", ["float32", "float64", "float16", "bfloat16"])
 def test_gate_epilogue_in_every_kernel_family(lib, dtype):
     """RpbGemm.epilogue = LSTM gates: applied inside the tcgen05 kernel's register epilogue when that writes C directly,
