@@ -43,10 +43,6 @@ struct DeviceState {
     std::atomic<bool> bal_dirty{false};   /* a kernel gave up part-way: clear the counters before the next use */
     int* sync_ctrs = nullptr;             /* rendezvous of a launch's CTAs: SYNC_CTRS counters (one per launch, taken in turn), 128 bytes apart */
     std::atomic<unsigned int> sync_serial{0};
-    std::mutex sync_mu;                   /* guards the three fields below */
-    cudaEvent_t sync_event = nullptr;     /* recorded behind the last launch that took the rendezvous */
-    cudaStream_t sync_stream = nullptr;
-    bool sync_recorded = false;
     std::mutex mu;                        /* guards the scratch fields: per device, because growing the scratch waits
                                            * for this device, whose work may in turn wait for another thread's GPU */
 };
@@ -867,44 +863,28 @@ int launch_umma(const RpbProblem& p, void* C, const void* A, const void* B, Devi
      * its operand panels from L2 by itself; in step, the L2 request coalescer serves units that share a panel with one
      * lookup (measured on 32768 x 8192 x 8192 bf16: sectors delivered per sector read 1.11 -> 1.2, DRAM reads -17%,
      * 3-5% less time at the burst clock, 2-4% more throughput under the power cap).  RPB_TILE_SYNC=0 switches it off,
-     * 1 = tile starts only, n > 1 = every n K blocks.
-     * The units wait for one another, so all CTAs of the launch must be resident: a persistent grid of at most one CTA
-     * per SM is, unless another kernel holds SMs for as long as this one runs.  Two such launches that share the SMs
-     * could each wait for CTAs the other one keeps from starting, so a launch only takes the rendezvous when the
-     * previous one that did has finished or sits earlier in the same stream, and never inside a stream capture (a
-     * replayed graph may run beside anything).  The wait itself is bounded like every other and reports through the
-     * status word.  The counter is one of SYNC_CTRS, zeroed in stream order before the launch. */
-    bool sync_launch = false;
-    std::unique_lock<std::mutex> sync_lock(d->sync_mu, std::defer_lock);
+     * 1 = tile starts only, n > 1 = every n K blocks, -n = the same for tiles of any length.
+     * The units wait for one another, which presumes that all CTAs of the launch are resident: a persistent grid of at
+     * most one CTA per SM is, unless another kernel holds SMs meanwhile.  The wait is therefore soft: a unit that has
+     * waited ~30 us switches the rendezvous off for the rest of the launch (Args.sync_patience), so the worst case --
+     * two such launches sharing the SMs, a replayed graph beside anything -- costs that once.  The two words are one of
+     * SYNC_CTRS pairs, taken in turn and zeroed in stream order before the launch (a memset node in a capture). */
     {
         const char* e = getenv("RPB_TILE_SYNC");
-        const int env = e ? atoi(e) : 32;
+        const int env_raw = e ? atoi(e) : 32;
+        const int env = env_raw < 0 ? -env_raw : env_raw;                           /* negative: tiles of any length (tests) */
         const long long units = pair ? sms / 2 : sms;
-        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
-        if (env > 0 && !a.bal && a.tail_splits == 1 && a.splits == 1 && p.batch == 1 && tiles >= 3 * units) {
-            if (cudaStreamIsCapturing(stream, &cap) != cudaSuccess) { cudaGetLastError(); cap = cudaStreamCaptureStatusActive; }
-            if (cap == cudaStreamCaptureStatusNone) {
-                sync_lock.lock();
-                bool free_now = !d->sync_recorded || d->sync_stream == stream;
-                if (!free_now) {
-                    const cudaError_t q = cudaEventQuery(d->sync_event);
-                    if (q == cudaSuccess) free_now = true;
-                    else cudaGetLastError();                        /* cudaErrorNotReady is not an error here */
-                }
-                if (free_now && !d->sync_event && cudaEventCreateWithFlags(&d->sync_event, cudaEventDisableTiming) != cudaSuccess) {
-                    cudaGetLastError();
-                    free_now = false;
-                }
-                if (free_now) {
-                    int* ctr = d->sync_ctrs + (size_t)(d->sync_serial.fetch_add(1) % SYNC_CTRS) * 32;
-                    RPB_CUDA(cudaMemsetAsync(ctr, 0, sizeof(int), stream));
-                    a.sync_ctr = ctr;
-                    a.sync_every = env > 1 ? env : 0;
-                    sync_launch = true;
-                } else {
-                    sync_lock.unlock();
-                }
-            }
+        const long long whole = a.tail_splits > 1 ? a.tail_begin : a.total_work;     /* whole tiles in round-robin order */
+        /* long tiles only: a rendezvous costs the producer about a microsecond, which its lead over the tensor pipe
+         * (the stages in flight, ~2-3 us) hides a few times per 50+ us tile but not twice per 23 us tile (bf16 4096^3
+         * with it: 100 -> 109 us) */
+        if (env > 0 && !a.bal && a.splits == 1 && p.batch == 1 && whole >= 3 * units && (a.k_iters >= 128 || env_raw < 0)) {
+            int* ctr = d->sync_ctrs + (size_t)(d->sync_serial.fetch_add(1) % SYNC_CTRS) * 32;
+            RPB_CUDA(cudaMemsetAsync(ctr, 0, 2 * sizeof(int), stream));
+            a.sync_ctr = ctr;
+            a.sync_every = env > 1 ? env : 0;
+            a.sync_items = whole;
+            a.sync_patience = 60000;
         }
     }
     if (a.act) t_act_fused = true;
@@ -922,11 +902,6 @@ int launch_umma(const RpbProblem& p, void* C, const void* A, const void* B, Devi
     else if (BN == 64) rc = launch_umma_bn<T, 64>(pa.mn_major, pb.mn_major, ma, mb, mc, mp, a, grid, stream);
     else if (BN == 128) rc = launch_umma_bn<T, 128>(pa.mn_major, pb.mn_major, ma, mb, mc, mp, a, grid, stream);
     else rc = launch_umma_bn<T, 256>(pa.mn_major, pb.mn_major, ma, mb, mc, mp, a, grid, stream);
-    if (sync_launch) {
-        if (!rc && cudaEventRecord(d->sync_event, stream) == cudaSuccess) { d->sync_stream = stream; d->sync_recorded = true; }
-        else cudaGetLastError();
-        sync_lock.unlock();
-    }
     if (rc) return -1;
     if ((a.bal || a.tail_fuse) && release_scratch(d, stream)) return -1;
     if (a.tail_splits > 1 && !a.tail_fuse) {

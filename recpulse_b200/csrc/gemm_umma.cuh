@@ -127,12 +127,16 @@ struct Args {
     long long wait_limit;  /* bound of every mbarrier wait, in SM clock cycles */
     uint32_t epi_sleep_ns; /* back-off between polls of the epilogue warps' wait for a finished accumulator (0 = spin) */
     int epi_pipe;          /* 1: the 16-bit TMA-store epilogue runs software-pipelined (RPB_EPI_PIPE=0 for the plain loop) */
-    /* Tile-start rendezvous (sync_ctr != null; round-robin order of whole tiles only): before a CTA's (pair's)
-     * producers load their nth tile, every unit that has an nth tile must have got there -- the leader's producer counts
-     * itself in, both producers poll the launch's counter (zeroed by the host before the launch) until it reaches
-     * min((n + 1) * units, tiles).  Units that share an operand panel then ask L2 for the same lines at nearly the
-     * same time, which the L2 request coalescer turns into one lookup. */
+    /* Rendezvous of the units (sync_ctr != null; round-robin order, the whole tiles of the first sync_items work items):
+     * before a CTA's (pair's) producers load their nth tile, and every sync_every K blocks inside it, every unit whose
+     * nth item takes part must have got there -- the leader's producer counts itself in at sync_ctr[0], both producers
+     * poll it until it reaches the number of arrivals due by then.  Units that share an operand panel then ask L2 for the
+     * same lines at nearly the same time, which the L2 request coalescer turns into one lookup.  sync_ctr[1] is the
+     * launch's `off` word: a unit that has waited sync_patience clocks sets it and nobody waits any more.  The host zeroes
+     * both words in stream order before the launch. */
     int* sync_ctr;
+    long long sync_items;
+    long long sync_patience;
     int sync_every;        /* also every so many K blocks inside a tile (0: at tile starts only) */
     int wide_skew;         /* double-width tiles: K blocks by which the second accumulator trails the first at a tile's ends */
     int c_f32;             /* 1: the output is packed float32 [batch][m][n] (unrounded sums of 16-bit operands); the
@@ -552,33 +556,35 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             uint32_t sa = smem_base, eb = empty_bar(0), fb = full_bar(0);
             bool alive = true, traced = false;
             long long w = work_begin; int phase_w = 0; Item item;
-            /* rendezvous of all units that are at the same point of their nth tile (Args.sync_ctr) */
+            /* rendezvous of all units that are at the same point of their nth whole tile (Args.sync_ctr).  Soft: a unit
+             * that has waited `sync_patience` clocks sets the launch's `off` word and from then on nobody waits -- so CTAs
+             * that are not resident (another kernel holds their SMs) cost one patience, not a hang or an error. */
             long long tile_no = 0; int sync_target = 0;
-            auto rendezvous = [&]() -> bool {
-                const long long left_units = args.total_work - tile_no * work_step;      /* units that have an nth tile */
-                sync_target += (int)(left_units < work_step ? left_units : work_step);
-                int ok = 1;
+            bool sync_on = args.sync_ctr != nullptr;
+            auto rendezvous = [&]() {
+                long long part = args.sync_items - tile_no * work_step;                  /* units whose nth item takes part */
+                part = part < 0 ? 0 : (part < work_step ? part : work_step);
+                sync_target += (int)part;
+                int off = 0;
                 if (lane == 0) {
                     if (leader) atomicAdd(args.sync_ctr, 1);
                     const volatile int* c = args.sync_ctr;
                     const long long t0 = clock64();
-                    for (uint32_t i = 0; *c < sync_target; ++i) {
+                    for (uint32_t i = 0; c[0] < sync_target; ++i) {
+                        if (c[1]) break;
                         __nanosleep(100);
-                        if ((i & 63u) == 63u && (*abort_flag || clock64() - t0 > args.wait_limit)) { ok = 0; break; }
+                        if ((i & 15u) == 15u && clock64() - t0 > args.sync_patience) { atomicExch(args.sync_ctr + 1, 1); break; }
                     }
-                    if (!ok) {
-                        *abort_flag = 1;
-                        volatile int* st = args.status;
-                        if (*st == 0) *st = 7;
-                        __threadfence_system();
-                    }
+                    off = c[1];
                 }
-                return __shfl_sync(0xffffffffu, ok, 0) != 0;
+                if (__shfl_sync(0xffffffffu, off, 0)) sync_on = false;
             };
             while (alive && next_item(w, phase_w, item)) {
                 const int mt = item.mt, nt = item.nt, bz = item.bz, it0 = item.it0, it1 = item.it1;
                 int since_sync = 0;
-                if (args.sync_ctr && !rendezvous()) { alive = false; break; }
+                /* whole tiles of the full waves take part (not the K slices of a cut last wave) */
+                const bool sync_item = sync_on && tile_no * work_step + unit_id < args.sync_items;
+                if (sync_item) rendezvous();
                 const int row0 = mt * TILE_M + (int)cta_rank * BLOCK_M;     /* this CTA's rows of A */
                 const int col0 = nt * TILE_N + (int)cta_rank * BN;          /* this CTA's columns of B (first accumulator) */
                 const int r0 = it0 / args.k_blocks;
@@ -586,9 +592,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                 int a_r = r0 * args.a_reduce_mul, b_r = r0 * args.b_reduce_mul;
                 const int a_b = bz * args.a_batch_mul, b_b = bz * args.b_batch_mul;
                 for (int left = it1 - it0; left > 0; --left) {
-                    if (args.sync_ctr && args.sync_every > 0 && ++since_sync > args.sync_every) {
+                    if (sync_item && sync_on && args.sync_every > 0 && ++since_sync > args.sync_every) {
                         since_sync = 1;
-                        if (!rendezvous()) { alive = false; break; }
+                        rendezvous();
                     }
                     if (!mbar_wait_warp(eb, parity, abort_flag, args.status, 1, args.wait_limit)) { alive = false; break; }
                     if (args.trace && !traced && lane == 0) { trace_mark(args.trace, 2); }

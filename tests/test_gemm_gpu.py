@@ -329,11 +329,12 @@ def test_double_width_pair_tile(lib, dtype, plan, monkeypatch):
 
 
 @pytest.mark.parametrize("plan", ["64,1,0", "128,1,1", "128,1,2"])
-def test_rendezvous_of_the_ctas_changes_no_bit_and_never_crosses_streams(lib, plan, monkeypatch):
+def test_rendezvous_of_the_ctas_changes_no_bit_and_cannot_hang(lib, plan, monkeypatch):
     """Launches of several waves of whole tiles keep their CTAs (pairs) in step with a counter they all wait on at
-    tile starts and every few K blocks.  The product must be the same bits with and without it; and two such
-    launches on two streams at once must both finish (the second one runs without the rendezvous, because CTAs of
-    two kernels that each wait for all of their own could keep one another from starting)."""
+    tile starts and every few K blocks.  The product must be the same bits with and without it.  The wait is soft
+    (a unit that has waited ~30 us switches it off for the launch), so two such launches on two streams at once --
+    whose CTAs may keep one another from starting -- must both finish with the right bits and a clean status, and
+    so must a launch replayed from a CUDA graph."""
     import torch
     dtype = "bfloat16"
     monkeypatch.setenv("RPB_UMMA_PLAN", plan)
@@ -348,17 +349,17 @@ def test_rendezvous_of_the_ctas_changes_no_bit_and_never_crosses_streams(lib, pl
                                 CODE[dtype], 0, C.c_void_p(stream) if stream else None) == 0
     blank = lambda: dev(np.zeros((m, n), np.uint16), dtype)
     outs = {}
-    for setting in ("0", "1", "2", "32"):           # off, tile starts only, every 2 K blocks, the default
+    for setting in ("0", "-1", "-2", "-32"):        # off; tile starts only, every 2 / 32 K blocks (negative: short tiles too)
         monkeypatch.setenv("RPB_TILE_SYNC", setting)
         tc = blank(); run(tc)
         outs[setting] = tc.to_numpy()
         assert lib.rpb_device_status(0) == 0
-    for setting in ("1", "2", "32"):
+    for setting in ("-1", "-2", "-32"):
         assert np.array_equal(outs[setting], outs["0"]), setting
     ref = f64(a, dtype) @ f64(b, dtype)
     check_close(outs["0"], O.narrow(ref.astype(np.float32), CODE[dtype]), dtype, k, f"plan {plan}")
     # two streams at once, several rounds
-    monkeypatch.setenv("RPB_TILE_SYNC", "2")
+    monkeypatch.setenv("RPB_TILE_SYNC", "-2")
     s1, s2 = torch.cuda.Stream(), torch.cuda.Stream()
     c1, c2 = blank(), blank()
     torch.cuda.synchronize()
@@ -367,6 +368,19 @@ def test_rendezvous_of_the_ctas_changes_no_bit_and_never_crosses_streams(lib, pl
     torch.cuda.synchronize()
     assert lib.rpb_device_status(0) == 0
     assert np.array_equal(c1.to_numpy(), outs["0"]) and np.array_equal(c2.to_numpy(), outs["0"])
+    # captured once, replayed three times (the counter is zeroed by a memset node of the graph)
+    c3 = blank()
+    side = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        run(c3, torch.cuda.current_stream().cuda_stream)
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize()
+    assert lib.rpb_device_status(0) == 0
+    assert np.array_equal(c3.to_numpy(), outs["0"])
+    del graph
+    assert lib.rpb_scratch_reset(0) == 0
 
 
 @pytest.mark.parametrize("dtype", ["float32", "float64", "float16", "bfloat16"])
