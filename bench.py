@@ -74,7 +74,7 @@ def parse():
     p.add_argument("--no-workloads", action="store_true", help="time only --workload, not the other configurations")
     p.add_argument("--no-graph", action="store_true", help="do not replay the step from a CUDA graph on launch-bound workloads")
     p.add_argument("--compare", action="store_true", help="also time the reference as shipped and the node path on the same step")
-    p.add_argument("--comm-sms", type=int, default=16, help="SMs the dA GEMM leaves to the dB reduction (N > 1)")
+    p.add_argument("--comm-sms", type=int, default=-1, help="SMs the dA GEMM leaves to the dB reduction (N > 1); -1: the library chooses 16 or 32")
     p.add_argument("--db-wire", type=int, default=0, help="0: dB partials cross NVLink in float32; 1: in the operand type")
     p.add_argument("--rows", type=int, default=0, help="override the row count M of the workload (profiling cases)")
     return p.parse_args()

@@ -302,8 +302,9 @@ RpbShard* rpb_shard_create(const void* unique_id, int rank, int world, int devic
 void rpb_shard_destroy(RpbShard* shard);
 int rpb_shard_rank(const RpbShard* shard);
 int rpb_shard_world(const RpbShard* shard);
-/* comm_sms: SMs the dA GEMM leaves free while the dB reduction is in flight (default 16; the GEMM
- * kernels are persistent and would otherwise keep the collective's thread blocks waiting).
+/* comm_sms: SMs the dA GEMM leaves free while the dB reduction is in flight (the GEMM kernels are
+ * persistent and would otherwise keep the collective's thread blocks waiting).  -1 (default): 16, or 32
+ * when the exchange is expected to outlast the GEMM (few rows per rank); 0: none.
  * db_wire: 0 (default) = the float16 / bfloat16 dB partials cross NVLink as float32 sums and are
  * rounded once after the reduction; 1 = all-reduce in the operand type (half the bytes, one extra
  * rounding per reduction step). */

@@ -172,7 +172,7 @@ struct RpbShard {
     float* stage = nullptr;            /* float32 dB partials [k][n] */
     size_t stage_bytes = 0;
     int sm_count = 0;
-    int comm_sms = 16;                 /* SMs the dA GEMM leaves to the collective's thread blocks */
+    int comm_sms = -1;                 /* SMs the dA GEMM leaves to the collective's thread blocks; -1: chosen per call */
     int db_wire = 0;                   /* 0: float32 reduce-scatter + rounded all-gather; 1: all-reduce in the operand type */
     bool pending = false;              /* a dB reduction is in flight on the side stream */
 };
@@ -368,7 +368,7 @@ int rpb_shard_world(const RpbShard* s) { return s ? s->world : -1; }
 unsigned long long rpb_shard_collective_count(void) { return g_collectives.load(); }
 
 int rpb_shard_configure(RpbShard* s, int comm_sms, int db_wire) {
-    if (!s || comm_sms < 0 || db_wire < 0 || db_wire > 1) return -1;
+    if (!s || comm_sms < -1 || db_wire < 0 || db_wire > 1) return -1;
     s->comm_sms = comm_sms;
     s->db_wire = db_wire;
     return 0;
@@ -413,7 +413,18 @@ int rp_matmul_rowsharded_backward(RpbShard* s, void* dA_rows, void* dB, const vo
         g.b_row = 1; g.b_col = n;             /* B^T read through swapped strides */
         /* the GEMM kernels are persistent and fill every SM; a collective launched beside one would wait for it
          * to end, so while a reduction is in flight the GEMM leaves comm_sms SMs free */
-        if (s->pending && s->comm_sms > 0 && s->sm_count - s->comm_sms >= 2) g.max_sms = s->sm_count - s->comm_sms;
+        int cs = s->comm_sms;
+        if (cs < 0) {
+            /* 16 SMs let a 2-4 rank reduction finish inside the dA GEMM.  When the rows per rank get few (8 ranks of the
+             * 65536-row workload) the exchange outlasts the GEMM and is what the step waits for: NCCL then needs all of
+             * its thread blocks resident.  Measured at 8 GPUs, 8192 rows per rank: 2.72 ms per step with 16 SMs left free,
+             * 2.41 with 32, 2.44 with 48.  Model: the GEMM at 1.3 PFLOP/s against the exchanged bytes at 260 GB/s. */
+            const double es = (double)rpb_dtype_size((int)dtype);
+            const double t_gemm = 2.0 * (double)rows * k * n / 1.3e15;
+            const double t_comm = (double)(s->world - 1) / s->world * (double)k * n * (4.0 + es) / 260e9;
+            cs = t_comm > t_gemm ? 32 : 16;
+        }
+        if (s->pending && cs > 0 && s->sm_count - cs >= 2) g.max_sms = s->sm_count - cs;
         if (rp_matmul_ex(dA_rows, dC_rows, B, &g, dtype, s->device, stream)) return -1;
     }
     return rpb_shard_db_end(s, st);

@@ -84,7 +84,7 @@ class RowShardedMatmul:
         if not self.handle:
             raise RuntimeError("rpb_shard_create failed")
         if comm_sms is not None or db_wire is not None:
-            self.lib.rpb_shard_configure(self.handle, 16 if comm_sms is None else comm_sms, 0 if db_wire is None else db_wire)
+            self.lib.rpb_shard_configure(self.handle, -1 if comm_sms is None else comm_sms, 0 if db_wire is None else db_wire)
         if world > 1:
             self._check(self.lib.rp_shard_replicate(self.handle, _ptr(b), b.numel() * b.element_size(), src, self._stream()),
                         "rp_shard_replicate")
