@@ -138,6 +138,7 @@ struct Args {
     long long sync_items;
     long long sync_patience;
     int sync_every;        /* also every so many K blocks inside a tile (0: at tile starts only) */
+    unsigned sync_sleep;   /* ns between polls of the counter */
     int wide_skew;         /* double-width tiles: K blocks by which the second accumulator trails the first at a tile's ends */
     int c_f32;             /* 1: the output is packed float32 [batch][m][n] (unrounded sums of 16-bit operands); the
                             * epilogue then writes it like a K slice: `partial` = the output when splits == 1 */
@@ -572,7 +573,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                     const long long t0 = clock64();
                     for (uint32_t i = 0; c[0] < sync_target; ++i) {
                         if (c[1]) break;
-                        __nanosleep(100);
+                        if (args.sync_sleep) __nanosleep(args.sync_sleep);
                         if ((i & 15u) == 15u && clock64() - t0 > args.sync_patience) { atomicExch(args.sync_ctr + 1, 1); break; }
                     }
                     off = c[1];
