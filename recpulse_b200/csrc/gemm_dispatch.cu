@@ -885,9 +885,10 @@ int launch_umma(const RpbProblem& p, void* C, const void* A, const void* B, Devi
             a.sync_every = env > 1 ? env : 0;
             a.sync_items = whole;
             a.sync_patience = 60000;
-            /* pause between polls of the counter: none.  The tighter the units leave a rendezvous, the more of their
-             * requests coalesce (32768 x 8192 x 8192 and 8192 x 32768 x 8192 under the power cap: 0 ns 1370 / 1392 TFLOP/s,
-             * 100 ns 1366 / 1386, 400 ns 1358 / 1378); a poll is one L2 round trip, ~150 pollers for about a microsecond */
+            /* pause between polls of the counter: none (then four polls are kept in flight, a quarter of a round trip
+             * apart).  The tighter the units leave a rendezvous, the more of their requests coalesce (32768 x 8192 x 8192
+             * and 8192 x 32768 x 8192 under the power cap: pauses of 400 / 100 / 0 ns 1358 / 1366 / 1370 and 1378 / 1386 /
+             * 1392 TFLOP/s; staggered polls another +0.2 / +0.5%); ~150 pollers for about a microsecond */
             a.sync_sleep = 0;
             if (const char* se = getenv("RPB_SYNC_SLEEP_NS")) { const int v = atoi(se); a.sync_sleep = (unsigned)(v < 0 ? 0 : v); }
         }

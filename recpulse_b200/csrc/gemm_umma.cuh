@@ -571,10 +571,34 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                     if (leader) atomicAdd(args.sync_ctr, 1);
                     const volatile int* c = args.sync_ctr;
                     const long long t0 = clock64();
-                    for (uint32_t i = 0; c[0] < sync_target; ++i) {
-                        if (c[1]) break;
-                        if (args.sync_sleep) __nanosleep(args.sync_sleep);
-                        if ((i & 15u) == 15u && clock64() - t0 > args.sync_patience) { atomicExch(args.sync_ctr + 1, 1); break; }
+                    if (args.sync_sleep) {
+                        for (uint32_t i = 0; c[0] < sync_target; ++i) {
+                            if (c[1]) break;
+                            __nanosleep(args.sync_sleep);
+                            if ((i & 15u) == 15u && clock64() - t0 > args.sync_patience) { atomicExch(args.sync_ctr + 1, 1); break; }
+                        }
+                    } else {
+                        /* Four polls in flight, issued a quarter of an L2 round trip apart and each re-issued when it
+                         * returns: the counter is sampled every ~150 ns instead of once per round trip, so the units leave
+                         * the rendezvous closer together. */
+                        int v0 = c[0]; __nanosleep(120);
+                        int v1 = c[0]; __nanosleep(120);
+                        int v2 = c[0]; __nanosleep(120);
+                        int v3 = c[0];
+                        for (uint32_t i = 0;; ++i) {
+                            if (v0 >= sync_target) break;
+                            v0 = c[0];
+                            if (v1 >= sync_target) break;
+                            v1 = c[0];
+                            if (v2 >= sync_target) break;
+                            v2 = c[0];
+                            if (v3 >= sync_target) break;
+                            v3 = c[0];
+                            if ((i & 3u) == 3u && (c[1] || clock64() - t0 > args.sync_patience)) {
+                                if (!c[1]) atomicExch(args.sync_ctr + 1, 1);
+                                break;
+                            }
+                        }
                     }
                     off = c[1];
                 }
