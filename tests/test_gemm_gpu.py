@@ -383,6 +383,34 @@ def test_rendezvous_of_the_ctas_changes_no_bit_and_cannot_hang(lib, plan, monkey
     assert lib.rpb_scratch_reset(0) == 0
 
 
+def test_placement_aware_tile_order_changes_no_bit(lib, monkeypatch):
+    """On a full grid of CTA pairs the library learns where the hardware places the clusters (the first such launch
+    records every cluster's SM) and from then on deals the tiles of each wave so that the pairs of one GPC take a
+    3 x 3 block of them.  Which pair computes a tile must not change a bit of it: launches before and after the
+    permutation exists are compared with RPB_PLACE=0, ragged edges and a last wave that is not full included."""
+    dtype = "bfloat16"
+    rng = np.random.default_rng(7300)
+    for (m, k, n) in ((16384, 264, 8192), (20000, 136, 6152)):       # 1024 and 948 double-width tiles, column groups of 6
+        a = rand_operand(rng, (m, k), dtype); b = rand_operand(rng, (k, n), dtype, scale=1 / np.sqrt(k))
+        ta, tb = dev(a, dtype), dev(b, dtype)
+        g = rpb.RpbGemm(); lib.rpb_gemm_packed(C.byref(g), m, k, n)
+
+        def run():
+            tc = dev(np.zeros((m, n), np.uint16), dtype)
+            assert lib.rp_matmul_ex(C.c_void_p(tc.data_ptr), C.c_void_p(ta.data_ptr), C.c_void_p(tb.data_ptr), C.byref(g),
+                                    CODE[dtype], 0, None) == 0
+            assert lib.rpb_last_kernel() == _lib.KERNEL_UMMA
+            return tc.to_numpy()
+        monkeypatch.setenv("RPB_PLACE", "0")
+        plain = run()
+        monkeypatch.delenv("RPB_PLACE")
+        for _ in range(4):
+            assert np.array_equal(run(), plain)
+        ref = f64(a, dtype) @ f64(b, dtype)
+        check_close(plain, O.narrow(ref.astype(np.float32), CODE[dtype]), dtype, k, f"{m}x{k}x{n}")
+    assert lib.rpb_device_status(0) == 0
+
+
 @pytest.mark.parametrize("dtype", ["float32", "float64", "float16", "bfloat16"])
 def test_gate_epilogue_in_every_kernel_family(lib, dtype):
     """RpbGemm.epilogue = LSTM gates: applied inside the tcgen05 kernel's register epilogue when that writes C directly,
