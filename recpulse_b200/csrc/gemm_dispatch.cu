@@ -42,13 +42,12 @@ struct DeviceState {
     int* bal_flags = nullptr;             /* hand-off counters of the balanced schedule: [slot][rank][ready, done], all
                                            * zero between launches (the kernel clears what it used) */
     std::atomic<bool> bal_dirty{false};   /* a kernel gave up part-way: clear the counters before the next use */
-    /* placement-aware tile order of the pair kernels (Args.wave_slot): state 0 nothing known, 1 a launch is recording
-     * where the hardware puts the clusters, 2 permutation ready, 3 the placement does not fit the scheme */
+    /* placement-aware tile order of the pair kernels (Args.wave_slot): state 0 = eligible launches record where the
+     * hardware puts the clusters, 2 = permutation ready, 3 = the placement does not fit the scheme */
     std::mutex place_mu;
     int place_state = 0;
-    int* place_smid = nullptr;            /* mapped host memory, PLACE_MAX ints */
-    unsigned char* place_slot = nullptr;  /* device memory, PLACE_MAX bytes */
-    cudaEvent_t place_event = nullptr;
+    int* place_smid = nullptr;            /* mapped host memory, PLACE_MAX ints, -1 until a kernel wrote them */
+    unsigned char place_slot[PLACE_MAX];
     int* sync_ctrs = nullptr;             /* rendezvous of a launch's CTAs: SYNC_CTRS counters (one per launch, taken in turn), 128 bytes apart */
     std::atomic<unsigned int> sync_serial{0};
     std::mutex mu;                        /* guards the scratch fields: per device, because growing the scratch waits
@@ -170,6 +169,12 @@ int device_state(int device_id, DeviceState** out) {
             d.status = g_status_words + device_id;
             RPB_CUDA(cudaMalloc(&d.bal_flags, sizeof(int) * 4 * BAL_MAX_UNITS));
             RPB_CUDA(cudaMemset(d.bal_flags, 0, sizeof(int) * 4 * BAL_MAX_UNITS));
+            {
+                void* w = nullptr;
+                RPB_CUDA(cudaHostAlloc(&w, sizeof(int) * PLACE_MAX, cudaHostAllocPortable | cudaHostAllocMapped));
+                d.place_smid = reinterpret_cast<int*>(w);
+                for (int i = 0; i < PLACE_MAX; ++i) d.place_smid[i] = -1;
+            }
             RPB_CUDA(cudaMalloc(&d.sync_ctrs, SYNC_CTRS * 128));
             RPB_CUDA(cudaMemset(d.sync_ctrs, 0, SYNC_CTRS * 128));
             RPB_CUDA(cudaEventCreateWithFlags(&d.scratch_free, cudaEventDisableTiming));
@@ -866,7 +871,6 @@ int launch_umma(const RpbProblem& p, void* C, const void* A, const void* B, Devi
             }
         }
     }
-    bool place_recording = false;
     /* Rendezvous of the CTAs (pairs) at tile starts and every 32 K blocks, for launches of several waves of whole tiles
      * in round-robin order (Args.sync_ctr): without it the units drift apart by 2-3% per tile and every unit fetches
      * its operand panels from L2 by itself; in step, the L2 request coalescer serves units that share a panel with one
@@ -905,9 +909,9 @@ int launch_umma(const RpbProblem& p, void* C, const void* A, const void* B, Devi
     /* Placement-aware tile order (Args.wave_slot) for pair kernels on the full grid of a 148-SM part, column groups of
      * six tiles.  Measured: SM ids are dealt round-robin over the 8 GPCs at TPC granularity (TPC t sits in GPC t % 8; six
      * GPCs have 9 TPCs, two have 10), the SMs of a GPC share an L2 request coalescer, and the hardware places cluster c of
-     * a full grid on the same TPC every time.  So the first such launch records the SM of every cluster; once it has
-     * finished, the host deals each GPC's nine pairs a 3 x 3 block of the 12 x 6 tiles a wave covers (the two left-over
-     * pairs take the two left-over tiles).  The permutation is indexed by cluster, so a launch that the hardware places
+     * a full grid on the same TPC every time.  So eligible launches record the SM of every cluster in mapped host memory
+     * until the table is complete; then the host deals each GPC's nine pairs a 3 x 3 block of the 12 x 6 tiles a wave
+     * covers (the two left-over pairs take the two left-over tiles) and passes the permutation by value.  The permutation is indexed by cluster, so a launch that the hardware places
      * differently is still correct, it only shares less.  16384 x 8192 x 8192 bf16 (ncu): sectors delivered per
      * sector read 1.32 -> 1.49 (cuBLAS 1.47), L2 lookups 328 -> 290 M; +0.9% under the power cap.  RPB_PLACE=0: off. */
     if (pair && a.splits == 1 && p.batch == 1 && !a.bal && d->sm_count == 148 && sms == 148 && a.group_n == 6 &&
@@ -915,42 +919,33 @@ int launch_umma(const RpbProblem& p, void* C, const void* A, const void* B, Devi
         const char* pe = getenv("RPB_PLACE");
         if (!(pe && atoi(pe) == 0)) {
             std::lock_guard<std::mutex> lock(d->place_mu);
-            if (d->place_state == 1 && cudaEventQuery(d->place_event) == cudaSuccess) {
-                /* the recording launch has finished: build the permutation */
-                bool ok = true;
-                unsigned char slot[PLACE_MAX]; bool seen_tpc[74] = {}, seen_slot[74] = {};
-                for (int c = 0; c < 74 && ok; ++c) {
-                    const int sm = d->place_smid[c], tpc = sm >> 1;
-                    if (sm < 0 || tpc >= 74 || seen_tpc[tpc]) { ok = false; break; }
-                    seen_tpc[tpc] = true;
-                    const int g8 = tpc & 7, q = tpc >> 3;
-                    const int sl = q >= 9 ? 72 + g8 : (3 * (g8 >> 1) + q / 3) * 6 + 3 * (g8 & 1) + q % 3;
-                    if (sl >= 74 || seen_slot[sl]) { ok = false; break; }
-                    seen_slot[sl] = true;
-                    slot[c] = (unsigned char)sl;
+            if (d->place_state == 0) {
+                /* has an earlier launch filled in every cluster's SM?  (plain reads of mapped host memory: nothing here
+                 * synchronises, queries or copies, so it is safe beside a stream capture) */
+                const volatile int* rec = d->place_smid;
+                bool all = true;
+                for (int c = 0; c < 74; ++c) all = all && rec[c] >= 0;
+                if (all) {
+                    bool ok = true;
+                    bool seen_tpc[74] = {}, seen_slot[74] = {};
+                    for (int c = 0; c < 74 && ok; ++c) {
+                        const int tpc = rec[c] >> 1;
+                        if (tpc >= 74 || seen_tpc[tpc]) { ok = false; break; }
+                        seen_tpc[tpc] = true;
+                        const int g8 = tpc & 7, q = tpc >> 3;
+                        const int sl = q >= 9 ? 72 + g8 : (3 * (g8 >> 1) + q / 3) * 6 + 3 * (g8 & 1) + q % 3;
+                        if (sl >= 74 || seen_slot[sl]) { ok = false; break; }
+                        seen_slot[sl] = true;
+                        d->place_slot[c] = (unsigned char)sl;
+                    }
+                    d->place_state = ok ? 2 : 3;
                 }
-                if (ok && cudaMemcpy(d->place_slot, slot, 74, cudaMemcpyHostToDevice) != cudaSuccess) { cudaGetLastError(); ok = false; }
-                d->place_state = ok ? 2 : 3;
-            } else if (d->place_state == 1) {
-                cudaGetLastError();                       /* cudaErrorNotReady */
             }
             if (d->place_state == 2) {
-                a.wave_slot = d->place_slot;
+                a.wave_slot_on = 1;
+                memcpy(a.wave_slot, d->place_slot, 74);
             } else if (d->place_state == 0) {
-                cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
-                if (cudaStreamIsCapturing(stream, &cap) != cudaSuccess) { cudaGetLastError(); cap = cudaStreamCaptureStatusActive; }
-                if (cap == cudaStreamCaptureStatusNone) {
-                    bool ready = true;
-                    if (!d->place_smid) {
-                        void* w = nullptr;
-                        ready = cudaHostAlloc(&w, sizeof(int) * PLACE_MAX, cudaHostAllocPortable | cudaHostAllocMapped) == cudaSuccess &&
-                                cudaMalloc(&d->place_slot, PLACE_MAX) == cudaSuccess &&
-                                cudaEventCreateWithFlags(&d->place_event, cudaEventDisableTiming) == cudaSuccess;
-                        if (ready) { d->place_smid = reinterpret_cast<int*>(w); for (int i = 0; i < PLACE_MAX; ++i) d->place_smid[i] = -1; }
-                        else { cudaGetLastError(); d->place_state = 3; }
-                    }
-                    if (ready) { a.smid_out = d->place_smid; place_recording = true; }
-                }
+                a.smid_out = d->place_smid;
             }
         }
     }
@@ -969,11 +964,6 @@ int launch_umma(const RpbProblem& p, void* C, const void* A, const void* B, Devi
     else if (BN == 64) rc = launch_umma_bn<T, 64>(pa.mn_major, pb.mn_major, ma, mb, mc, mp, a, grid, stream);
     else if (BN == 128) rc = launch_umma_bn<T, 128>(pa.mn_major, pb.mn_major, ma, mb, mc, mp, a, grid, stream);
     else rc = launch_umma_bn<T, 256>(pa.mn_major, pb.mn_major, ma, mb, mc, mp, a, grid, stream);
-    if (place_recording) {
-        std::lock_guard<std::mutex> lock(d->place_mu);
-        if (!rc && d->place_state == 0 && cudaEventRecord(d->place_event, stream) == cudaSuccess) d->place_state = 1;
-        else cudaGetLastError();
-    }
     if (rc) return -1;
     if ((a.bal || a.tail_fuse) && release_scratch(d, stream)) return -1;
     if (a.tail_splits > 1 && !a.tail_fuse) {

@@ -140,12 +140,13 @@ struct Args {
     int sync_every;        /* also every so many K blocks inside a tile (0: at tile starts only) */
     unsigned sync_sleep;   /* ns between polls of the counter */
     /* Placement-aware tile order (pairs on a full grid).  smid_out != null: the leader of unit u stores the SM it runs on
-     * in smid_out[u] (mapped host memory; the host learns where the hardware puts the clusters).  wave_slot != null:
+     * in smid_out[u] (mapped host memory; the host learns where the hardware puts the clusters).  wave_slot_on:
      * in every full wave of whole tiles unit u computes tile wave * units + wave_slot[u] instead of wave * units + u; the
      * host builds that permutation so that the units of one GPC -- which share an L2 request coalescer -- take a 3 x 3
      * block of the wave's tiles and ask for the same three A panels and three B panels. */
     int* smid_out;
-    const unsigned char* wave_slot;
+    int wave_slot_on;
+    unsigned char wave_slot[80];
     int wide_skew;         /* double-width tiles: K blocks by which the second accumulator trails the first at a tile's ends */
     int c_f32;             /* 1: the output is packed float32 [batch][m][n] (unrounded sums of 16-bit operands); the
                             * epilogue then writes it like a K slice: `partial` = the output when splits == 1 */
@@ -493,7 +494,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         asm volatile("mov.u32 %0, %%smid;" : "=r"(sm));
         args.smid_out[unit_id] = (int)sm;
     }
-    const uint32_t my_slot = args.wave_slot ? (uint32_t)args.wave_slot[unit_id] : (uint32_t)unit_id;
+    const uint32_t my_slot = args.wave_slot_on ? (uint32_t)args.wave_slot[unit_id] : (uint32_t)unit_id;
     auto next_item = [&](long long& w, int& phase, Item& o) -> bool {
         if (args.bal) {
             /* This CTA's (pair's) range [s, e) of tile x K-block units starts inside tile ta (at K block ka) and ends
@@ -549,7 +550,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             const uint32_t tiles_mn = (uint32_t)(args.tiles_m * args.tiles_n);
             uint32_t q = wi / tiles_mn;
             int t = (int)(wi - q * tiles_mn);
-            if (args.wave_slot) {                       /* splits == batch == 1: wi is the tile, wi % units this unit */
+            if (args.wave_slot_on) {                    /* splits == batch == 1: wi is the tile, wi % units this unit */
                 const uint32_t units = (uint32_t)work_step, wave = wi / units;
                 if ((wave + 1u) * units <= tb32) t = (int)(wave * units + my_slot);
             }
